@@ -1,0 +1,100 @@
+/* C ABI of libb200_linear.so: the linear-layer GEMMs of chriskuchar/llms-from-scratch-cuda
+ * (its cuda/matmul.cu) as hand-written sm_100a kernels.
+ *
+ * All matrices are dense row-major with the inner extent as leading dimension, exactly as
+ * the reference passes them (cuda/kernels.cuh:46-65):
+ *     A [M,K]   left input / saved activation
+ *     B [K,N]   weight, stored [in, out]
+ *     C [M,N]   output;  dC [M,N] upstream gradient;  dA [M,K];  dB [K,N]
+ * Every pointer is a device pointer on the context's device.  Calls are asynchronous on the
+ * context's stream (default: the legacy default stream, which is what the reference uses).
+ * Every function returns 0 on success or a B200_E_* code; nothing here calls exit().
+ */
+#ifndef B200_LINEAR_H
+#define B200_LINEAR_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200_linear_ctx b200_linear_ctx;
+
+enum {
+    B200_OK = 0,
+    B200_E_BADARG = 1,       /* null pointer, non-positive dimension, unknown enum */
+    B200_E_CUDA = 2,         /* a CUDA runtime/driver call failed (see b200_linear_last_cuda_error) */
+    B200_E_NODEVICE = 3,     /* no sm_100 device is current */
+    B200_E_DEVICE_WAIT = 4,  /* a kernel gave up on a bounded wait (see b200_linear_sync) */
+    B200_E_TOOBIG = 5        /* size beyond a stated limit */
+};
+
+/* GEMM selector for b200_linear_gemm_*: the three products of the linear layer. */
+enum {
+    B200_GEMM_FWD_NN = 0,    /* out[M,N]  = A[M,K] * B[K,N]             (cuda/matmul.cu:10,61)  */
+    B200_GEMM_DGRAD_NT = 1,  /* out[M,K]  = dC[M,N] * B[K,N]^T          (cuda/matmul.cu:30,82)  */
+    B200_GEMM_WGRAD_TN = 2   /* out[K,N] (+)= A[M,K]^T * dC[M,N]        (cuda/matmul.cu:40,94)  */
+};
+
+/* Context = what the reference keeps in its cublasHandle_t (cublasCreate / cublasDestroy in
+ * llama2-mistral/src/model.cpp:11,372,404,709): stream, SM count, tensor-map cache, split-K
+ * workspace and the device status word.  One per process and GPU. */
+int b200_linear_create(b200_linear_ctx** out);
+int b200_linear_destroy(b200_linear_ctx* ctx);
+/* cudaStream_t passed as void*; replaces cublasSetStream (never called by the reference,
+ * which stays on the legacy default stream). */
+int b200_linear_set_stream(b200_linear_ctx* ctx, void* cuda_stream);
+/* Synchronise the context's stream and return B200_E_DEVICE_WAIT if any kernel since the last
+ * call recorded a timed-out wait (the raw device code is stored in *device_code if non-null). */
+int b200_linear_sync(b200_linear_ctx* ctx, int* device_code);
+/* Number of kernels this library has launched on this context so far. */
+long long b200_linear_launch_count(const b200_linear_ctx* ctx);
+int b200_linear_last_cuda_error(const b200_linear_ctx* ctx);
+const char* b200_linear_strerror(int code);
+
+/* bf16 storage, fp32 accumulate.  Replaces
+ *   matmul_forward(cublasHandle_t, __nv_bfloat16* C, const __nv_bfloat16* A, const __nv_bfloat16* B, M,N,K)
+ *   cuda/matmul.cu:55-71, declared cuda/kernels.cuh:348.   C = bf16_rn(A*B). */
+int b200_linear_forward_bf16(b200_linear_ctx* ctx, void* C, const void* A, const void* B, int M, int N,
+                             int K);
+/* Replaces matmul_backward(handle, dA, dB, dC, A, B, M,N,K), cuda/matmul.cu:73-104, declared
+ * cuda/kernels.cuh:350.  dA = bf16_rn(dC*B^T);  dB = bf16_rn(float(dB) + A^T*dC)  (beta = 1).
+ * dA or dB may be NULL to skip that product. */
+int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* dB, const void* dC, const void* A,
+                              const void* B, int M, int N, int K);
+/* True-fp32 twins.  Replace matmul_forward / matmul_backward on float*, cuda/matmul.cu:4-48,
+ * declared cuda/kernels.cuh:47-65 (cublasSgemm, default math mode). */
+int b200_linear_forward_f32(b200_linear_ctx* ctx, float* C, const float* A, const float* B, int M, int N,
+                            int K);
+int b200_linear_backward_f32(b200_linear_ctx* ctx, float* dA, float* dB, const float* dC, const float* A,
+                             const float* B, int M, int N, int K);
+
+/* One product at a time, with beta in {0,1} selectable for every layout (the shape/layout/beta
+ * sweep).  `which` is a B200_GEMM_* value; M,N,K keep the meaning above for every `which`;
+ * x, y are the two inputs in the order of the formulas above (A,B / dC,B / A,dC). */
+int b200_linear_gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x,
+                          const void* y, int M, int N, int K);
+int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x,
+                         const float* y, int M, int N, int K);
+
+/* Tuning / introspection.  A plan is what the dispatcher would launch for a bf16 product:
+ * tile width BN (output columns per tile; 0 = CUDA-core kernel), cta_pair (1 = 2-CTA tiles),
+ * split-K factor.  Pure host arithmetic: usable without a GPU. */
+typedef struct {
+    int bn;
+    int cta_pair;
+    int splits;
+    int m_fastest;
+    int tiles;
+    int waves_x100;
+} b200_linear_plan_t;
+int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
+                          b200_linear_plan_t* plan);
+/* Force a plan for subsequent bf16 calls on this context (bn = -1 restores the heuristic). */
+int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_LINEAR_H */

@@ -1,0 +1,491 @@
+// Host side of libb200_linear.so: context, tensor-map cache, plan selection, kernel
+// dispatch and the extern "C" entry points declared in include/b200_linear.h.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <unordered_map>
+
+#include "../../include/b200_linear.h"
+#include "gemm_sm100.cuh"
+#include "gemm_simt.cuh"
+
+using namespace b200;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+struct TmKey {
+    const void* ptr;
+    uint64_t inner, outer;
+    uint32_t box_inner, box_outer;
+    bool operator==(const TmKey& o) const {
+        return ptr == o.ptr && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
+               box_outer == o.box_outer;
+    }
+};
+struct TmKeyHash {
+    size_t operator()(const TmKey& k) const {
+        uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.inner + 0x7F4A7C15u) * 0xBF58476D1CE4E5B9ull;
+        h ^= (k.outer + 0x1CE4E5B9u) * 0x94D049BB133111EBull;
+        h ^= (static_cast<uint64_t>(k.box_inner) << 32 | k.box_outer) * 0xD6E8FEB86659FD93ull;
+        return static_cast<size_t>(h ^ (h >> 29));
+    }
+};
+
+}  // namespace
+
+struct b200_linear_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    float* ws = nullptr;  // split-K workspace
+    size_t ws_bytes = 0;
+    int* status_dev = nullptr;
+    long long launches = 0;
+    int last_cuda = 0;
+    int force_bn = -1, force_pair = 0, force_splits = 0;
+    EncodeTiledFn encode = nullptr;
+    std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
+};
+
+namespace {
+
+int cuda_fail(b200_linear_ctx* ctx, cudaError_t e) {
+    if (ctx) ctx->last_cuda = static_cast<int>(e);
+    return B200_E_CUDA;
+}
+#define CU_TRY(ctx, expr)                                    \
+    do {                                                     \
+        cudaError_t e__ = (expr);                            \
+        if (e__ != cudaSuccess) return cuda_fail((ctx), e__); \
+    } while (0)
+
+// bf16 2-D tensor map over a row-major [outer][inner] matrix, 128-byte swizzle.
+int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
+                   uint32_t box_outer, CUtensorMap* out) {
+    TmKey key{ptr, inner, outer, box_inner, box_outer};
+    auto it = ctx->tm_cache.find(key);
+    if (it != ctx->tm_cache.end()) {
+        *out = it->second;
+        return B200_OK;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        ctx->last_cuda = 100000 + static_cast<int>(r);
+        return B200_E_CUDA;
+    }
+    if (ctx->tm_cache.size() > 8192) ctx->tm_cache.clear();
+    ctx->tm_cache.emplace(key, *out);
+    return B200_OK;
+}
+
+int ensure_workspace(b200_linear_ctx* ctx, size_t bytes) {
+    if (bytes <= ctx->ws_bytes) return B200_OK;
+    if (ctx->ws) CU_TRY(ctx, cudaFree(ctx->ws));
+    ctx->ws = nullptr;
+    ctx->ws_bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    CU_TRY(ctx, cudaMalloc(&ctx->ws, want));
+    ctx->ws_bytes = want;
+    return B200_OK;
+}
+
+inline int ceil_div_i(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace
+
+// ------------------------------------------------------------------- plan
+// Cost model in SM cycles.  One tcgen05.mma of 128 x BN x 16 takes BN/2 cycles at the
+// tensor-core rate; a stage of BK = 64 is four of them, and it also has to stream
+// (128 + BN) * 128 bytes out of shared memory at 128 B/cycle.
+static long long plan_cost(int Mo, int No, int Kc, int bn, int splits, int sms, int* tiles_out) {
+    const int m_tiles = ceil_div_i(Mo, BM), n_tiles = ceil_div_i(No, bn);
+    const int kb_total = ceil_div_i(Kc, BK);
+    const int kbps = ceil_div_i(kb_total, splits);
+    const int real_splits = ceil_div_i(kb_total, kbps);
+    const long long tiles = 1LL * m_tiles * n_tiles * real_splits;
+    const long long rounds = (tiles + sms - 1) / sms;
+    const long long mma = 2LL * bn > 128 + bn ? 2LL * bn : 128 + bn;
+    const long long mainloop = kbps * mma + 600;      // + pipeline fill per tile
+    const long long epilogue = 14LL * bn + 400;       // TMEM drain + stores per tile
+    long long cost = rounds * (mainloop > epilogue ? mainloop : epilogue) + epilogue + 3000;
+    if (real_splits > 1) {
+        const double bytes = 2.0 * real_splits * Mo * (double)No * 4.0;  // partials written, then read
+        cost += static_cast<long long>(bytes / 1800.0) + 5000;           // second kernel
+    }
+    if (tiles_out) *tiles_out = static_cast<int>(tiles);
+    return cost;
+}
+
+extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
+                                     b200_linear_plan_t* plan) {
+    (void)beta1;
+    if (!plan || M <= 0 || N <= 0 || K <= 0 || sm_count <= 0 || which < 0 || which > 2) return B200_E_BADARG;
+    int Mo, No, Kc;
+    if (which == B200_GEMM_FWD_NN) { Mo = M; No = N; Kc = K; }
+    else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; }
+    else { Mo = K; No = N; Kc = M; }
+    memset(plan, 0, sizeof(*plan));
+    if ((N % 8) != 0 || (K % 8) != 0) {  // a row pitch that TMA cannot describe
+        plan->bn = 0;
+        plan->splits = 1;
+        plan->tiles = ceil_div_i(Mo, ST_BM) * ceil_div_i(No, ST_BN);
+        return B200_OK;
+    }
+    static const int bns[4] = {256, 192, 128, 64};
+    static const int sps[12] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
+    const int kb_total = ceil_div_i(Kc, BK);
+    long long best = -1;
+    for (int bi = 0; bi < 4; ++bi) {
+        const int bn = bns[bi];
+        if (bn > 64 && bn - No >= 64) continue;  // tile much wider than the output
+        for (int si = 0; si < 12; ++si) {
+            const int s = sps[si];
+            if (s > 1 && kb_total / s < 4) break;  // keep >= 4 stages of work per split
+            int tiles = 0;
+            const long long c = plan_cost(Mo, No, Kc, bn, s, sm_count, &tiles);
+            if (best < 0 || c < best) {
+                best = c;
+                plan->bn = bn;
+                const int kbps = ceil_div_i(kb_total, s);
+                plan->splits = ceil_div_i(kb_total, kbps);
+                plan->tiles = tiles;
+            }
+        }
+    }
+    plan->cta_pair = 0;
+    plan->m_fastest = Mo <= No ? 1 : 0;
+    plan->waves_x100 = static_cast<int>(100LL * plan->tiles / sm_count);
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------- launch
+namespace {
+
+template <int BN, bool P_MN, bool Q_MN, int EPI>
+int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& gp,
+               int grid) {
+    using Cfg = TileCfg<BN>;
+    static bool configured = false;
+    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, EPI>;
+    if (!configured) {
+        CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured = true;
+    }
+    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tmP, tmQ, gp);
+    CU_TRY(ctx, cudaGetLastError());
+    ctx->launches++;
+    return B200_OK;
+}
+
+template <bool P_MN, bool Q_MN, int EPI>
+int launch_bn(b200_linear_ctx* ctx, int bn, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+              const GemmParams& gp, int grid) {
+    switch (bn) {
+        case 256: return launch_one<256, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
+        case 192: return launch_one<192, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
+        case 128: return launch_one<128, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
+        case 64: return launch_one<64, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
+        default: return B200_E_BADARG;
+    }
+}
+
+template <bool P_MN, bool Q_MN>
+int launch_epi(b200_linear_ctx* ctx, int bn, int epi, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+               const GemmParams& gp, int grid) {
+    switch (epi) {
+        case EPI_BF16: return launch_bn<P_MN, Q_MN, EPI_BF16>(ctx, bn, tmP, tmQ, gp, grid);
+        case EPI_BF16_BETA1: return launch_bn<P_MN, Q_MN, EPI_BF16_BETA1>(ctx, bn, tmP, tmQ, gp, grid);
+        default: return launch_bn<P_MN, Q_MN, EPI_F32_PARTIAL>(ctx, bn, tmP, tmQ, gp, grid);
+    }
+}
+
+template <typename T>
+int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, const T* y, int M, int N,
+                int K);
+
+// One bf16 product on the tensor cores (or the CUDA-core kernel for TMA-unfriendly pitches).
+int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x, const void* y, int M,
+              int N, int K) {
+    if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2)
+        return B200_E_BADARG;
+    b200_linear_plan_t plan;
+    int rc = b200_linear_plan_bf16(which, beta1, M, N, K, ctx->sm_count, &plan);
+    if (rc) return rc;
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
+                             reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    if (plan.bn == 0 || !aligned16)
+        return launch_simt<__nv_bfloat16>(ctx, which, beta1, static_cast<__nv_bfloat16*>(out),
+                                          static_cast<const __nv_bfloat16*>(x),
+                                          static_cast<const __nv_bfloat16*>(y), M, N, K);
+    int Mo, No, Kc;
+    bool p_mn, q_mn;
+    if (which == B200_GEMM_FWD_NN) { Mo = M; No = N; Kc = K; p_mn = false; q_mn = true; }
+    else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
+    else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
+
+    int bn = plan.bn, splits = plan.splits;
+    if (ctx->force_bn > 0) {
+        bn = ctx->force_bn;
+        splits = ctx->force_splits > 0 ? ctx->force_splits : 1;
+    }
+    GemmParams gp;
+    gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
+    gp.m_tiles = ceil_div_i(Mo, BM);
+    gp.n_tiles = ceil_div_i(No, bn);
+    gp.kb_total = ceil_div_i(Kc, BK);
+    if (splits > gp.kb_total) splits = gp.kb_total;
+    gp.kb_per_split = ceil_div_i(gp.kb_total, splits);
+    gp.splits = ceil_div_i(gp.kb_total, gp.kb_per_split);
+    gp.m_fastest = plan.m_fastest;
+    gp.status = ctx->status_dev;
+    const long long total_tiles = 1LL * gp.m_tiles * gp.n_tiles * gp.splits;
+    if (total_tiles > 0x7FFFFFFFLL) return B200_E_TOOBIG;
+    const int grid = total_tiles < ctx->sm_count ? static_cast<int>(total_tiles) : ctx->sm_count;
+
+    // Operand P has Mo rows, operand Q has No rows; x,y map onto them per product.
+    const void* P = x;
+    const void* Q = y;
+    CUtensorMap tmP, tmQ;
+    // K-major: [rows][Kc], box {BK, rows-per-tile}.  MN-major: [Kc][rows], box {64, BK}.
+    if (p_mn) rc = get_tensor_map(ctx, P, Mo, Kc, 64, BK, &tmP);
+    else      rc = get_tensor_map(ctx, P, Kc, Mo, BK, BM, &tmP);
+    if (rc) return rc;
+    if (q_mn) rc = get_tensor_map(ctx, Q, No, Kc, 64, BK, &tmQ);
+    else      rc = get_tensor_map(ctx, Q, Kc, No, BK, bn, &tmQ);
+    if (rc) return rc;
+
+    int epi = beta1 ? EPI_BF16_BETA1 : EPI_BF16;
+    if (gp.splits > 1) {
+        rc = ensure_workspace(ctx, static_cast<size_t>(gp.splits) * Mo * No * sizeof(float));
+        if (rc) return rc;
+        epi = EPI_F32_PARTIAL;
+        gp.out = ctx->ws;
+    } else {
+        gp.out = out;
+    }
+    if (p_mn) rc = launch_epi<true, true>(ctx, bn, epi, tmP, tmQ, gp, grid);
+    else if (q_mn) rc = launch_epi<false, true>(ctx, bn, epi, tmP, tmQ, gp, grid);
+    else rc = launch_epi<false, false>(ctx, bn, epi, tmP, tmQ, gp, grid);
+    if (rc) return rc;
+    if (gp.splits > 1) {
+        const long long n = 1LL * Mo * No;
+        long long blocks = (n / 8 + 255) / 256;
+        if (blocks > 4LL * ctx->sm_count) blocks = 4LL * ctx->sm_count;
+        if (beta1)
+            splitk_reduce_bf16<true><<<static_cast<int>(blocks), 256, 0, ctx->stream>>>(
+                static_cast<__nv_bfloat16*>(out), ctx->ws, n, gp.splits);
+        else
+            splitk_reduce_bf16<false><<<static_cast<int>(blocks), 256, 0, ctx->stream>>>(
+                static_cast<__nv_bfloat16*>(out), ctx->ws, n, gp.splits);
+        CU_TRY(ctx, cudaGetLastError());
+        ctx->launches++;
+    }
+    return B200_OK;
+}
+
+template <typename T, bool P_MN, bool Q_MN>
+int launch_simt_layout(b200_linear_ctx* ctx, const SimtParams& sp, bool vec) {
+    dim3 grid(ceil_div_i(sp.No, ST_BN), ceil_div_i(sp.Mo, ST_BM), sp.splits);
+    if (grid.y > 65535u) return B200_E_TOOBIG;
+    if constexpr (sizeof(T) == 4) {
+        if (vec) gemm_simt<T, P_MN, Q_MN, true><<<grid, ST_THREADS, 0, ctx->stream>>>(sp);
+        else     gemm_simt<T, P_MN, Q_MN, false><<<grid, ST_THREADS, 0, ctx->stream>>>(sp);
+    } else {
+        gemm_simt<T, P_MN, Q_MN, false><<<grid, ST_THREADS, 0, ctx->stream>>>(sp);
+    }
+    CU_TRY(ctx, cudaGetLastError());
+    ctx->launches++;
+    return B200_OK;
+}
+
+template <typename T>
+int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, const T* y, int M, int N,
+                int K) {
+    if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2)
+        return B200_E_BADARG;
+    SimtParams sp;
+    if (which == B200_GEMM_FWD_NN) { sp.Mo = M; sp.No = N; sp.Kc = K; }
+    else if (which == B200_GEMM_DGRAD_NT) { sp.Mo = M; sp.No = K; sp.Kc = N; }
+    else { sp.Mo = K; sp.No = N; sp.Kc = M; }
+    sp.P = x; sp.Q = y;
+    // Split the contraction when the output alone cannot fill the GPU.
+    const long long tiles = 1LL * ceil_div_i(sp.Mo, ST_BM) * ceil_div_i(sp.No, ST_BN);
+    int splits = 1;
+    if (tiles < ctx->sm_count) {
+        splits = static_cast<int>((2LL * ctx->sm_count + tiles - 1) / tiles);
+        const int max_splits = sp.Kc / 256 > 0 ? sp.Kc / 256 : 1;
+        if (splits > max_splits) splits = max_splits;
+        if (splits > 64) splits = 64;
+    }
+    int per = ceil_div_i(ceil_div_i(sp.Kc, splits), ST_BK) * ST_BK;
+    splits = ceil_div_i(sp.Kc, per);
+    sp.splits = splits;
+    sp.kc_per_split = per;
+    sp.beta1 = beta1;
+    if (splits > 1) {
+        int rc = ensure_workspace(ctx, static_cast<size_t>(splits) * sp.Mo * sp.No * sizeof(float));
+        if (rc) return rc;
+        sp.out = ctx->ws;
+    } else {
+        sp.out = out;
+    }
+    const bool vec = sizeof(T) == 4 && (N % 4) == 0 && (K % 4) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    int rc;
+    if (which == B200_GEMM_FWD_NN) rc = launch_simt_layout<T, false, true>(ctx, sp, vec);
+    else if (which == B200_GEMM_DGRAD_NT) rc = launch_simt_layout<T, false, false>(ctx, sp, vec);
+    else rc = launch_simt_layout<T, true, true>(ctx, sp, vec);
+    if (rc) return rc;
+    if (splits > 1) {
+        const long long n = 1LL * sp.Mo * sp.No;
+        long long blocks = (n + 255) / 256;
+        if (blocks > 8LL * ctx->sm_count) blocks = 8LL * ctx->sm_count;
+        splitk_reduce_generic<T><<<static_cast<int>(blocks), 256, 0, ctx->stream>>>(out, ctx->ws, n, splits, beta1);
+        CU_TRY(ctx, cudaGetLastError());
+        ctx->launches++;
+    }
+    return B200_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------ C entry points
+extern "C" int b200_linear_create(b200_linear_ctx** out) {
+    if (!out) return B200_E_BADARG;
+    *out = nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return B200_E_NODEVICE;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return B200_E_NODEVICE;
+    if (prop.major != 10) return B200_E_NODEVICE;  // tcgen05 / TMEM exist on sm_100 only
+    b200_linear_ctx* ctx = new b200_linear_ctx();
+    ctx->device = dev;
+    ctx->sm_count = prop.multiProcessorCount;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+        delete ctx;
+        return B200_E_CUDA;
+    }
+    ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
+        cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
+        delete ctx;
+        return B200_E_CUDA;
+    }
+    ctx->ws_bytes = 64ull << 20;
+    if (cudaMalloc(&ctx->ws, ctx->ws_bytes) != cudaSuccess) {
+        cudaFree(ctx->status_dev);
+        delete ctx;
+        return B200_E_CUDA;
+    }
+    *out = ctx;
+    return B200_OK;
+}
+
+extern "C" int b200_linear_destroy(b200_linear_ctx* ctx) {
+    if (!ctx) return B200_E_BADARG;
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(ctx->ws);
+    cudaFree(ctx->status_dev);
+    delete ctx;
+    return B200_OK;
+}
+
+extern "C" int b200_linear_set_stream(b200_linear_ctx* ctx, void* cuda_stream) {
+    if (!ctx) return B200_E_BADARG;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    return B200_OK;
+}
+
+extern "C" int b200_linear_sync(b200_linear_ctx* ctx, int* device_code) {
+    if (!ctx) return B200_E_BADARG;
+    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    int code = 0;
+    CU_TRY(ctx, cudaMemcpy(&code, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (device_code) *device_code = code;
+    if (code != 0) {
+        CU_TRY(ctx, cudaMemset(ctx->status_dev, 0, sizeof(int)));
+        return B200_E_DEVICE_WAIT;
+    }
+    return B200_OK;
+}
+
+extern "C" long long b200_linear_launch_count(const b200_linear_ctx* ctx) { return ctx ? ctx->launches : -1; }
+extern "C" int b200_linear_last_cuda_error(const b200_linear_ctx* ctx) { return ctx ? ctx->last_cuda : -1; }
+
+extern "C" const char* b200_linear_strerror(int code) {
+    switch (code) {
+        case B200_OK: return "ok";
+        case B200_E_BADARG: return "bad argument";
+        case B200_E_CUDA: return "CUDA call failed";
+        case B200_E_NODEVICE: return "no sm_100 device current";
+        case B200_E_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
+        case B200_E_TOOBIG: return "size beyond limit";
+        default: return "unknown error";
+    }
+}
+
+extern "C" int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits) {
+    if (!ctx) return B200_E_BADARG;
+    if (bn > 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return B200_E_BADARG;
+    ctx->force_bn = bn;
+    ctx->force_pair = cta_pair;
+    ctx->force_splits = splits;
+    return B200_OK;
+}
+
+extern "C" int b200_linear_gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x,
+                                     const void* y, int M, int N, int K) {
+    return gemm_bf16(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K);
+}
+extern "C" int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x,
+                                    const float* y, int M, int N, int K) {
+    return launch_simt<float>(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K);
+}
+
+extern "C" int b200_linear_forward_bf16(b200_linear_ctx* ctx, void* C, const void* A, const void* B, int M,
+                                        int N, int K) {
+    return gemm_bf16(ctx, B200_GEMM_FWD_NN, 0, C, A, B, M, N, K);
+}
+extern "C" int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* dB, const void* dC,
+                                         const void* A, const void* B, int M, int N, int K) {
+    if (!dA && !dB) return B200_E_BADARG;
+    if (dA) {
+        int rc = gemm_bf16(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K);
+        if (rc) return rc;
+    }
+    if (dB) return gemm_bf16(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K);
+    return B200_OK;
+}
+extern "C" int b200_linear_forward_f32(b200_linear_ctx* ctx, float* C, const float* A, const float* B, int M,
+                                       int N, int K) {
+    return launch_simt<float>(ctx, B200_GEMM_FWD_NN, 0, C, A, B, M, N, K);
+}
+extern "C" int b200_linear_backward_f32(b200_linear_ctx* ctx, float* dA, float* dB, const float* dC,
+                                        const float* A, const float* B, int M, int N, int K) {
+    if (!dA && !dB) return B200_E_BADARG;
+    if (dA) {
+        int rc = launch_simt<float>(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K);
+        if (rc) return rc;
+    }
+    if (dB) return launch_simt<float>(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K);
+    return B200_OK;
+}

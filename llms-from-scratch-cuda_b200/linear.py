@@ -1,0 +1,168 @@
+"""Host-side mirror of the reference's GEMM-leaf interface over the C ABI of libb200_linear.so.
+
+The reference's interface is C++ (cuda/kernels.cuh:47-65, 348-351 of
+chriskuchar/llms-from-scratch-cuda):
+
+    matmul_forward (handle, C, A, B, M, N, K)             C[M,N]  = A[M,K] @ B[K,N]
+    matmul_backward(handle, dA, dB, dC, A, B, M, N, K)    dA[M,K] = dC @ B^T ; dB[K,N] += A^T @ dC
+
+The functions below keep those names, argument order and meaning; the dtype overload
+(float* vs __nv_bfloat16*) is picked from the tensors' dtype.  Arguments are torch CUDA
+tensors (used only as device memory: `data_ptr()`) or raw integer device addresses.
+Unlike the reference (which prints and exits, cuda/tensor.h:10-29) errors raise
+`LinearError`.  There is no CPU or library fallback: if the CUDA library is missing the
+import of this module fails.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb200_linear.so")
+
+FWD_NN, DGRAD_NT, WGRAD_TN = 0, 1, 2
+
+
+class LinearError(RuntimeError):
+    def __init__(self, code, what, detail=""):
+        self.code = code
+        super().__init__(f"{what}: b200_linear error {code}{detail}")
+
+
+class Plan(ctypes.Structure):
+    _fields_ = [("bn", ctypes.c_int), ("cta_pair", ctypes.c_int), ("splits", ctypes.c_int),
+                ("m_fastest", ctypes.c_int), ("tiles", ctypes.c_int), ("waves_x100", ctypes.c_int)]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python llms-from-scratch-cuda_b200/build.py` "
+            "(there is no fallback path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    lib.b200_linear_create.argtypes = [ctypes.POINTER(vp)]
+    lib.b200_linear_destroy.argtypes = [vp]
+    lib.b200_linear_set_stream.argtypes = [vp, vp]
+    lib.b200_linear_sync.argtypes = [vp, ctypes.POINTER(ci)]
+    lib.b200_linear_launch_count.argtypes = [vp]
+    lib.b200_linear_launch_count.restype = ctypes.c_longlong
+    lib.b200_linear_last_cuda_error.argtypes = [vp]
+    lib.b200_linear_strerror.argtypes = [ci]
+    lib.b200_linear_strerror.restype = ctypes.c_char_p
+    for name in ("b200_linear_forward_bf16", "b200_linear_forward_f32"):
+        getattr(lib, name).argtypes = [vp, vp, vp, vp, ci, ci, ci]
+    for name in ("b200_linear_backward_bf16", "b200_linear_backward_f32"):
+        getattr(lib, name).argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci]
+    for name in ("b200_linear_gemm_bf16", "b200_linear_gemm_f32"):
+        getattr(lib, name).argtypes = [vp, ci, ci, vp, vp, vp, ci, ci, ci]
+    lib.b200_linear_plan_bf16.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(Plan)]
+    lib.b200_linear_force_plan.argtypes = [vp, ci, ci, ci]
+    return lib
+
+
+lib = _load()
+
+
+def strerror(code):
+    return lib.b200_linear_strerror(int(code)).decode()
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if not t.is_cuda:
+        raise LinearError(1, "argument", " (tensor is not on a CUDA device)")
+    if not t.is_contiguous():
+        raise LinearError(1, "argument", " (tensor is not contiguous)")
+    return t.data_ptr()
+
+
+def _suffix(*tensors):
+    for t in tensors:
+        if t is None or isinstance(t, int):
+            continue
+        if t.dtype == torch.bfloat16:
+            return "bf16"
+        if t.dtype == torch.float32:
+            return "f32"
+        raise LinearError(1, "argument", f" (unsupported dtype {t.dtype})")
+    raise LinearError(1, "argument", " (dtype cannot be inferred from raw pointers; pass dtype=)")
+
+
+class Handle:
+    """What the reference keeps in its cublasHandle_t: one per process and GPU."""
+
+    def __init__(self, stream=None):
+        h = ctypes.c_void_p()
+        rc = lib.b200_linear_create(ctypes.byref(h))
+        if rc:
+            raise LinearError(rc, "b200_linear_create", f" ({strerror(rc)})")
+        self._h = h
+        if stream is not None:
+            self.set_stream(stream)
+
+    def set_stream(self, stream):
+        s = stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+        self._check(lib.b200_linear_set_stream(self._h, ctypes.c_void_p(s)), "set_stream")
+
+    def _check(self, rc, what):
+        if rc:
+            raise LinearError(rc, what, f" ({strerror(rc)}; cuda {lib.b200_linear_last_cuda_error(self._h)})")
+
+    def sync(self):
+        """Wait for the stream and raise if any kernel recorded a timed-out wait."""
+        code = ctypes.c_int(0)
+        rc = lib.b200_linear_sync(self._h, ctypes.byref(code))
+        if rc:
+            raise LinearError(rc, "b200_linear_sync", f" ({strerror(rc)}; device code {code.value})")
+
+    @property
+    def launches(self):
+        return int(lib.b200_linear_launch_count(self._h))
+
+    def force_plan(self, bn=-1, cta_pair=0, splits=0):
+        self._check(lib.b200_linear_force_plan(self._h, bn, cta_pair, splits), "force_plan")
+
+    def destroy(self):
+        if self._h:
+            lib.b200_linear_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def matmul_forward(handle, C, A, B, M, N, K, dtype=None):
+    """C[M,N] = A[M,K] @ B[K,N]  (reference: cuda/matmul.cu:4-18 fp32, :55-71 bf16)."""
+    sfx = dtype or _suffix(C, A, B)
+    fn = getattr(lib, "b200_linear_forward_" + sfx)
+    handle._check(fn(handle._h, _ptr(C), _ptr(A), _ptr(B), M, N, K), "matmul_forward")
+
+
+def matmul_backward(handle, dA, dB, dC, A, B, M, N, K, dtype=None):
+    """dA[M,K] = dC @ B^T (overwrite); dB[K,N] += A^T @ dC  (reference: cuda/matmul.cu:21-48, 73-104)."""
+    sfx = dtype or _suffix(dA, dB, dC)
+    fn = getattr(lib, "b200_linear_backward_" + sfx)
+    handle._check(fn(handle._h, _ptr(dA), _ptr(dB), _ptr(dC), _ptr(A), _ptr(B), M, N, K), "matmul_backward")
+
+
+def gemm(handle, which, beta1, out, x, y, M, N, K, dtype=None):
+    """One product (FWD_NN / DGRAD_NT / WGRAD_TN) with beta in {0,1}: the sweep entry point."""
+    sfx = dtype or _suffix(out, x, y)
+    fn = getattr(lib, "b200_linear_gemm_" + sfx)
+    handle._check(fn(handle._h, which, int(bool(beta1)), _ptr(out), _ptr(x), _ptr(y), M, N, K), "gemm")
+
+
+def plan_bf16(which, beta1, M, N, K, sm_count=148):
+    p = Plan()
+    rc = lib.b200_linear_plan_bf16(which, int(bool(beta1)), M, N, K, sm_count, ctypes.byref(p))
+    if rc:
+        raise LinearError(rc, "plan_bf16", f" ({strerror(rc)})")
+    return p
