@@ -1,0 +1,443 @@
+#!/usr/bin/env python
+"""Benchmark of the linear-layer GEMM path (contract: one JSON line on stdout from rank 0).
+
+Workload ("step"): every GEMM of one LLaMA-2/Mistral-125M decoder layer plus the LM head,
+forward + backward, for one micro-batch of B=16 x T=512 = 8192 tokens in bf16 — the second
+configuration of BASELINE.json.  As the reference launches them (cuda/attention.cu:597-599,616;
+cuda/swiglu.cu:161-162,169; llama2-mistral/src/model.cpp:612,635): projections
+Q 768->768, K 768->256, V 768->256, O 768->768, gate 768->2048, up 768->2048, down 2048->768,
+LM head 768->32000; each runs matmul_forward once and matmul_backward once (dgrad, and wgrad
+accumulating into dW with beta=1), 24 GEMMs and 1.517e12 FLOP per step.  Inputs are seeded
+synthetic tensors (weights N(0,0.02), activations and upstream gradients N(0,1)).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+TOKENS = 8192  # B=16 x T=512
+# name, N (out features), K (in features)
+PROJECTIONS = [("q", 768, 768), ("k", 256, 768), ("v", 256, 768), ("o", 768, 768),
+               ("gate", 2048, 768), ("up", 2048, 768), ("down", 768, 2048), ("lm_head", 32000, 768)]
+STEP_FLOP = sum(3 * 2 * TOKENS * n * k for _, n, k in PROJECTIONS)
+ACCUM = 16  # micro-batches per optimizer step in the reference's training config
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": d.get("bf16_tflops"), "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "hbm_gbs": d.get("hbm_gbs"), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.rows:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not (t0 - 0.05 <= ts <= t1 + 0.15):
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def make_buffers(torch, dev, oracle_mod, host=False):
+    """Per-projection operand set. Device tensors; with host=True also pinned host copies of the
+    per-micro-batch operands (A and dC)."""
+    bufs = []
+    g = torch.Generator(device=dev).manual_seed(1234)
+    for i, (name, n, k) in enumerate(PROJECTIONS):
+        b = {"name": name, "N": n, "K": k}
+        b["A"] = torch.randn(TOKENS, k, device=dev, generator=g).to(torch.bfloat16)
+        b["B"] = (0.02 * torch.randn(k, n, device=dev, generator=g)).to(torch.bfloat16)
+        b["dC"] = torch.randn(TOKENS, n, device=dev, generator=g).to(torch.bfloat16)
+        b["C"] = torch.empty(TOKENS, n, device=dev, dtype=torch.bfloat16)
+        b["dA"] = torch.empty(TOKENS, k, device=dev, dtype=torch.bfloat16)
+        b["dB"] = torch.zeros(k, n, device=dev, dtype=torch.bfloat16)
+        if host:
+            b["A_host"] = b["A"].cpu().pin_memory()
+            b["dC_host"] = b["dC"].cpu().pin_memory()
+            b["dA_host"] = torch.empty(TOKENS, k, dtype=torch.bfloat16).pin_memory()
+        bufs.append(b)
+    return bufs
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()  # raises if the CUDA library is missing: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    h = pkg.Handle()
+    bufs = make_buffers(torch, dev, None, host=True)
+
+    def step_device():
+        for b in bufs:
+            pkg.matmul_forward(h, b["C"], b["A"], b["B"], TOKENS, b["N"], b["K"])
+        for b in reversed(bufs):
+            pkg.matmul_backward(h, b["dA"], b["dB"], b["dC"], b["A"], b["B"], TOKENS, b["N"], b["K"])
+
+    grad_flat = None
+    if world > 1:
+        # data parallel by tokens: every rank holds the same weights and its own 8192-token
+        # micro-batch; the dW buckets are summed across ranks once per optimizer step.
+        grad_flat = torch.zeros(sum(b["dB"].numel() for b in bufs), device=dev, dtype=torch.bfloat16)
+        off = 0
+        for b in bufs:
+            n = b["dB"].numel()
+            b["dB"] = grad_flat[off:off + n].view_as(b["dB"])
+            off += n
+
+    def exchange():
+        if world > 1:
+            dist.all_reduce(grad_flat)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step_device()
+    exchange()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    launches0 = h.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for i in range(args.steps):
+        step_device()
+        if (i + 1) % ACCUM == 0:
+            exchange()
+    if args.steps % ACCUM != 0:
+        exchange()  # the exchange is inside the timed region at least once
+    e1.record()
+    barrier()
+    t1 = time.time()
+    h.sync()
+    ms = e0.elapsed_time(e1)
+    launches = h.launches - launches0
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    value = world * args.steps * STEP_FLOP / (ms * 1e-3) / 1e12
+
+    # ---- end to end: host buffers in, host buffers out, through the same calls
+    h2d = sum(b["A_host"].numel() + b["dC_host"].numel() for b in bufs) * 2
+    d2h = sum(b["dA_host"].numel() for b in bufs) * 2
+
+    def step_e2e():
+        for b in bufs:
+            b["A"].copy_(b["A_host"], non_blocking=True)
+            b["dC"].copy_(b["dC_host"], non_blocking=True)
+        step_device()
+        for b in bufs:
+            b["dA_host"].copy_(b["dA"], non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    step_e2e()
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = t.item()
+    e2e_value = world * e2e_steps * STEP_FLOP / (ms_e2e * 1e-3) / 1e12
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- per-GEMM timing (rank 0): CUDA events on the launching stream, each GEMM alone
+    per = []
+    dominant = None
+    for b in bufs:
+        for kind, call, flop in (
+                ("fwd_nn", lambda: pkg.gemm(h, pkg.FWD_NN, 0, b["C"], b["A"], b["B"], TOKENS, b["N"], b["K"]), 1),
+                ("dgrad_nt", lambda: pkg.gemm(h, pkg.DGRAD_NT, 0, b["dA"], b["dC"], b["B"], TOKENS, b["N"], b["K"]), 1),
+                ("wgrad_tn", lambda: pkg.gemm(h, pkg.WGRAD_TN, 1, b["dB"], b["A"], b["dC"], TOKENS, b["N"], b["K"]), 1)):
+            for _ in range(3):
+                call()
+            reps = 10
+            l0 = h.launches
+            e0.record()
+            for _ in range(reps):
+                call()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / reps * 1e3
+            fl = 2.0 * TOKENS * b["N"] * b["K"]
+            rec = {"proj": b["name"], "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1),
+                   "launches_per_call": (h.launches - l0) // reps}
+            per.append(rec)
+            if dominant is None or us > dominant["us"]:
+                dominant = dict(rec, flop=fl)
+    h.sync()
+    peaks = measured_peaks()
+    total_us = sum(r["us"] for r in per)
+    roofline = {"bound": "tensor", "kernel": "gemm_bf16_sm100 (%s %s, M=8192)" % (dominant["proj"], dominant["gemm"]),
+                "achieved": round(dominant["flop"] / dominant["us"] / 1e6, 1), "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s", "frac": round(dominant["flop"] / dominant["us"] / 1e6 / peaks["bf16_tflops"], 4),
+                "peak_source": peaks["source"] + " (burst: kernel timed alone)",
+                "share_of_step": round(dominant["us"] / total_us, 3), "traffic": None,
+                "step_frac_of_sustained": round(value / world / peaks["bf16_tflops_sustained"], 4)}
+
+    cpu = cpu_baseline_port()
+    line = {"metric": "bf16 GEMM TFLOP/s, all linear-layer GEMMs of one 125M decoder layer + LM head, fwd+bwd",
+            "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[1]: decoder-layer projections (Q,K,V,O,gate,up,down) + LM head 768->32000, "
+                                   "M=8192 tokens (B16xT512), fwd + dgrad + wgrad(beta=1), 24 GEMMs/step",
+                       "l2": "no flush: the step's working set (~1.7 GB, every GEMM its own buffers) exceeds the 126 MB L2",
+                       "parallelism": "dp%d by tokens, dW all-reduce (NCCL) every %d micro-batches" % (world, ACCUM),
+                       "flop_per_step": STEP_FLOP},
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "what": "A and dC of every projection copied from pinned host memory, 24 GEMMs through the C ABI, every dA read back"},
+            "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline_port(seconds_hint=15.0):
+    """The oracle's fp32 host GEMM (a CPU restatement of cuda/matmul.cu: the reference has no CPU
+    code) on a bounded sample: the seven decoder-layer projections at M=8192, fwd+dgrad+wgrad."""
+    import numpy as np
+    from oracle import oracle
+    flops, secs = 0.0, 0.0
+    rng = np.random.default_rng(0)
+    passes = 0
+    while secs < 10.0 and passes < 8:
+      passes += 1
+      for name, n, k in PROJECTIONS[:-1]:
+        A = rng.standard_normal((TOKENS, k), dtype=np.float32)
+        B = (0.02 * rng.standard_normal((k, n), dtype=np.float32))
+        dC = rng.standard_normal((TOKENS, n), dtype=np.float32)
+        C = np.empty((TOKENS, n), np.float32)
+        dA = np.empty((TOKENS, k), np.float32)
+        dB = np.zeros((k, n), np.float32)
+        t = time.time()
+        oracle.gemm_f32(0, 0, C, A, B, TOKENS, n, k)
+        oracle.gemm_f32(1, 0, dA, dC, B, TOKENS, n, k)
+        oracle.gemm_f32(2, 1, dB, A, dC, TOKENS, n, k)
+        secs += time.time() - t
+        flops += 3 * 2.0 * TOKENS * n * k
+    return {"value": round(flops / secs / 1e12, 4), "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+            "seconds": round(secs, 2),
+            "sample": "fp32 OpenMP host GEMM (oracle/oracle_gemm.c), the 7 decoder-layer projections at M=8192, "
+                      "fwd+dgrad+wgrad, %d pass(es) (no LM head)" % passes}
+
+
+def run_reference(args):
+    """The reference's own, unmodified cuda/matmul.cu (cuBLAS) from oracle/_ref on the same workload
+    and GPU; where that build is absent, the oracle's CPU port on a bounded sample."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_matmul.so")
+    base = {"impl": "reference", "metric": "bf16 GEMM TFLOP/s, all linear-layer GEMMs of one 125M decoder layer + LM head, fwd+bwd",
+            "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "data": "synthetic"}
+    import torch
+    if not os.path.exists(path) or not torch.cuda.is_available():
+        cpu = cpu_baseline_port()
+        base.update({"value": cpu["value"], "dtype": "f32", "ms_per_step": None, "cpu_baseline": cpu,
+                     "config": {"workload": cpu["sample"]},
+                     "e2e": {"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        print(json.dumps(base))
+        return
+    lib = ctypes.CDLL(path)
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    lib.ref_create.argtypes = [ctypes.POINTER(vp)]
+    lib.ref_matmul_forward_bf16.argtypes = [vp, vp, vp, vp, ci, ci, ci]
+    lib.ref_matmul_forward_bf16.restype = None
+    lib.ref_matmul_backward_bf16.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci]
+    lib.ref_matmul_backward_bf16.restype = None
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    hd = vp()
+    assert lib.ref_create(ctypes.byref(hd)) == 0
+    bufs = make_buffers(torch, dev, None)
+
+    def step():
+        for b in bufs:
+            lib.ref_matmul_forward_bf16(hd, b["C"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"])
+        for b in reversed(bufs):
+            lib.ref_matmul_backward_bf16(hd, b["dA"].data_ptr(), b["dB"].data_ptr(), b["dC"].data_ptr(),
+                                         b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = e0.elapsed_time(e1)
+    value = args.steps * STEP_FLOP / (ms * 1e-3) / 1e12
+    per = []
+    for b in bufs:
+        for kind, call in (("fwd_nn", lambda: lib.ref_matmul_forward_bf16(hd, b["C"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"])),
+                           ("dgrad+wgrad", lambda: lib.ref_matmul_backward_bf16(hd, b["dA"].data_ptr(), b["dB"].data_ptr(), b["dC"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"]))):
+            for _ in range(3):
+                call()
+            e0.record()
+            for _ in range(10):
+                call()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 10 * 1e3
+            fl = 2.0 * TOKENS * b["N"] * b["K"] * (1 if kind == "fwd_nn" else 2)
+            per.append({"proj": b["name"], "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1)})
+    base.update({"value": round(value, 2), "dtype": "bf16", "ms_per_step": round(ms / args.steps, 4),
+                 "config": {"workload": "configs[1]: decoder-layer projections (Q,K,V,O,gate,up,down) + LM head 768->32000, "
+                                        "M=8192 tokens (B16xT512), fwd + dgrad + wgrad(beta=1), 24 GEMMs/step",
+                            "implementation": "reference cuda/matmul.cu unmodified (cuBLAS) on the same GPU; the reference has no CPU implementation of this path",
+                            "flop_per_step": STEP_FLOP},
+                 "clocks": sampler.stop(t0, t1),
+                 "cpu_baseline": {"value": round(value, 2), "unit": "TFLOP/s", "cores": 0, "kind": "reference",
+                                  "sample": "whole workload on the GPU (cuBLAS); not a CPU run"},
+                 "e2e": {"value": round(value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                 "per_gemm": per})
+    print(json.dumps(base))
+
+
+def run_only(args):
+    """One GEMM of the workload, a few launches, at a reduced token count: the small case that
+    profiler captures use (still larger than L2 for the LM head)."""
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    h = pkg.Handle()
+    proj, kind = args.only.split(":")
+    n, k = {name: (n, k) for name, n, k in PROJECTIONS}[proj]
+    M = args.tokens
+    g = torch.Generator(device=dev).manual_seed(7)
+    A = torch.randn(M, k, device=dev, generator=g).to(torch.bfloat16)
+    B = (0.02 * torch.randn(k, n, device=dev, generator=g)).to(torch.bfloat16)
+    dC = torch.randn(M, n, device=dev, generator=g).to(torch.bfloat16)
+    which = {"fwd_nn": pkg.FWD_NN, "dgrad_nt": pkg.DGRAD_NT, "wgrad_tn": pkg.WGRAD_TN}[kind]
+    out = torch.zeros({0: (M, n), 1: (M, k), 2: (k, n)}[which], device=dev, dtype=torch.bfloat16)
+    x, y = {0: (A, B), 1: (dC, B), 2: (A, dC)}[which]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pkg.gemm(h, which, which == 2, out, x, y, M, n, k)
+    e0.record()
+    for _ in range(args.reps):
+        pkg.gemm(h, which, which == 2, out, x, y, M, n, k)
+    e1.record()
+    torch.cuda.synchronize()
+    h.sync()
+    us = e0.elapsed_time(e1) / args.reps * 1e3
+    print(json.dumps({"only": args.only, "tokens": M, "N": n, "K": k, "us": round(us, 2),
+                      "tflops": round(2.0 * M * n * k / us / 1e6, 1), "launches": h.launches}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, help="profile mode: <projection>:<fwd_nn|dgrad_nt|wgrad_tn>")
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -177,41 +177,59 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
 // ---------------------------------------------------------------- launch
 namespace {
 
-template <int BN, bool P_MN, bool Q_MN, int EPI>
+template <int BN, bool P_MN, bool Q_MN, int EPI, int CTAS>
 int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& gp,
                int grid) {
-    using Cfg = TileCfg<BN>;
+    using Cfg = TileCfg<BN, CTAS>;
     static bool configured = false;
-    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, EPI>;
+    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, EPI, CTAS>;
     if (!configured) {
         CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured = true;
     }
-    kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(tmP, tmQ, gp);
-    CU_TRY(ctx, cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, gp));
     ctx->launches++;
     return B200_OK;
 }
 
 template <bool P_MN, bool Q_MN, int EPI>
-int launch_bn(b200_linear_ctx* ctx, int bn, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+int launch_bn(b200_linear_ctx* ctx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
               const GemmParams& gp, int grid) {
+    if (ctas == 2) {
+        switch (bn) {
+            case 256: return launch_one<256, P_MN, Q_MN, EPI, 2>(ctx, tmP, tmQ, gp, grid);
+            case 128: return launch_one<128, P_MN, Q_MN, EPI, 2>(ctx, tmP, tmQ, gp, grid);
+            default: return B200_E_BADARG;
+        }
+    }
     switch (bn) {
-        case 256: return launch_one<256, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
-        case 192: return launch_one<192, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
-        case 128: return launch_one<128, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
-        case 64: return launch_one<64, P_MN, Q_MN, EPI>(ctx, tmP, tmQ, gp, grid);
+        case 256: return launch_one<256, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
+        case 192: return launch_one<192, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
+        case 128: return launch_one<128, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
+        case 64: return launch_one<64, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
         default: return B200_E_BADARG;
     }
 }
 
 template <bool P_MN, bool Q_MN>
-int launch_epi(b200_linear_ctx* ctx, int bn, int epi, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+int launch_epi(b200_linear_ctx* ctx, int bn, int ctas, int epi, const CUtensorMap& tmP, const CUtensorMap& tmQ,
                const GemmParams& gp, int grid) {
     switch (epi) {
-        case EPI_BF16: return launch_bn<P_MN, Q_MN, EPI_BF16>(ctx, bn, tmP, tmQ, gp, grid);
-        case EPI_BF16_BETA1: return launch_bn<P_MN, Q_MN, EPI_BF16_BETA1>(ctx, bn, tmP, tmQ, gp, grid);
-        default: return launch_bn<P_MN, Q_MN, EPI_F32_PARTIAL>(ctx, bn, tmP, tmQ, gp, grid);
+        case EPI_BF16: return launch_bn<P_MN, Q_MN, EPI_BF16>(ctx, bn, ctas, tmP, tmQ, gp, grid);
+        case EPI_BF16_BETA1: return launch_bn<P_MN, Q_MN, EPI_BF16_BETA1>(ctx, bn, ctas, tmP, tmQ, gp, grid);
+        default: return launch_bn<P_MN, Q_MN, EPI_F32_PARTIAL>(ctx, bn, ctas, tmP, tmQ, gp, grid);
     }
 }
 
@@ -239,14 +257,15 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
     else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
 
-    int bn = plan.bn, splits = plan.splits;
+    int bn = plan.bn, splits = plan.splits, ctas = plan.cta_pair ? 2 : 1;
     if (ctx->force_bn > 0) {
         bn = ctx->force_bn;
         splits = ctx->force_splits > 0 ? ctx->force_splits : 1;
+        ctas = ctx->force_pair ? 2 : 1;
     }
     GemmParams gp;
     gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
-    gp.m_tiles = ceil_div_i(Mo, BM);
+    gp.m_tiles = ceil_div_i(Mo, BM * ctas);
     gp.n_tiles = ceil_div_i(No, bn);
     gp.kb_total = ceil_div_i(Kc, BK);
     if (splits > gp.kb_total) splits = gp.kb_total;
@@ -256,7 +275,8 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     gp.status = ctx->status_dev;
     const long long total_tiles = 1LL * gp.m_tiles * gp.n_tiles * gp.splits;
     if (total_tiles > 0x7FFFFFFFLL) return B200_E_TOOBIG;
-    const int grid = total_tiles < ctx->sm_count ? static_cast<int>(total_tiles) : ctx->sm_count;
+    const int slots = ctx->sm_count / ctas;  // CTAs (or CTA pairs) resident at once
+    const int grid = (total_tiles < slots ? static_cast<int>(total_tiles) : slots) * ctas;
 
     // Operand P has Mo rows, operand Q has No rows; x,y map onto them per product.
     const void* P = x;
@@ -267,7 +287,7 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     else      rc = get_tensor_map(ctx, P, Kc, Mo, BK, BM, &tmP);
     if (rc) return rc;
     if (q_mn) rc = get_tensor_map(ctx, Q, No, Kc, 64, BK, &tmQ);
-    else      rc = get_tensor_map(ctx, Q, Kc, No, BK, bn, &tmQ);
+    else      rc = get_tensor_map(ctx, Q, Kc, No, BK, bn / ctas, &tmQ);
     if (rc) return rc;
 
     int epi = beta1 ? EPI_BF16_BETA1 : EPI_BF16;
@@ -279,9 +299,9 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     } else {
         gp.out = out;
     }
-    if (p_mn) rc = launch_epi<true, true>(ctx, bn, epi, tmP, tmQ, gp, grid);
-    else if (q_mn) rc = launch_epi<false, true>(ctx, bn, epi, tmP, tmQ, gp, grid);
-    else rc = launch_epi<false, false>(ctx, bn, epi, tmP, tmQ, gp, grid);
+    if (p_mn) rc = launch_epi<true, true>(ctx, bn, ctas, epi, tmP, tmQ, gp, grid);
+    else if (q_mn) rc = launch_epi<false, true>(ctx, bn, ctas, epi, tmP, tmQ, gp, grid);
+    else rc = launch_epi<false, false>(ctx, bn, ctas, epi, tmP, tmQ, gp, grid);
     if (rc) return rc;
     if (gp.splits > 1) {
         const long long n = 1LL * Mo * No;
@@ -446,6 +466,7 @@ extern "C" const char* b200_linear_strerror(int code) {
 extern "C" int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits) {
     if (!ctx) return B200_E_BADARG;
     if (bn > 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return B200_E_BADARG;
+    if (bn > 0 && cta_pair && bn != 128 && bn != 256) return B200_E_BADARG;
     ctx->force_bn = bn;
     ctx->force_pair = cta_pair;
     ctx->force_splits = splits;

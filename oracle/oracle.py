@@ -37,6 +37,8 @@ lib = _load()
 
 
 def out_shape(which, M, N, K):
+    if which not in (FWD_NN, DGRAD_NT, WGRAD_TN):
+        raise ValueError(f"unknown product {which}")
     return {FWD_NN: (M, N), DGRAD_NT: (M, K), WGRAD_TN: (K, N)}[which]
 
 

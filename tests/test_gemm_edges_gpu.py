@@ -1,0 +1,183 @@
+"""GPU edge cases and size-independent properties of the linear-layer GEMMs (through the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run(pkg, handle, which, beta, x, y, old, M, N, K):
+    out = old.clone()
+    pkg.gemm(handle, which, beta, out, x, y, M, N, K)
+    handle.sync()
+    return out
+
+
+def _ref64(which, beta, x, y, old):
+    xd, yd = x.double(), y.double()
+    r = {0: lambda: xd @ yd, 1: lambda: xd @ yd.T, 2: lambda: xd.T @ yd}[which]()
+    return r + old.double() if beta else r
+
+
+def _shapes(which, M, N, K):
+    ins = {0: ((M, K), (K, N)), 1: ((M, N), (K, N)), 2: ((M, K), (M, N))}[which]
+    out = {0: (M, N), 1: (M, K), 2: (K, N)}[which]
+    return ins, out
+
+
+# ragged sizes: M free; N, K multiples of 8 (tensor-core path with tails) and not (CUDA-core path)
+RAGGED = [(1, 8, 8), (127, 136, 72), (129, 264, 200), (1000, 520, 1032), (257, 250, 130), (33, 7, 5),
+          (4100, 768, 24), (300, 8, 4096)]
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+@pytest.mark.parametrize("dt,tol", [(torch.bfloat16, 1e-2), (torch.float32, 1e-5)])
+def test_ragged_shapes(pkg, handle, which, dt, tol):
+    g = torch.Generator(device=DEV).manual_seed(1234 + which)
+    for (M, N, K) in RAGGED:
+        ins, outs = _shapes(which, M, N, K)
+        x = torch.randn(ins[0], device=DEV, generator=g).to(dt)
+        y = torch.randn(ins[1], device=DEV, generator=g).to(dt)
+        old = torch.randn(outs, device=DEV, generator=g).to(dt)
+        for beta in (0, 1):
+            got = _run(pkg, handle, which, beta, x, y, old, M, N, K)
+            want = _ref64(which, beta, x, y, old)
+            err = ((got.double() - want).abs().max() / want.abs().max().clamp_min(1e-30)).item()
+            assert err <= tol, (which, dt, M, N, K, beta, err)
+
+
+@pytest.mark.parametrize("bn,pair", [(64, 0), (128, 0), (192, 0), (256, 0), (128, 1), (256, 1)])
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_every_tile_shape_and_split(pkg, handle, which, bn, pair):
+    """Each tile width, single CTA and CTA pair, with and without split-K, beta 0 and 1."""
+    g = torch.Generator(device=DEV).manual_seed(99)
+    dt = torch.bfloat16
+    try:
+        for (M, N, K) in [(384, 512, 320), (1000, 264, 136), (2048, 768, 768)]:
+            ins, outs = _shapes(which, M, N, K)
+            x = torch.randn(ins[0], device=DEV, generator=g).to(dt)
+            y = torch.randn(ins[1], device=DEV, generator=g).to(dt)
+            old = torch.randn(outs, device=DEV, generator=g).to(dt)
+            for splits, beta in ((1, 0), (1, 1), (3, 0), (2, 1)):
+                handle.force_plan(bn, pair, splits)
+                got = _run(pkg, handle, which, beta, x, y, old, M, N, K)
+                want = _ref64(which, beta, x, y, old)
+                err = ((got.double() - want).abs().max() / want.abs().max()).item()
+                assert err <= 1e-2, (which, bn, pair, splits, beta, M, N, K, err)
+    finally:
+        handle.force_plan(-1, 0, 0)
+
+
+def test_identity_weight_is_exact(pkg, handle):
+    """B = I: forward returns A and dgrad returns dC bit for bit; A = I: wgrad returns dC + old."""
+    dt = torch.bfloat16
+    M = N = K = 1024
+    g = torch.Generator(device=DEV).manual_seed(5)
+    a = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    eye = torch.eye(K, device=DEV, dtype=dt)
+    c = torch.empty(M, N, device=DEV, dtype=dt)
+    pkg.matmul_forward(handle, c, a, eye, M, N, K)
+    da = torch.empty(M, K, device=DEV, dtype=dt)
+    db = torch.zeros(K, N, device=DEV, dtype=dt)
+    pkg.matmul_backward(handle, da, db, a, eye, eye, M, N, K)  # dC := a, A := I
+    handle.sync()
+    assert torch.equal(c, a)
+    assert torch.equal(da, a)
+    assert torch.equal(db, a)
+
+
+def test_permutation_at_full_lm_head_width(pkg, handle):
+    """At the 32000-wide LM head: a 0/1 selection matrix as weight makes every output element a
+    copy of one input element, so the result is exact at any size."""
+    dt = torch.bfloat16
+    M, N, K = 8192, 32000, 768
+    g = torch.Generator(device=DEV).manual_seed(6)
+    a = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    sel = torch.randint(0, K, (N,), device=DEV, generator=g)
+    b = torch.zeros(K, N, device=DEV, dtype=dt)
+    b[sel, torch.arange(N, device=DEV)] = 1
+    c = torch.empty(M, N, device=DEV, dtype=dt)
+    pkg.matmul_forward(handle, c, a, b, M, N, K)
+    handle.sync()
+    assert torch.equal(c, a[:, sel])
+
+
+def test_zero_inputs_and_beta(pkg, handle):
+    dt = torch.bfloat16
+    M, N, K = 512, 256, 384
+    z = torch.zeros(M, K, device=DEV, dtype=dt)
+    dc = torch.randn(M, N, device=DEV).to(dt)
+    old = torch.randn(K, N, device=DEV).to(dt)
+    db = old.clone()
+    pkg.matmul_backward(handle, None, db, dc, z, None, M, N, K)  # A = 0: dB unchanged by beta=1
+    handle.sync()
+    assert torch.equal(db, old)
+    out = torch.full((K, N), 7.0, device=DEV, dtype=dt)
+    pkg.gemm(handle, 2, 0, out, z, dc, M, N, K)                    # beta = 0 overwrites
+    handle.sync()
+    assert not out.any()
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_run_to_run_determinism(pkg, handle, which):
+    dt = torch.bfloat16
+    M, N, K = 8192, 768, 768
+    ins, outs = _shapes(which, M, N, K)
+    x = torch.randn(ins[0], device=DEV).to(dt)
+    y = torch.randn(ins[1], device=DEV).to(dt)
+    old = torch.randn(outs, device=DEV).to(dt)
+    first = _run(pkg, handle, which, 1, x, y, old, M, N, K)
+    for _ in range(3):
+        assert torch.equal(_run(pkg, handle, which, 1, x, y, old, M, N, K), first)
+
+
+def test_linearity_in_fp32(pkg, handle):
+    M, N, K = 640, 384, 256
+    x1 = torch.randn(M, K, device=DEV)
+    x2 = torch.randn(M, K, device=DEV)
+    y = torch.randn(K, N, device=DEV)
+    z = torch.zeros(M, N, device=DEV)
+    s = _run(pkg, handle, 0, 0, x1, y, z, M, N, K) + _run(pkg, handle, 0, 0, x2, y, z, M, N, K)
+    t = _run(pkg, handle, 0, 0, x1 + x2, y, z, M, N, K)
+    assert ((s - t).abs().max() / t.abs().max()).item() <= 1e-5
+
+
+def test_bad_arguments_return_errors(pkg, handle):
+    t = torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16)
+    for args in ((t, t, t, 0, 64, 64), (t, t, t, 64, -1, 64), (t, t, t, 64, 64, 0)):
+        with pytest.raises(pkg.LinearError) as e:
+            pkg.matmul_forward(handle, *args)
+        assert e.value.code == 1
+    with pytest.raises(pkg.LinearError):
+        pkg.matmul_forward(handle, None, t, t, 64, 64, 64)
+    with pytest.raises(pkg.LinearError):
+        pkg.matmul_backward(handle, None, None, t, t, t, 64, 64, 64)
+    with pytest.raises(pkg.LinearError):
+        pkg.gemm(handle, 7, 0, t, t, t, 64, 64, 64)
+    with pytest.raises(pkg.LinearError):
+        pkg.matmul_forward(handle, t, t.cpu(), t, 64, 64, 64)
+    handle.sync()  # the context is still usable
+    pkg.matmul_forward(handle, t, t, t, 64, 64, 64)
+    handle.sync()
+
+
+def test_launch_counter_counts_our_kernels(pkg, handle):
+    t = torch.zeros(256, 256, device=DEV, dtype=torch.bfloat16)
+    before = handle.launches
+    pkg.matmul_forward(handle, t.clone(), t, t, 256, 256, 256)
+    handle.sync()
+    assert handle.launches > before
+
+
+def test_misaligned_pointers_take_the_cuda_core_path(pkg, handle):
+    dt = torch.bfloat16
+    M, N, K = 200, 72, 40
+    buf = torch.randn(M * K + 1, device=DEV).to(dt)
+    a = buf[1:].view(M, K)  # 2-byte aligned only
+    b = torch.randn(K, N, device=DEV).to(dt)
+    c = torch.empty(M, N, device=DEV, dtype=dt)
+    pkg.matmul_forward(handle, c, a.data_ptr(), b, M, N, K, dtype="bf16")
+    handle.sync()
+    want = a.double() @ b.double()
+    assert ((c.double() - want).abs().max() / want.abs().max()).item() <= 1e-2

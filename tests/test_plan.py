@@ -1,0 +1,46 @@
+"""Host-side plan selection (pure arithmetic, no GPU): invariants over the BASELINE shapes."""
+import itertools
+
+import pytest
+
+MS = [512, 2048, 8192, 16384, 65536]
+NKS = [768, 1280, 2048, 4096, 8192, 32000, 128256]
+
+
+def _dims(which, M, N, K):
+    return {0: (M, N, K), 1: (M, K, N), 2: (K, N, M)}[which]
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_plan_invariants(pkg, which):
+    for M, N, K in itertools.product(MS, NKS, NKS):
+        p = pkg.plan_bf16(which, which == 2, M, N, K, 148)
+        Mo, No, Kc = _dims(which, M, N, K)
+        assert p.bn in (64, 128, 192, 256)
+        kb = -(-Kc // 64)
+        assert 1 <= p.splits <= kb
+        per = -(-kb // p.splits)
+        assert (p.splits - 1) * per < kb  # every split owns at least one block
+        tiles = -(-Mo // 128) * -(-No // p.bn) * p.splits
+        assert p.tiles == tiles
+        assert p.m_fastest in (0, 1)
+
+
+def test_small_weight_gradients_split_the_token_dimension(pkg):
+    # dW of the 125M projections: the output alone gives far fewer tiles than SMs
+    for N, K in ((768, 768), (256, 768), (2048, 768), (768, 2048)):
+        p = pkg.plan_bf16(2, 1, 8192, N, K, 148)
+        assert p.splits > 1
+        assert p.tiles >= 74
+
+
+def test_unaligned_pitch_goes_to_cuda_core_kernel(pkg):
+    assert pkg.plan_bf16(0, 0, 100, 250, 136, 148).bn == 0
+    assert pkg.plan_bf16(0, 0, 100, 256, 130, 148).bn == 0
+    assert pkg.plan_bf16(0, 0, 101, 256, 136, 148).bn != 0  # M needs no alignment
+
+
+def test_plan_rejects_bad_arguments(pkg):
+    for args in ((3, 0, 8, 8, 8, 148), (0, 0, 0, 8, 8, 148), (0, 0, 8, -1, 8, 148), (0, 0, 8, 8, 8, 0)):
+        with pytest.raises(pkg.LinearError):
+            pkg.plan_bf16(*args)
