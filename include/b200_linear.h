@@ -79,8 +79,10 @@ int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out,
                          const float* y, int M, int N, int K);
 
 /* Tuning / introspection.  A plan is what the dispatcher would launch for a bf16 product:
- * tile width BN (output columns per tile; 0 = CUDA-core kernel), cta_pair (1 = 2-CTA tiles),
- * split-K factor.  Pure host arithmetic: usable without a GPU. */
+ * tile width BN (output columns per tile; 0 = CUDA-core kernel), cta_pair (1 = 256-row tiles
+ * computed by a 2-CTA cluster), and the work split: of `tiles` output tiles the first `dp_tiles`
+ * are computed whole, the others are each cut into `splits` ranges of the contraction
+ * (`sk_items` partial work items in all).  Pure host arithmetic: usable without a GPU. */
 typedef struct {
     int bn;
     int cta_pair;
@@ -88,10 +90,13 @@ typedef struct {
     int m_fastest;
     int tiles;
     int waves_x100;
+    int dp_tiles;
+    int sk_items;
 } b200_linear_plan_t;
 int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
                           b200_linear_plan_t* plan);
-/* Force a plan for subsequent bf16 calls on this context (bn = -1 restores the heuristic). */
+/* Force a plan for subsequent bf16 calls on this context (bn = -1 restores the heuristic).
+ * splits: 0 = cut only the ragged last wave (automatic), 1 = cut nothing, >= 2 = cut every tile. */
 int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits);
 
 #ifdef __cplusplus

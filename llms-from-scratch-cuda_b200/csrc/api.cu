@@ -6,6 +6,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <unordered_map>
 
@@ -50,9 +51,14 @@ struct b200_linear_ctx {
     float* ws = nullptr;  // split-K workspace
     size_t ws_bytes = 0;
     int* status_dev = nullptr;
+    int* sk_counters = nullptr;     // arrival counters of split tiles (zero between launches)
+    int sk_counters_len = 0;
+    long long* prof_dev = nullptr;  // role cycle counters (profiling builds only; else unused)
+    int dbg = 0;                    // timing-experiment switches (profiling builds only)
     long long launches = 0;
     int last_cuda = 0;
     int force_bn = -1, force_pair = 0, force_splits = 0;
+    int use_pdl = 1;
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
 };
@@ -110,27 +116,72 @@ inline int ceil_div_i(long long a, long long b) { return static_cast<int>((a + b
 }  // namespace
 
 // ------------------------------------------------------------------- plan
-// Cost model in SM cycles.  One tcgen05.mma of 128 x BN x 16 takes BN/2 cycles at the
-// tensor-core rate; a stage of BK = 64 is four of them, and it also has to stream
-// (128 + BN) * 128 bytes out of shared memory at 128 B/cycle.
-static long long plan_cost(int Mo, int No, int Kc, int bn, int splits, int sms, int* tiles_out) {
-    const int m_tiles = ceil_div_i(Mo, BM), n_tiles = ceil_div_i(No, bn);
-    const int kb_total = ceil_div_i(Kc, BK);
-    const int kbps = ceil_div_i(kb_total, splits);
-    const int real_splits = ceil_div_i(kb_total, kbps);
-    const long long tiles = 1LL * m_tiles * n_tiles * real_splits;
-    const long long rounds = (tiles + sms - 1) / sms;
-    const long long mma = 2LL * bn > 128 + bn ? 2LL * bn : 128 + bn;
-    const long long mainloop = kbps * mma + 600;      // + pipeline fill per tile
-    const long long epilogue = 14LL * bn + 400;       // TMEM drain + stores per tile
-    long long cost = rounds * (mainloop > epilogue ? mainloop : epilogue) + epilogue + 3000;
-    if (real_splits > 1) {
-        const double bytes = 2.0 * real_splits * Mo * (double)No * 4.0;  // partials written, then read
-        cost += static_cast<long long>(bytes / 1800.0) + 5000;           // second kernel
+namespace {
+
+struct Decomp {
+    int m_tiles, n_tiles, kb_total, tiles;
+    int dp_tiles, sk_splits, kb_per_sk, sk_items;
+};
+
+// How the output tiles of one product are spread over `slots` CTAs (or CTA pairs).
+//   force_splits >= 2: every tile is cut into that many ranges of the contraction;
+//   force_splits == 1: no tile is cut;
+//   force_splits == 0: the ragged last wave is cut so that it fills the slots, when that saves
+//                      enough main-loop time to pay for the fp32 round trip of the partials.
+Decomp decompose(int Mo, int No, int Kc, int bn, int ctas, int slots, int force_splits) {
+    Decomp d;
+    d.m_tiles = ceil_div_i(Mo, BM * ctas);
+    d.n_tiles = ceil_div_i(No, bn);
+    d.kb_total = ceil_div_i(Kc, BK);
+    d.tiles = d.m_tiles * d.n_tiles;
+    d.dp_tiles = d.tiles;
+    d.sk_splits = 1;
+    d.kb_per_sk = d.kb_total;
+    d.sk_items = 0;
+    int splits = 1, sk_tiles = 0;
+    if (force_splits >= 2) {
+        splits = force_splits < d.kb_total ? force_splits : d.kb_total;
+        sk_tiles = d.tiles;
+    } else if (force_splits == 0) {
+        const int rem = d.tiles % slots;
+        if (rem != 0) {
+            splits = slots / rem;
+            const int by_work = d.kb_total / 4;  // at least 4 blocks per range
+            if (splits > by_work) splits = by_work;
+            sk_tiles = rem;
+        }
     }
-    if (tiles_out) *tiles_out = static_cast<int>(tiles);
-    return cost;
+    if (splits >= 2) {
+        const int per = ceil_div_i(d.kb_total, splits);
+        splits = ceil_div_i(d.kb_total, per);
+        // worth it only if the cut saves at least ~6 blocks of main loop (or was asked for)
+        if (splits >= 2 && (force_splits >= 2 || d.kb_total - per >= 6)) {
+            d.dp_tiles = d.tiles - sk_tiles;
+            d.sk_splits = splits;
+            d.kb_per_sk = per;
+            d.sk_items = sk_tiles * splits;
+        }
+    }
+    return d;
 }
+
+// Estimated duration in nanoseconds.  Per-block (BK = 64) main-loop costs are measured
+// averages on a B200 under sustained load; they already contain the L2->SM feed limit that
+// makes narrow tiles and single-CTA tiles slower per FLOP than 256-wide CTA-pair tiles.
+double plan_cost_ns(const Decomp& d, int bn, int ctas, int slots) {
+    double per_kb;
+    if (ctas == 2) per_kb = bn == 256 ? 420.0 : 300.0;
+    else per_kb = bn == 256 ? 490.0 : bn == 192 ? 385.0 : bn == 128 ? 300.0 : 230.0;
+    const int dp_rounds = (d.dp_tiles + slots - 1) / slots;
+    const int sk_rounds = (d.sk_items + slots - 1) / slots;
+    double t = (static_cast<double>(dp_rounds) * d.kb_total + static_cast<double>(sk_rounds) * d.kb_per_sk) * per_kb;
+    t += 350.0 * (dp_rounds + sk_rounds);  // pipeline refill at item boundaries
+    t += 500.0 + 6.0 * bn;                 // the last epilogue is exposed
+    if (d.sk_items > 0) t += 1200.0 + 2.0 * d.sk_splits * bn;  // partial round trip + reduction
+    return t;
+}
+
+}  // namespace
 
 extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
                                      b200_linear_plan_t* plan) {
@@ -145,44 +196,80 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
         plan->bn = 0;
         plan->splits = 1;
         plan->tiles = ceil_div_i(Mo, ST_BM) * ceil_div_i(No, ST_BN);
+        plan->dp_tiles = plan->tiles;
         return B200_OK;
     }
-    static const int bns[4] = {256, 192, 128, 64};
-    static const int sps[12] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
-    const int kb_total = ceil_div_i(Kc, BK);
-    long long best = -1;
-    for (int bi = 0; bi < 4; ++bi) {
-        const int bn = bns[bi];
+    static const int cand[6][2] = {{256, 2}, {128, 2}, {256, 1}, {192, 1}, {128, 1}, {64, 1}};
+    double best = -1.0;
+    for (int ci = 0; ci < 6; ++ci) {
+        const int bn = cand[ci][0], ctas = cand[ci][1];
         if (bn > 64 && bn - No >= 64) continue;  // tile much wider than the output
-        for (int si = 0; si < 12; ++si) {
-            const int s = sps[si];
-            if (s > 1 && kb_total / s < 4) break;  // keep >= 4 stages of work per split
-            int tiles = 0;
-            const long long c = plan_cost(Mo, No, Kc, bn, s, sm_count, &tiles);
-            if (best < 0 || c < best) {
-                best = c;
-                plan->bn = bn;
-                const int kbps = ceil_div_i(kb_total, s);
-                plan->splits = ceil_div_i(kb_total, kbps);
-                plan->tiles = tiles;
-            }
+        if (ctas == 2 && sm_count < 2) continue;
+        const int slots = sm_count / ctas;
+        const Decomp d = decompose(Mo, No, Kc, bn, ctas, slots, 0);
+        const double c = plan_cost_ns(d, bn, ctas, slots);
+        if (best < 0 || c < best) {
+            best = c;
+            plan->bn = bn;
+            plan->cta_pair = ctas == 2;
+            plan->splits = d.sk_splits;
+            plan->tiles = d.tiles;
+            plan->dp_tiles = d.dp_tiles;
+            plan->sk_items = d.sk_items;
+            plan->waves_x100 = static_cast<int>(100LL * (d.dp_tiles + d.sk_items) / slots);
         }
     }
-    plan->cta_pair = 0;
     plan->m_fastest = Mo <= No ? 1 : 0;
-    plan->waves_x100 = static_cast<int>(100LL * plan->tiles / sm_count);
     return B200_OK;
 }
 
 // ---------------------------------------------------------------- launch
 namespace {
 
-template <int BN, bool P_MN, bool Q_MN, int EPI, int CTAS>
-int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& gp,
-               int grid) {
+// MN-major operand [Kc][rows] (rows a multiple of 64) seen as {64 elements, Kc, rows/64 panels}
+// so that one copy brings every 64-wide panel of a stage into its own 128B-swizzled block.
+int get_panel_map(b200_linear_ctx* ctx, const void* ptr, uint64_t rows, uint64_t kc, uint32_t panels,
+                  CUtensorMap* out) {
+    TmKey key{ptr, rows, kc, 0x30000u + panels, BK};
+    auto it = ctx->tm_cache.find(key);
+    if (it != ctx->tm_cache.end()) {
+        *out = it->second;
+        return B200_OK;
+    }
+    cuuint64_t dims[3] = {64, kc, rows / 64};
+    cuuint64_t strides[2] = {rows * 2, 128};
+    cuuint32_t box[3] = {64, BK, panels};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box,
+                             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        ctx->last_cuda = 100000 + static_cast<int>(r);
+        return B200_E_CUDA;
+    }
+    if (ctx->tm_cache.size() > 8192) ctx->tm_cache.clear();
+    ctx->tm_cache.emplace(key, *out);
+    return B200_OK;
+}
+
+int ensure_counters(b200_linear_ctx* ctx, int n) {
+    if (n <= ctx->sk_counters_len) return B200_OK;
+    if (ctx->sk_counters) CU_TRY(ctx, cudaFree(ctx->sk_counters));
+    ctx->sk_counters = nullptr;
+    ctx->sk_counters_len = 0;
+    const int want = n + 1024;
+    CU_TRY(ctx, cudaMalloc(&ctx->sk_counters, want * sizeof(int)));
+    CU_TRY(ctx, cudaMemset(ctx->sk_counters, 0, want * sizeof(int)));
+    ctx->sk_counters_len = want;
+    return B200_OK;
+}
+
+template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
+int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
+               const GemmParams& gp, int grid) {
     using Cfg = TileCfg<BN, CTAS>;
     static bool configured = false;
-    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, EPI, CTAS>;
+    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, BETA1, CTAS>;
     if (!configured) {
         CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured = true;
@@ -192,45 +279,46 @@ int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& 
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CTAS;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // The kernel's set-up may overlap the tail of the previous kernel in the stream; it waits
+    // (griddepcontrol.wait) before it touches global memory.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, gp));
+    cfg.numAttrs = 2;
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, gp));
     ctx->launches++;
     return B200_OK;
 }
 
-template <bool P_MN, bool Q_MN, int EPI>
+template <bool P_MN, bool Q_MN, bool BETA1>
 int launch_bn(b200_linear_ctx* ctx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-              const GemmParams& gp, int grid) {
+              const CUtensorMap& tmD, const GemmParams& gp, int grid) {
     if (ctas == 2) {
         switch (bn) {
-            case 256: return launch_one<256, P_MN, Q_MN, EPI, 2>(ctx, tmP, tmQ, gp, grid);
-            case 128: return launch_one<128, P_MN, Q_MN, EPI, 2>(ctx, tmP, tmQ, gp, grid);
+            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, gp, grid);
+            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, gp, grid);
             default: return B200_E_BADARG;
         }
     }
     switch (bn) {
-        case 256: return launch_one<256, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
-        case 192: return launch_one<192, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
-        case 128: return launch_one<128, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
-        case 64: return launch_one<64, P_MN, Q_MN, EPI, 1>(ctx, tmP, tmQ, gp, grid);
+        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
+        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
+        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
+        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
         default: return B200_E_BADARG;
     }
 }
 
 template <bool P_MN, bool Q_MN>
-int launch_epi(b200_linear_ctx* ctx, int bn, int ctas, int epi, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-               const GemmParams& gp, int grid) {
-    switch (epi) {
-        case EPI_BF16: return launch_bn<P_MN, Q_MN, EPI_BF16>(ctx, bn, ctas, tmP, tmQ, gp, grid);
-        case EPI_BF16_BETA1: return launch_bn<P_MN, Q_MN, EPI_BF16_BETA1>(ctx, bn, ctas, tmP, tmQ, gp, grid);
-        default: return launch_bn<P_MN, Q_MN, EPI_F32_PARTIAL>(ctx, bn, ctas, tmP, tmQ, gp, grid);
-    }
+int launch_beta(b200_linear_ctx* ctx, int bn, int ctas, int beta1, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+                const CUtensorMap& tmD, const GemmParams& gp, int grid) {
+    return beta1 ? launch_bn<P_MN, Q_MN, true>(ctx, bn, ctas, tmP, tmQ, tmD, gp, grid)
+                 : launch_bn<P_MN, Q_MN, false>(ctx, bn, ctas, tmP, tmQ, tmD, gp, grid);
 }
 
 template <typename T>
@@ -257,66 +345,64 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
     else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
 
-    int bn = plan.bn, splits = plan.splits, ctas = plan.cta_pair ? 2 : 1;
+    int bn = plan.bn, ctas = plan.cta_pair ? 2 : 1, force_splits = 0;
     if (ctx->force_bn > 0) {
         bn = ctx->force_bn;
-        splits = ctx->force_splits > 0 ? ctx->force_splits : 1;
         ctas = ctx->force_pair ? 2 : 1;
+        force_splits = ctx->force_splits;
     }
+    if (ctx->sm_count < ctas) return B200_E_NODEVICE;
+    const int max_slots = ctx->sm_count / ctas;  // CTAs (or CTA pairs) resident at once
+    const Decomp d = decompose(Mo, No, Kc, bn, ctas, max_slots, force_splits);
+    const long long items = static_cast<long long>(d.dp_tiles) + d.sk_items;
+    if (items > 0x7FFFFFFFLL || static_cast<long long>(d.tiles) * (d.sk_splits > 1 ? d.sk_splits : 1) > 0x7FFFFFFFLL)
+        return B200_E_TOOBIG;
+    const int slots = items < max_slots ? static_cast<int>(items) : max_slots;
+
     GemmParams gp;
     gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
-    gp.m_tiles = ceil_div_i(Mo, BM * ctas);
-    gp.n_tiles = ceil_div_i(No, bn);
-    gp.kb_total = ceil_div_i(Kc, BK);
-    if (splits > gp.kb_total) splits = gp.kb_total;
-    gp.kb_per_split = ceil_div_i(gp.kb_total, splits);
-    gp.splits = ceil_div_i(gp.kb_total, gp.kb_per_split);
+    gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
     gp.m_fastest = plan.m_fastest;
+    gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
+    gp.out = out;
     gp.status = ctx->status_dev;
-    const long long total_tiles = 1LL * gp.m_tiles * gp.n_tiles * gp.splits;
-    if (total_tiles > 0x7FFFFFFFLL) return B200_E_TOOBIG;
-    const int slots = ctx->sm_count / ctas;  // CTAs (or CTA pairs) resident at once
-    const int grid = (total_tiles < slots ? static_cast<int>(total_tiles) : slots) * ctas;
+    gp.prof = ctx->prof_dev;
+    gp.dbg = ctx->dbg;
+    gp.ws = nullptr;
+    gp.sk_counters = nullptr;
+    if (d.sk_items > 0) {
+        rc = ensure_workspace(ctx, static_cast<size_t>(d.sk_items) * ctas * BM * bn * sizeof(float));
+        if (rc) return rc;
+        rc = ensure_counters(ctx, (d.tiles - d.dp_tiles) * ctas);
+        if (rc) return rc;
+        gp.ws = ctx->ws;
+        gp.sk_counters = ctx->sk_counters;
+    }
 
     // Operand P has Mo rows, operand Q has No rows; x,y map onto them per product.
+    // K-major: [rows][Kc], box {BK, rows-per-CTA}.  MN-major: [Kc][rows], one 3-D copy of all the
+    // CTA's 64-wide panels when rows % 64 == 0, else one 2-D copy {64, BK} per panel.
     const void* P = x;
     const void* Q = y;
-    CUtensorMap tmP, tmQ;
-    // K-major: [rows][Kc], box {BK, rows-per-tile}.  MN-major: [Kc][rows], box {64, BK}.
-    if (p_mn) rc = get_tensor_map(ctx, P, Mo, Kc, 64, BK, &tmP);
-    else      rc = get_tensor_map(ctx, P, Kc, Mo, BK, BM, &tmP);
+    CUtensorMap tmP, tmQ, tmD;
+    gp.p_3d = p_mn && (Mo % 64) == 0;
+    gp.q_3d = q_mn && (No % 64) == 0;
+    if (gp.p_3d) rc = get_panel_map(ctx, P, Mo, Kc, BM / 64, &tmP);
+    else if (p_mn) rc = get_tensor_map(ctx, P, Mo, Kc, 64, BK, &tmP);
+    else rc = get_tensor_map(ctx, P, Kc, Mo, BK, BM, &tmP);
     if (rc) return rc;
-    if (q_mn) rc = get_tensor_map(ctx, Q, No, Kc, 64, BK, &tmQ);
-    else      rc = get_tensor_map(ctx, Q, Kc, No, BK, bn / ctas, &tmQ);
+    if (gp.q_3d) rc = get_panel_map(ctx, Q, No, Kc, bn / ctas / 64, &tmQ);
+    else if (q_mn) rc = get_tensor_map(ctx, Q, No, Kc, 64, BK, &tmQ);
+    else rc = get_tensor_map(ctx, Q, Kc, No, BK, bn / ctas, &tmQ);
+    if (rc) return rc;
+    // Output map for the epilogue's TMA stores: [Mo][No] bf16, box = 64 columns x 32 rows.
+    rc = get_tensor_map(ctx, out, No, Mo, 64, 32, &tmD);
     if (rc) return rc;
 
-    int epi = beta1 ? EPI_BF16_BETA1 : EPI_BF16;
-    if (gp.splits > 1) {
-        rc = ensure_workspace(ctx, static_cast<size_t>(gp.splits) * Mo * No * sizeof(float));
-        if (rc) return rc;
-        epi = EPI_F32_PARTIAL;
-        gp.out = ctx->ws;
-    } else {
-        gp.out = out;
-    }
-    if (p_mn) rc = launch_epi<true, true>(ctx, bn, ctas, epi, tmP, tmQ, gp, grid);
-    else if (q_mn) rc = launch_epi<false, true>(ctx, bn, ctas, epi, tmP, tmQ, gp, grid);
-    else rc = launch_epi<false, false>(ctx, bn, ctas, epi, tmP, tmQ, gp, grid);
-    if (rc) return rc;
-    if (gp.splits > 1) {
-        const long long n = 1LL * Mo * No;
-        long long blocks = (n / 8 + 255) / 256;
-        if (blocks > 4LL * ctx->sm_count) blocks = 4LL * ctx->sm_count;
-        if (beta1)
-            splitk_reduce_bf16<true><<<static_cast<int>(blocks), 256, 0, ctx->stream>>>(
-                static_cast<__nv_bfloat16*>(out), ctx->ws, n, gp.splits);
-        else
-            splitk_reduce_bf16<false><<<static_cast<int>(blocks), 256, 0, ctx->stream>>>(
-                static_cast<__nv_bfloat16*>(out), ctx->ws, n, gp.splits);
-        CU_TRY(ctx, cudaGetLastError());
-        ctx->launches++;
-    }
-    return B200_OK;
+    const int grid = slots * ctas;
+    if (p_mn) return launch_beta<true, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, gp, grid);
+    if (q_mn) return launch_beta<false, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, gp, grid);
+    return launch_beta<false, false>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, gp, grid);
 }
 
 template <typename T, bool P_MN, bool Q_MN>
@@ -405,6 +491,7 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
         return B200_E_CUDA;
     }
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (const char* e = getenv("B200_LINEAR_PDL")) ctx->use_pdl = atoi(e) != 0;
     if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
         delete ctx;
@@ -425,6 +512,8 @@ extern "C" int b200_linear_destroy(b200_linear_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaFree(ctx->ws);
     cudaFree(ctx->status_dev);
+    if (ctx->sk_counters) cudaFree(ctx->sk_counters);
+    if (ctx->prof_dev) cudaFree(ctx->prof_dev);
     delete ctx;
     return B200_OK;
 }
@@ -443,6 +532,7 @@ extern "C" int b200_linear_sync(b200_linear_ctx* ctx, int* device_code) {
     if (device_code) *device_code = code;
     if (code != 0) {
         CU_TRY(ctx, cudaMemset(ctx->status_dev, 0, sizeof(int)));
+        if (ctx->sk_counters) CU_TRY(ctx, cudaMemset(ctx->sk_counters, 0, ctx->sk_counters_len * sizeof(int)));
         return B200_E_DEVICE_WAIT;
     }
     return B200_OK;
@@ -462,6 +552,25 @@ extern "C" const char* b200_linear_strerror(int code) {
         default: return "unknown error";
     }
 }
+
+#ifdef B200_PROFILE
+extern "C" int b200_linear_debug_flags(b200_linear_ctx* ctx, int flags) {
+    if (!ctx) return B200_E_BADARG;
+    ctx->dbg = flags;
+    return B200_OK;
+}
+// Profiling builds only: copies the 16 role cycle counters of CTA 0 of the last tensor-core kernel.
+extern "C" int b200_linear_debug_prof(b200_linear_ctx* ctx, long long* out16) {
+    if (!ctx || !out16) return B200_E_BADARG;
+    if (!ctx->prof_dev) {
+        CU_TRY(ctx, cudaMalloc(&ctx->prof_dev, 16 * sizeof(long long)));
+        CU_TRY(ctx, cudaMemset(ctx->prof_dev, 0, 16 * sizeof(long long)));
+    }
+    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CU_TRY(ctx, cudaMemcpy(out16, ctx->prof_dev, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
+    return B200_OK;
+}
+#endif
 
 extern "C" int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits) {
     if (!ctx) return B200_E_BADARG;

@@ -1,7 +1,7 @@
 // Persistent, warp-specialised bf16 GEMM for sm_100a:
 //   TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma (fp32 accumulators in
 //   TMEM, double-buffered) -> epilogue warps (tcgen05.ld, fused beta=1 add and
-//   bf16 down-cast, or fp32 split-K partials).
+//   bf16 down-cast, TMA store).
 //
 // One kernel template covers the three GEMMs of the reference's linear layer
 // (cuda/matmul.cu:55-104 of the reference) by describing every product as
@@ -17,6 +17,14 @@
 //           loads its own 128 rows of P and its own BN/2 rows of Q (no multicast), the
 //           even CTA issues the MMAs for both, each CTA drains its own 128 x BN
 //           accumulator from its own TMEM.
+//
+// Work schedule ("slot" = a CTA, or a CTA pair): the first `dp_tiles` output tiles are
+// computed whole, round-robin over the slots.  The remaining tiles — the ragged last
+// wave, or every tile when the output alone cannot fill the GPU — are each cut into
+// `sk_splits` ranges of the contraction; every range is one work item that leaves an fp32
+// partial tile in the workspace, and the CTA whose partial arrives last adds all of them up
+// in a fixed order (so results do not depend on arrival order), applies beta and writes the
+// tile.  Nobody waits for anybody: only the last arriver does the reduction.
 #pragma once
 #include <cuda_bf16.h>
 #include "ptx.cuh"
@@ -26,25 +34,38 @@ namespace b200 {
 constexpr int BM = 128;        // output rows per CTA = TMEM lanes
 constexpr int BK = 64;         // contraction elements per stage = one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;     // contraction elements per tcgen05.mma (bf16)
-constexpr int GEMM_THREADS = 256;
+constexpr int GEMM_THREADS = 384;
+constexpr int EPI_WARPS = 8;     // warps 4..11
 constexpr int SMEM_BUDGET = 227 * 1024;
-
-enum EpilogueKind : int {
-    EPI_BF16 = 0,        // out_bf16 = rn(acc)
-    EPI_BF16_BETA1 = 1,  // out_bf16 = rn(acc + float(out_bf16))
-    EPI_F32_PARTIAL = 2  // workspace_f32[split] = acc   (split-K; reduced by a second kernel)
-};
+constexpr int EPI_BUF_BYTES = 32 * 128;  // one staging buffer: 32 rows x 64 bf16, 128-byte swizzled
 
 struct GemmParams {
     int Mo, No, Kc;          // output rows, output cols, contraction length
     int m_tiles, n_tiles;    // ceil(Mo/(BM*CTAS)), ceil(No/BN)
-    int splits;              // split-K factor (1 = none)
     int kb_total;            // ceil(Kc/BK)
-    int kb_per_split;        // ceil(kb_total/splits); every split owns >= 1 block
     int m_fastest;           // tile raster: 1 = consecutive tiles walk down the rows
-    void* out;               // bf16 [Mo,No] or fp32 workspace [splits,Mo,No]
+    int dp_tiles;            // tiles [0, dp_tiles) are computed whole
+    int sk_splits;           // tiles [dp_tiles, m_tiles*n_tiles) are cut into this many ranges
+    int kb_per_sk;           // ceil(kb_total/sk_splits); every range owns >= 1 block
+    int sk_items;            // (m_tiles*n_tiles - dp_tiles) * sk_splits
+    int p_3d, q_3d;          // MN-major operand described by a 3-D map: one copy per stage
+    void* out;               // bf16 [Mo,No]
+    float* ws;               // split partials: sk_items * CTAS blocks of BM x BN fp32
+    int* sk_counters;        // one arrival counter per (split tile, CTA of the pair); zero between launches
     int* status;             // device status word (0 = ok)
+    long long* prof;         // cycle counters of CTA 0 (only read by builds with B200_PROFILE)
+    int dbg;                 // timing experiments (only read by builds with B200_PROFILE; results are wrong)
 };
+
+#ifdef B200_PROFILE
+#define PROF_WRITE(idx, val) do { if (p.prof && blockIdx.x == 0) p.prof[idx] = (val); } while (0)
+#define PROF_MARK(idx) PROF_WRITE(idx, clock64() - t_kernel)
+#define DBG(bit) (p.dbg & (bit))
+#else
+#define PROF_WRITE(idx, val)
+#define PROF_MARK(idx)
+#define DBG(bit) false
+#endif
 
 template <int BN, int CTAS>
 struct TileCfg {
@@ -53,32 +74,54 @@ struct TileCfg {
     static constexpr int B_BYTES = B_ROWS * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int CTRL_BYTES = 1024;
-    static constexpr int STAGES_RAW = (SMEM_BUDGET - CTRL_BYTES - 1024) / STAGE_BYTES;
+    static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;  // one staging buffer per epilogue warp
+    static constexpr int STAGES_RAW = (SMEM_BUDGET - CTRL_BYTES - EPI_BYTES - 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;  // +1024: manual alignment
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + EPI_BYTES + 1024;  // +1024: manual alignment
     static constexpr int ACC_STRIDE = BN <= 64 ? 64 : (BN <= 128 ? 128 : 256);   // TMEM columns per accumulator
     static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
-    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
+    static constexpr int PARTIAL_FLOATS = BM * BN;     // one CTA's fp32 partial tile
+    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "tile width");
     static_assert(CTAS == 1 || (CTAS == 2 && B_ROWS % 64 == 0), "pair tiles split Q in 64-row panels");
     static_assert(STAGES >= 3, "pipeline too shallow");
 };
 
-struct TileCoord {
-    int m_blk, n_blk, split;
+// One unit of work of a slot.
+struct WorkItem {
+    int m_blk, n_blk;   // output tile
+    int kb0, kb1;       // contraction blocks [kb0, kb1)
+    int sk_item;        // -1: whole tile; else index of this partial in the workspace
+    int sk_tile;        // index of the split tile (counter index), when sk_item >= 0
 };
-__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int t) {
-    TileCoord c;
-    const int per_split = p.m_tiles * p.n_tiles;
-    c.split = t / per_split;
-    const int r = t - c.split * per_split;
-    if (p.m_fastest) {
-        c.n_blk = r / p.m_tiles;
-        c.m_blk = r - c.n_blk * p.m_tiles;
+
+// The i-th work item of `slot` (split items first, then whole tiles); false when the slot is done.
+__device__ __forceinline__ bool get_work(const GemmParams& p, int slot, int nslots, int i, WorkItem& w) {
+    const int my_sk = p.sk_items > slot ? (p.sk_items - slot + nslots - 1) / nslots : 0;
+    int tile;
+    if (i < my_sk) {
+        const int u = slot + i * nslots;
+        w.sk_item = u;
+        w.sk_tile = u / p.sk_splits;
+        const int split = u - w.sk_tile * p.sk_splits;
+        tile = p.dp_tiles + w.sk_tile;
+        w.kb0 = split * p.kb_per_sk;
+        w.kb1 = min(w.kb0 + p.kb_per_sk, p.kb_total);
     } else {
-        c.m_blk = r / p.n_tiles;
-        c.n_blk = r - c.m_blk * p.n_tiles;
+        tile = slot + (i - my_sk) * nslots;
+        if (tile >= p.dp_tiles) return false;
+        w.sk_item = -1;
+        w.sk_tile = 0;
+        w.kb0 = 0;
+        w.kb1 = p.kb_total;
     }
-    return c;
+    if (p.m_fastest) {
+        w.n_blk = tile / p.m_tiles;
+        w.m_blk = tile - w.n_blk * p.m_tiles;
+    } else {
+        w.m_blk = tile / p.n_tiles;
+        w.n_blk = tile - w.m_blk * p.n_tiles;
+    }
+    return true;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -94,58 +137,142 @@ struct alignas(8) GemmCtrl {
     unsigned long long empty[8];       // MMA -> TMA: stage consumed
     unsigned long long tmem_full[2];   // MMA -> epilogue: accumulator finished
     unsigned long long tmem_empty[2];  // epilogue -> MMA: accumulator drained (pair: lives in the even CTA)
+    unsigned long long sk_written;     // the 4 epilogue warps have stored their part of a partial tile
+    unsigned long long sk_decided;     // "am I the last arriver" has been published in sk_last
     uint32_t tmem_base;
     int abort_flag;
+    int sk_last;
 };
 
-// Drain one 128 x BN fp32 accumulator (this warp's 32 lanes) to global memory.
-template <int BN, int EPI>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t taddr, int row, int n0,
-                                               int split) {
-    const bool row_ok = row < p.Mo;
+// Float offset of (epilogue warp q, 32-column group c32, float4 index j4, lane) inside one
+// CTA's partial tile.  Chosen so that every warp-wide float4 access is one contiguous 512 bytes.
+template <int BN>
+__device__ __forceinline__ int partial_offset(int q, int c32, int j4, int lane) {
+    return (((q * (BN / 32) + c32) * 8 + j4) * 32 + lane) * 4;
+}
+
+// Store this warp's share of the accumulator as an fp32 partial tile.  Epilogue warp (q, hsel)
+// owns TMEM lanes 32q..32q+31 and every second 32-column group, starting with group hsel.
+template <int BN>
+__device__ __forceinline__ void epilogue_store_partial(float* block, uint32_t taddr, int q, int hsel, int lane) {
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = hsel; c < BN / 32; c += 2) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if constexpr (EPI == EPI_F32_PARTIAL) {
-            float* dst = reinterpret_cast<float*>(p.out) + (static_cast<size_t>(split) * p.Mo + row) * p.No + col0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(block + partial_offset<BN>(q, c, j, lane)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    }
+}
+
+// acc[0..31] += the 32 values of (q, c32, lane) in one partial tile.
+template <int BN>
+__device__ __forceinline__ void load_partial32(float4 (&v)[8], const float* blk, int q, int c32, int lane) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        v[j] = __ldcg(reinterpret_cast<const float4*>(blk + partial_offset<BN>(q, c32, j, lane)));
+}
+__device__ __forceinline__ void add_partial32(uint32_t* acc, const float4 (&v)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        acc[4 * j + 0] = __float_as_uint(__uint_as_float(acc[4 * j + 0]) + v[j].x);
+        acc[4 * j + 1] = __float_as_uint(__uint_as_float(acc[4 * j + 1]) + v[j].y);
+        acc[4 * j + 2] = __float_as_uint(__uint_as_float(acc[4 * j + 2]) + v[j].z);
+        acc[4 * j + 3] = __float_as_uint(__uint_as_float(acc[4 * j + 3]) + v[j].w);
+    }
+}
+
+// Write this warp's share of the output tile as bf16.  Epilogue warp (q, hsel) owns rows
+// row0..row0+31 and every second 64-column chunk, starting with chunk hsel: chunk ->
+// (beta=1: add the old values) -> bf16 -> the warp's 128B-swizzled staging buffer -> one TMA
+// store of a 32 x 64 box (TMA clips rows/columns beyond the matrix, so tails need no predicates).
+// The fp32 values come from TMEM (FROM_WS = false) or from the sum of `nsplits` partial tiles
+// in the workspace, added in the order 0..nsplits-1 (FROM_WS = true).
+template <int BN, bool BETA1, bool FROM_WS>
+__device__ __forceinline__ void epilogue_store_bf16(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
+                                                    uint32_t taddr, const float* partials, size_t partial_stride,
+                                                    int nsplits, int q, int hsel, int row0, int lane, int n0) {
+    const int row = row0 + lane;
+#pragma unroll 1
+    for (int c = hsel; c < BN / 64; c += 2) {
+        const int col0 = n0 + c * 64;
+        if (col0 >= p.No) break;  // whole chunk beyond the matrix (warp-uniform)
+        uint32_t r[64];
+        if constexpr (!FROM_WS) {
+            tmem_ld_32x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tmem_ld_32x32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        }
+        uint4 old[8];
+        if constexpr (BETA1) {
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.No + col0;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-                if (row_ok && col0 + 4 * j < p.No)
-                    *reinterpret_cast<uint4*>(dst + 4 * j) =
-                        make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.No + col0;
+                old[j] = (row < p.Mo && col0 + 8 * j < p.No) ? *reinterpret_cast<const uint4*>(src + 8 * j)
+                                                           : make_uint4(0, 0, 0, 0);
+        }
+        if constexpr (FROM_WS) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (row_ok && col0 + 8 * j < p.No) {
-                    float v[8];
+            for (int e = 0; e < 64; ++e) r[e] = 0u;  // +0.0f
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * j + e]);
-                    if constexpr (EPI == EPI_BF16_BETA1) {
-                        const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
-                        v[0] += bf16_lo(o.x); v[1] += bf16_hi(o.x);
-                        v[2] += bf16_lo(o.y); v[3] += bf16_hi(o.y);
-                        v[4] += bf16_lo(o.z); v[5] += bf16_hi(o.z);
-                        v[6] += bf16_lo(o.w); v[7] += bf16_hi(o.w);
-                    }
-                    *reinterpret_cast<uint4*>(dst + 8 * j) =
-                        make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                   pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            for (int half = 0; half < 2; ++half) {
+                const int c32 = 2 * c + half;
+                int sp = 0;
+                for (; sp + 1 < nsplits; sp += 2) {  // two partial tiles in flight, added in order
+                    float4 va[8], vb[8];
+                    load_partial32<BN>(va, partials + sp * partial_stride, q, c32, lane);
+                    load_partial32<BN>(vb, partials + (sp + 1) * partial_stride, q, c32, lane);
+                    add_partial32(&r[32 * half], va);
+                    add_partial32(&r[32 * half], vb);
+                }
+                if (sp < nsplits) {
+                    float4 va[8];
+                    load_partial32<BN>(va, partials + sp * partial_stride, q, c32, lane);
+                    add_partial32(&r[32 * half], va);
                 }
             }
+        } else {
+            tmem_ld_wait();
+        }
+        // the warp's previous store must have finished reading the staging buffer
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * j + e]);
+            if constexpr (BETA1) {
+                // Same two roundings as the reference's cuBLAS path: bf16_rn(bf16_rn(acc) + old).
+                const uint32_t a0 = pack_bf16x2(v[0], v[1]), a1 = pack_bf16x2(v[2], v[3]);
+                const uint32_t a2 = pack_bf16x2(v[4], v[5]), a3 = pack_bf16x2(v[6], v[7]);
+                v[0] = bf16_lo(a0) + bf16_lo(old[j].x); v[1] = bf16_hi(a0) + bf16_hi(old[j].x);
+                v[2] = bf16_lo(a1) + bf16_lo(old[j].y); v[3] = bf16_hi(a1) + bf16_hi(old[j].y);
+                v[4] = bf16_lo(a2) + bf16_lo(old[j].z); v[5] = bf16_hi(a2) + bf16_hi(old[j].z);
+                v[6] = bf16_lo(a3) + bf16_lo(old[j].w); v[7] = bf16_hi(a3) + bf16_hi(old[j].w);
+            }
+            // 128-byte swizzle: 16-byte chunk j of row `lane` lives at chunk (j ^ (lane & 7))
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                           pack_bf16x2(v[6], v[7]));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < p.Mo && !DBG(2)) {
+            tma_store_2d(tmD, smem_u32(buf), col0, row0);
+            tma_store_commit();
         }
     }
 }
 
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (even CTA only in a pair), 2 = TMEM allocator,
-// 3 = idle, 4..7 = epilogue (warp w owns TMEM lanes 32*(w-4) .. +31).
-template <int BN, bool P_MN, bool Q_MN, int EPI, int CTAS>
+// 3 = idle, 4..11 = epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 only, so warps w and
+// w+4 share a lane quarter and split its columns between them.
+template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
     using Cfg = TileCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr bool PAIR = CTAS == 2;
@@ -154,13 +281,18 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                                                ~static_cast<uintptr_t>(1023));
     GemmCtrl* ctrl = reinterpret_cast<GemmCtrl*>(smem);
     uint8_t* tiles = smem + Cfg::CTRL_BYTES;  // stage s: [P tile | Q tile]
+    uint8_t* epi_bufs = tiles + STAGES * Cfg::STAGE_BYTES;  // per epilogue warp: 2 staging buffers
     volatile int* abort_flag = &ctrl->abort_flag;
 
+#ifdef B200_PROFILE
+    const long long t_kernel = clock64();
+    unsigned long long g_kernel;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_kernel));
+#endif
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // position in the CTA pair
-    const int total_tiles = p.m_tiles * p.n_tiles * p.splits;
-    const int first_tile = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
+    const int slot = blockIdx.x / CTAS, nslots = gridDim.x / CTAS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -169,14 +301,18 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
-            mbar_init(smem_u32(&ctrl->tmem_empty[a]), 4 * CTAS);
+            mbar_init(smem_u32(&ctrl->tmem_empty[a]), EPI_WARPS * CTAS);
         }
+        mbar_init(smem_u32(&ctrl->sk_written), EPI_WARPS);
+        mbar_init(smem_u32(&ctrl->sk_decided), 1);
         ctrl->abort_flag = 0;
+        ctrl->sk_last = 0;
         fence_mbar_init();
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tmP);
         tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmD);
     }
     if (warp == 2) {
         tmem_alloc<CTAS>(smem_u32(&ctrl->tmem_base), Cfg::TMEM_COLS);
@@ -190,6 +326,12 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     }
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
+    // Programmatic dependent launch: everything above overlapped the tail of the previous kernel
+    // in the stream; its results (and its reads of our output buffers) are complete only after
+    // this wait.  The next kernel may start its own set-up as soon as our CTAs make room.
+    griddep_wait();
+    griddep_launch_dependents();
+    if (threadIdx.x == 0) PROF_MARK(0);
 
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
@@ -197,13 +339,11 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             uint32_t stage = 0, phase = 0;
             uint32_t issued = 0;  // number of stage fills issued so far
             bool ok = true;
-            for (int t = first_tile; t < total_tiles && ok; t += tile_step) {
-                const TileCoord tc = decode_tile(p, t);
-                const int kb0 = tc.split * p.kb_per_split;
-                const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
-                const int m0 = (tc.m_blk * CTAS + static_cast<int>(rank)) * BM;
-                const int n0 = tc.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
-                for (int kb = kb0; kb < kb1; ++kb) {
+            WorkItem w;
+            for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+                const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
+                const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
                                    DEV_TIMEOUT_EMPTY)) {
                         ok = false;
@@ -213,24 +353,40 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, 0) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
                     const uint32_t sQ = sP + Cfg::A_BYTES;
-                    if (rank == 0) mbar_arrive_expect_tx(local_bar, CTAS * Cfg::STAGE_BYTES);
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(local_bar, DBG(8) ? CTAS * Cfg::A_BYTES : CTAS * Cfg::STAGE_BYTES);
                     const int c0 = kb * BK;
-                    auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
+                    auto load2 = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
                         if constexpr (PAIR) tma_load_2d_pair(dst, tm, bar, x, y);
                         else tma_load_2d(dst, tm, bar, x, y);
                     };
-                    if constexpr (P_MN) {  // global [Kc][Mo]: box = 64 output rows x BK contraction rows
+                    auto load3 = [&](uint32_t dst, const CUtensorMap* tm, int y, int z) {
+                        if constexpr (PAIR) tma_load_3d_pair(dst, tm, bar, 0, y, z);
+                        else tma_load_3d(dst, tm, bar, 0, y, z);
+                    };
+                    if constexpr (P_MN) {  // global [Kc][Mo]: 64-wide column panels of BK contraction rows
+                        if (p.p_3d) {
+                            load3(sP, &tmP, c0, m0 >> 6);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < BM / 64; ++j) load(sP + j * (64 * BK * 2), &tmP, m0 + 64 * j, c0);
+                            for (int j = 0; j < BM / 64; ++j) load2(sP + j * (64 * BK * 2), &tmP, m0 + 64 * j, c0);
+                        }
                     } else {               // global [Mo][Kc]: box = BK contraction x BM rows
-                        load(sP, &tmP, c0, m0);
+                        load2(sP, &tmP, c0, m0);
                     }
-                    if constexpr (Q_MN) {
+                    if (DBG(8)) {
+                    } else if constexpr (Q_MN) {
+                        if (p.q_3d) {
+                            load3(sQ, &tmQ, c0, n0 >> 6);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < Cfg::B_ROWS / 64; ++j) load(sQ + j * (64 * BK * 2), &tmQ, n0 + 64 * j, c0);
+                            for (int j = 0; j < Cfg::B_ROWS / 64; ++j)
+                                load2(sQ + j * (64 * BK * 2), &tmQ, n0 + 64 * j, c0);
+                        }
                     } else {
-                        load(sQ, &tmQ, c0, n0);
+                        load2(sQ, &tmQ, c0, n0);
                     }
+                    if (issued == 0) PROF_MARK(1);
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -261,13 +417,11 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             //                8-row groups 1024 B apart (SBO); +16 rows = 2048 B per UMMA_K step.
             constexpr uint32_t P_LBO = P_MN ? 64 * BK * 2 : 16, P_STEP = P_MN ? UMMA_K * 128 : UMMA_K * 2;
             constexpr uint32_t Q_LBO = Q_MN ? 64 * BK * 2 : 16, Q_STEP = Q_MN ? UMMA_K * 128 : UMMA_K * 2;
-            uint32_t stage = 0, phase = 0, it = 0;
+            uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
-                const TileCoord tc = decode_tile(p, t);
-                const int kb0 = tc.split * p.kb_per_split;
-                const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
-                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            WorkItem w;
+            for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+                const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
                 if (!mbar_wait<PAIR>(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
                                      DEV_TIMEOUT_TMEM_E)) {
                     ok = false;
@@ -275,20 +429,22 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status,
                                    DEV_TIMEOUT_FULL)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
+                    if (i == 0 && kb == w.kb0) PROF_MARK(2);
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
                     const uint32_t sQ = sP + Cfg::A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t dP = umma_smem_desc(sP + k * P_STEP, P_LBO, 1024);
                         const uint64_t dQ = umma_smem_desc(sQ + k * Q_STEP, Q_LBO, 1024);
-                        umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        if (DBG(4) && k > 0) continue;
+                        umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
                     }
                     // frees the stage (in both CTAs of a pair) when the MMAs retire
                     if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
@@ -300,30 +456,81 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     else umma_commit(smem_u32(&ctrl->tmem_full[acc]));
                 }
             }
+            PROF_MARK(3);
         }
     } else if (warp >= 4) {
         // ---------------------------------------------------------- epilogue
-        const int q = warp - 4;  // TMEM lane quarter
-        uint32_t it = 0;
+        const int q = warp & 3;            // TMEM lane quarter
+        const int hsel = (warp - 4) >> 2;  // which half of the column chunks
+        uint32_t sk_phase = 0;
         bool ok = true;
-        for (int t = first_tile; t < total_tiles && ok; t += tile_step, ++it) {
-            const TileCoord tc = decode_tile(p, t);
-            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status,
-                           DEV_TIMEOUT_TMEM_F);
-            ok = __all_sync(0xffffffffu, ok);
+        WorkItem w;
+        for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+            const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
+            if (lane == 0)
+                ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
-            const int row = (tc.m_blk * CTAS + static_cast<int>(rank)) * BM + q * 32 + lane;
+            if (warp == 4 && lane == 0) PROF_MARK(4);  // last item's accumulator ready
+            const int row0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM + q * 32;
             const uint32_t taddr = tmem_base + acc * Cfg::ACC_STRIDE + (static_cast<uint32_t>(q * 32) << 16);
-            epilogue_store<BN, EPI>(p, taddr, row, tc.n_blk * BN, tc.split);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (PAIR) mbar_arrive_cluster(smem_u32(&ctrl->tmem_empty[acc]), 0);
-                else mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+            uint8_t* my_buf = epi_bufs + (warp - 4) * EPI_BUF_BYTES;
+            auto release_acc = [&]() {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (PAIR) mbar_arrive_cluster(smem_u32(&ctrl->tmem_empty[acc]), 0);
+                    else mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+                }
+            };
+            if (w.sk_item < 0) {
+                if (!DBG(1))
+                    epilogue_store_bf16<BN, BETA1, false>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
+                                                          w.n_blk * BN);
+                release_acc();
+            } else {
+                // One range of a split tile: park the partial, count the arrival, and if every
+                // other range of this tile has already arrived, reduce them all and write the tile.
+                float* block = p.ws + (static_cast<size_t>(w.sk_item) * CTAS + rank) * Cfg::PARTIAL_FLOATS;
+                epilogue_store_partial<BN>(block, taddr, q, hsel, lane);
+                release_acc();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->sk_written));
+                if (warp == 4 && lane == 0) {
+                    if (mbar_wait(smem_u32(&ctrl->sk_written), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER)) {
+                        int* counter = p.sk_counters + w.sk_tile * CTAS + rank;
+                        __threadfence();  // the four warps' partial stores, ordered before the count
+                        const int prev = atomicAdd(counter, 1);
+                        const int last = prev == p.sk_splits - 1;
+                        if (last) atomicExch(counter, 0);  // leave the counter ready for the next launch
+                        ctrl->sk_last = last;
+                        __threadfence();
+                    }
+                    mbar_arrive(smem_u32(&ctrl->sk_decided));
+                }
+                if (lane == 0)
+                    ok = mbar_wait(smem_u32(&ctrl->sk_decided), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                sk_phase ^= 1;
+                if (ctrl->sk_last) {
+                    __threadfence();
+                    const float* first = p.ws + (static_cast<size_t>(w.sk_tile) * p.sk_splits * CTAS + rank) *
+                                                    Cfg::PARTIAL_FLOATS;
+                    epilogue_store_bf16<BN, BETA1, true>(p, &tmD, my_buf, 0, first,
+                                                         static_cast<size_t>(CTAS) * Cfg::PARTIAL_FLOATS, p.sk_splits, q,
+                                                         hsel, row0, lane, w.n_blk * BN);
+                }
+                // every warp must have read sk_last before the next split item overwrites it
+                __syncwarp();
             }
         }
+        // every TMA store of this warp must have read its staging buffer and landed before exit
+        if (warp == 4 && lane == 0) PROF_MARK(5);
+        if (lane == 0) tma_store_wait_all<0>();
+        if (warp == 4 && lane == 0) PROF_MARK(6);
     }
 
     // ------------------------------------------------------------- teardown
@@ -333,36 +540,20 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         cluster_arrive_release();
         cluster_wait_acquire();
     }
+    if (threadIdx.x == 0) PROF_MARK(7);
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
     }
-}
-
-// Split-K reduction: out = rn( sum_s ws[s] (+ float(out) when beta1) ), fixed order s = 0..S-1.
-// n = Mo*No, a multiple of 8.
-template <bool BETA1>
-__global__ void splitk_reduce_bf16(__nv_bfloat16* __restrict__ out, const float* __restrict__ ws,
-                                   long long n, int splits) {
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 8;
-    for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8; i < n;
-         i += stride) {
-        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < splits; ++s) {
-            const float4 x = *reinterpret_cast<const float4*>(ws + s * n + i);
-            const float4 y = *reinterpret_cast<const float4*>(ws + s * n + i + 4);
-            a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
-            a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
-        }
-        if constexpr (BETA1) {
-            const uint4 o = *reinterpret_cast<const uint4*>(out + i);
-            a[0] += bf16_lo(o.x); a[1] += bf16_hi(o.x); a[2] += bf16_lo(o.y); a[3] += bf16_hi(o.y);
-            a[4] += bf16_lo(o.z); a[5] += bf16_hi(o.z); a[6] += bf16_lo(o.w); a[7] += bf16_hi(o.w);
-        }
-        *reinterpret_cast<uint4*>(out + i) =
-            make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
-                       pack_bf16x2(a[6], a[7]));
+#ifdef B200_PROFILE
+    if (threadIdx.x == 0) {
+        unsigned long long g_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_end));
+        PROF_WRITE(9, clock64() - t_kernel);
+        PROF_WRITE(14, (long long)(g_end - g_kernel));
+        if (p.prof && blockIdx.x == 0) { p.prof[13] = p.prof[15]; p.prof[15] = (long long)g_kernel; p.prof[12] = (long long)g_end; }
     }
+#endif
 }
 
 }  // namespace b200

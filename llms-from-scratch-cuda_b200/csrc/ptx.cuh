@@ -130,6 +130,23 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
         "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// 3-D tiled loads (used for MN-major operands viewed as {64 elements, rows, 64-wide panels}).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int x,
+                                            int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                                 int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 // shared::cluster address of `addr` (a shared::cta address) in CTA `cta` of the cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t cta) {
     uint32_t r;
@@ -277,6 +294,14 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t fmt, uint32_t m, uint
                                                   uint32_t a_mn, uint32_t b_mn) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) |
            ((m >> 4) << 24);
+}
+
+// ------------------------------------------------ programmatic dependent launch
+__device__ __forceinline__ void griddep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ----------------------------------------------------------------- cluster

@@ -60,6 +60,48 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
     return out
 
 
+KERNEL_SOURCES = ["embedding.cu", "rmsnorm.cu", "rope.cu", "flash_attention.cu", "attention.cu", "swiglu.cu",
+                  "softmax.cu", "crossentropy.cu", "residual.cu", "adamw.cu"]
+
+
+def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False):
+    """The reference's `train` program twice, from its sources where they lie:
+         oracle/_ref/train_ref_<model>    as the reference builds it (cuda/matmul.cu -> cuBLAS)
+         oracle/_ref/train_b200_<model>   the same host and kernel objects, with cuda/matmul.cu left out
+                                          and libb200_linear.so (+ the cuBLAS stand-in) linked instead
+       Returns (ref_path, b200_path) or (None, None) when the checkout or nvcc is absent."""
+    out_dir = os.path.join(HERE, "_ref")
+    tag = model.replace("-", "_")
+    ref_bin = os.path.join(out_dir, "train_ref_" + tag)
+    our_bin = os.path.join(out_dir, "train_b200_" + tag)
+    cuda_dir = os.path.join(reference, "cuda")
+    src_dir = os.path.join(reference, model, "src")
+    if not os.path.isdir(src_dir) or shutil.which("nvcc") is None:
+        return (ref_bin if os.path.exists(ref_bin) else None, our_bin if os.path.exists(our_bin) else None)
+    pkg = os.path.join(os.path.dirname(HERE), "llms-from-scratch-cuda_b200")
+    ours = [os.path.join(pkg, "libb200_linear.so"), os.path.join(pkg, "libb200_cublas_shim.so")]
+    srcs = [os.path.join(cuda_dir, f) for f in KERNEL_SOURCES] + \
+           [os.path.join(src_dir, f) for f in ("main.cpp", "model.cpp", "dataloader.cpp")]
+    if not force and _newer(ref_bin, srcs) and _newer(our_bin, srcs + ours):
+        return ref_bin, our_bin
+    os.makedirs(out_dir, exist_ok=True)
+    obj_dir = os.path.join(out_dir, "obj_" + tag)
+    os.makedirs(obj_dir, exist_ok=True)
+    common = ["nvcc", "-std=c++17", "-O3", "--use_fast_math", "-gencode", "arch=compute_100a,code=sm_100a",
+              "-I", cuda_dir, "-I", src_dir]
+    objs = []
+    for src in srcs + [os.path.join(cuda_dir, "matmul.cu")]:
+        obj = os.path.join(obj_dir, os.path.basename(src) + ".o")
+        subprocess.run(common + ["-x", "cu", "-c", src, "-o", obj], check=True)
+        objs.append(obj)
+    matmul_obj = objs.pop()
+    subprocess.run(["nvcc", "-o", ref_bin] + objs + [matmul_obj, "-lcublas",
+                                                    "-Xlinker", "-rpath=/usr/local/cuda/lib64"], check=True)
+    subprocess.run(["nvcc", "-o", our_bin] + objs + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim",
+                   "-Xlinker", "-rpath=$ORIGIN/../../llms-from-scratch-cuda_b200"], check=True)
+    return ref_bin, our_bin
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=DEFAULT_REFERENCE)
@@ -67,3 +109,4 @@ if __name__ == "__main__":
     a = ap.parse_args()
     print(build_oracle(a.force))
     print(build_reference(a.reference, a.force))
+    print(build_train(a.reference, "llama2-mistral", a.force))

@@ -61,6 +61,18 @@ def round_bf16(a):
     return a
 
 
+def reference_bf16_result(product64, old=None):
+    """What the reference's bf16 path stores for a product whose exact value is `product64`:
+    bf16_rn(product) for beta = 0 (cuda/matmul.cu:61,82 of the reference) and, for the beta = 1
+    weight gradient (cuda/matmul.cu:94), bf16_rn(bf16_rn(product) + old): cuBLAS rounds the
+    product to the output type before it adds the old value (observed bit for bit on a B200,
+    tests/golden/reference_cublas.npz)."""
+    r = round_bf16(np.asarray(product64, dtype=np.float64).astype(np.float32))
+    if old is None:
+        return r
+    return round_bf16((r.astype(np.float64) + np.asarray(old, dtype=np.float64)).astype(np.float32))
+
+
 def gemm_f64(which, x, y, M, N, K, old=None):
     """float64 result of product `which` (+ old when given)."""
     x = np.ascontiguousarray(x, dtype=np.float32)

@@ -17,12 +17,23 @@ def test_plan_invariants(pkg, which):
         p = pkg.plan_bf16(which, which == 2, M, N, K, 148)
         Mo, No, Kc = _dims(which, M, N, K)
         assert p.bn in (64, 128, 192, 256)
+        assert p.cta_pair in (0, 1)
+        if p.cta_pair:
+            assert p.bn in (128, 256)
+        rows = 256 if p.cta_pair else 128
+        assert p.tiles == -(-Mo // rows) * -(-No // p.bn)
         kb = -(-Kc // 64)
         assert 1 <= p.splits <= kb
         per = -(-kb // p.splits)
-        assert (p.splits - 1) * per < kb  # every split owns at least one block
-        tiles = -(-Mo // 128) * -(-No // p.bn) * p.splits
-        assert p.tiles == tiles
+        assert (p.splits - 1) * per < kb  # every range owns at least one block
+        assert 0 <= p.dp_tiles <= p.tiles
+        assert p.sk_items == (p.tiles - p.dp_tiles) * p.splits
+        if p.splits == 1:
+            assert p.dp_tiles == p.tiles and p.sk_items == 0
+        else:
+            slots = 148 // (2 if p.cta_pair else 1)
+            assert p.dp_tiles % slots == 0     # only the ragged last wave is cut
+            assert p.sk_items <= slots         # and its pieces fit one wave
         assert p.m_fastest in (0, 1)
 
 
@@ -30,8 +41,9 @@ def test_small_weight_gradients_split_the_token_dimension(pkg):
     # dW of the 125M projections: the output alone gives far fewer tiles than SMs
     for N, K in ((768, 768), (256, 768), (2048, 768), (768, 2048)):
         p = pkg.plan_bf16(2, 1, 8192, N, K, 148)
-        assert p.splits > 1
-        assert p.tiles >= 74
+        assert p.splits > 1 and p.dp_tiles == 0
+        busy = p.sk_items * (2 if p.cta_pair else 1)
+        assert busy >= 74, (N, K, p.bn, p.cta_pair, p.splits)
 
 
 def test_unaligned_pitch_goes_to_cuda_core_kernel(pkg):
