@@ -99,6 +99,24 @@ int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_coun
  * splits: 0 = cut only the ragged last wave (automatic), 1 = cut nothing, >= 2 = cut every tile. */
 int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits);
 
+/* Weight gradient dB[K,N] = bf16_rn(bf16_rn(A[M,K]^T * dC[M,N]) + dB) that allocates nothing.
+ * This entry point has no counterpart in the reference.  It exists for hosts in which this
+ * library must never allocate device memory: a trainer that gave the whole GPU to its own arena
+ * at start-up (a later cudaMalloc just fails), or a step loop that cannot take the device-wide
+ * stall of cudaMalloc/cudaFree when a context's workspace would have to grow.  It needs no
+ * context: its split-K scratch is a fixed array of about 8 MiB inside the library image, resident on
+ * every GPU that loads the library until the process exits.
+ *   - Limit: ceil(K/128) * ceil(N/128) <= 128 output tiles (e.g. 768x2048 or 2048x4096); larger
+ *     outputs return B200_E_TOOBIG.  N and K must be multiples of 8 and the pointers 16-byte
+ *     aligned (B200_E_BADARG otherwise; there is no slower fallback behind this call).
+ *   - The first call on each device looks up the array's device address and configures the
+ *     kernel; make that first call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels can run at the same time
+ *     (different streams) race.  Calls on one stream are safe; each clears the counters it needs.
+ *   - Asynchronous on `cuda_stream` (a cudaStream_t; NULL = legacy default stream). */
+int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const void* dC, int M, int N, int K,
+                                   void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

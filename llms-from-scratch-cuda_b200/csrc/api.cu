@@ -563,11 +563,12 @@ extern "C" int b200_linear_debug_flags(b200_linear_ctx* ctx, int flags) {
 extern "C" int b200_linear_debug_prof(b200_linear_ctx* ctx, long long* out16) {
     if (!ctx || !out16) return B200_E_BADARG;
     if (!ctx->prof_dev) {
-        CU_TRY(ctx, cudaMalloc(&ctx->prof_dev, 16 * sizeof(long long)));
-        CU_TRY(ctx, cudaMemset(ctx->prof_dev, 0, 16 * sizeof(long long)));
+        CU_TRY(ctx, cudaMalloc(&ctx->prof_dev, 32 * sizeof(long long)));
+        CU_TRY(ctx, cudaMemset(ctx->prof_dev, 0, 32 * sizeof(long long)));
     }
     CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    CU_TRY(ctx, cudaMemcpy(out16, ctx->prof_dev, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
+    CU_TRY(ctx, cudaMemcpy(out16, ctx->prof_dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost));
+    CU_TRY(ctx, cudaMemset(ctx->prof_dev + 16, 0, 16 * sizeof(long long)));
     return B200_OK;
 }
 #endif
@@ -617,5 +618,143 @@ extern "C" int b200_linear_backward_f32(b200_linear_ctx* ctx, float* dA, float* 
         if (rc) return rc;
     }
     if (dB) return launch_simt<float>(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K);
+    return B200_OK;
+}
+
+// ------------------------------------------------- weight gradient without any allocation
+// For hosts that must not see this library allocate device memory: a trainer that has handed
+// the whole GPU to an arena of its own at start-up (a later cudaMalloc simply fails there), or a
+// step loop that cannot afford the device-wide synchronisation that cudaMalloc / cudaFree imply
+// when the context's workspace has to grow for a shape it has not seen yet.  The split-K
+// scratch (fp32 partial tiles, arrival counters, status word) lives in the fixed array below,
+// which every GPU that loads this library carries until the process exits.
+namespace {
+
+constexpr int NA_BN = 128;                 // tile width used by this entry point (single-CTA tiles)
+constexpr int NA_MAX_ITEMS = 128;          // partial tiles that fit the array
+constexpr int NA_COUNTERS = 256;
+struct NoAllocScratch {
+    float partials[static_cast<size_t>(NA_MAX_ITEMS) * BM * NA_BN];  // 8 MiB
+    int counters[NA_COUNTERS];
+    int status;
+};
+
+struct NoAllocDevice {
+    bool ready = false;
+    NoAllocScratch* scratch = nullptr;  // device address of g_noalloc_scratch on that device
+    int sm_count = 0;
+    EncodeTiledFn encode = nullptr;
+};
+NoAllocDevice g_noalloc_dev[64];
+
+}  // namespace
+
+// In host code this name is only a handle for cudaGetSymbolAddress; kernels get the address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+// dB[K,N] = bf16_rn(bf16_rn(A[M,K]^T * dC[M,N]) + dB)   -- the beta = 1 product of matmul_backward.
+extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const void* dC, int M, int N, int K,
+                                              void* cuda_stream) {
+    if (!dB || !A || !dC || M <= 0 || N <= 0 || K <= 0) return B200_E_BADARG;
+    if ((N % 8) != 0 || (K % 8) != 0 ||
+        ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(dC)) & 15) != 0)
+        return B200_E_BADARG;  // no CUDA-core fallback here: TMA needs 16-byte pitches and pointers
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_E_NODEVICE;
+    NoAllocDevice& nd = g_noalloc_dev[dev];
+    using Cfg = TileCfg<NA_BN, 1>;
+    auto kern = gemm_bf16_sm100<NA_BN, true, true, true, 1>;
+    if (!nd.ready) {  // once per device, with that device current
+        int major = 0, sms = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+            return B200_E_NODEVICE;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            return B200_E_CUDA;
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || !fn)
+            return B200_E_CUDA;
+        void* base = nullptr;
+        if (cudaGetSymbolAddress(&base, g_noalloc_scratch) != cudaSuccess || !base) return B200_E_CUDA;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+            return B200_E_CUDA;
+        nd.scratch = static_cast<NoAllocScratch*>(base);
+        nd.sm_count = sms;
+        nd.encode = reinterpret_cast<EncodeTiledFn>(fn);
+        nd.ready = true;
+    }
+    const int Mo = K, No = N, Kc = M;  // output rows/cols, contraction over the tokens
+    const int tiles = ceil_div_i(Mo, BM) * ceil_div_i(No, NA_BN);
+    if (tiles > NA_MAX_ITEMS || tiles > NA_COUNTERS) return B200_E_TOOBIG;
+    int splits = NA_MAX_ITEMS / tiles;
+    if (splits > nd.sm_count / tiles) splits = nd.sm_count / tiles;
+    const int kb_total = ceil_div_i(Kc, BK);
+    if (splits > kb_total / 4) splits = kb_total / 4;
+    if (splits < 1) splits = 1;
+    const Decomp d = decompose(Mo, No, Kc, NA_BN, 1, nd.sm_count, splits);
+    if (d.sk_items > NA_MAX_ITEMS) return B200_E_TOOBIG;
+    const int items = d.dp_tiles + d.sk_items;
+    const int grid = items < nd.sm_count ? items : nd.sm_count;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+
+    GemmParams gp;
+    gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
+    gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
+    gp.m_fastest = Mo <= No ? 1 : 0;
+    gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
+    gp.p_3d = (Mo % 64) == 0;
+    gp.q_3d = (No % 64) == 0;
+    gp.out = dB;
+    gp.ws = nd.scratch->partials;
+    gp.sk_counters = nd.scratch->counters;
+    gp.status = &nd.scratch->status;
+    gp.prof = nullptr;
+    gp.dbg = 0;
+
+    auto encode = [&](CUtensorMap* tm, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                      const cuuint32_t* box) {
+        const cuuint32_t estr[3] = {1, 1, 1};
+        return nd.encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    auto mn_major_map = [&](CUtensorMap* tm, const void* ptr, int rows, bool as3d, int panels) {
+        if (as3d) {
+            const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(Kc), static_cast<cuuint64_t>(rows / 64)};
+            const cuuint64_t strides[2] = {static_cast<cuuint64_t>(rows) * 2, 128};
+            const cuuint32_t box[3] = {64, BK, static_cast<cuuint32_t>(panels)};
+            return encode(tm, ptr, 3, dims, strides, box);
+        }
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(Kc)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(rows) * 2};
+        const cuuint32_t box[2] = {64, BK};
+        return encode(tm, ptr, 2, dims, strides, box);
+    };
+    CUtensorMap tmP, tmQ, tmD;
+    if (!mn_major_map(&tmP, A, Mo, gp.p_3d != 0, BM / 64)) return B200_E_CUDA;
+    if (!mn_major_map(&tmQ, dC, No, gp.q_3d != 0, NA_BN / 64)) return B200_E_CUDA;
+    {
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(No), static_cast<cuuint64_t>(Mo)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(No) * 2};
+        const cuuint32_t box[2] = {64, 32};
+        if (!encode(&tmD, dB, 2, dims, strides, box)) return B200_E_CUDA;
+    }
+    // The array keeps whatever the previous call left: the counters and the status word must start at zero.
+    if (cudaMemsetAsync(nd.scratch->counters, 0, sizeof(int) * (NA_COUNTERS + 1), stream) != cudaSuccess)
+        return B200_E_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, gp) != cudaSuccess) return B200_E_CUDA;
     return B200_OK;
 }

@@ -60,10 +60,14 @@ struct GemmParams {
 #ifdef B200_PROFILE
 #define PROF_WRITE(idx, val) do { if (p.prof && blockIdx.x == 0) p.prof[idx] = (val); } while (0)
 #define PROF_MARK(idx) PROF_WRITE(idx, clock64() - t_kernel)
+#define PROF_T(name) const long long name = clock64()
+#define PROF_MAX(idx, val) do { if (p.prof) atomicMax((unsigned long long*)&p.prof[idx], (unsigned long long)(val)); } while (0)
 #define DBG(bit) (p.dbg & (bit))
 #else
 #define PROF_WRITE(idx, val)
 #define PROF_MARK(idx)
+#define PROF_T(name)
+#define PROF_MAX(idx, val)
 #define DBG(bit) false
 #endif
 
@@ -493,10 +497,13 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 // One range of a split tile: park the partial, count the arrival, and if every
                 // other range of this tile has already arrived, reduce them all and write the tile.
                 float* block = p.ws + (static_cast<size_t>(w.sk_item) * CTAS + rank) * Cfg::PARTIAL_FLOATS;
+                PROF_T(ts0);
                 epilogue_store_partial<BN>(block, taddr, q, hsel, lane);
                 release_acc();
+                PROF_T(ts1);
                 __threadfence();
                 __syncwarp();
+                PROF_T(ts2);
                 if (lane == 0) mbar_arrive(smem_u32(&ctrl->sk_written));
                 if (warp == 4 && lane == 0) {
                     if (mbar_wait(smem_u32(&ctrl->sk_written), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER)) {
@@ -515,6 +522,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
                 sk_phase ^= 1;
+                PROF_T(ts3);
+                if (warp == 4 && lane == 0) { PROF_MAX(16, ts1 - ts0); PROF_MAX(17, ts2 - ts1); PROF_MAX(18, ts3 - ts2); }
                 if (ctrl->sk_last) {
                     __threadfence();
                     const float* first = p.ws + (static_cast<size_t>(w.sk_tile) * p.sk_splits * CTAS + rank) *
@@ -522,6 +531,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     epilogue_store_bf16<BN, BETA1, true>(p, &tmD, my_buf, 0, first,
                                                          static_cast<size_t>(CTAS) * Cfg::PARTIAL_FLOATS, p.sk_splits, q,
                                                          hsel, row0, lane, w.n_blk * BN);
+                    PROF_T(ts4);
+                    if (warp == 4 && lane == 0) PROF_MAX(19, ts4 - ts3);
                 }
                 // every warp must have read sk_last before the next split item overwrites it
                 __syncwarp();
