@@ -224,20 +224,32 @@ def run_ours(args):
     # ---- per-GEMM timing (rank 0): CUDA events on the launching stream, each GEMM alone
     per = []
     dominant = None
+    side = torch.cuda.Stream()
+    h.set_stream(side)  # per-GEMM timing: 10 launches captured in a CUDA graph, replayed, timed with events on that stream
     for b in bufs:
         for kind, call, flop in (
                 ("fwd_nn", lambda: pkg.gemm(h, pkg.FWD_NN, 0, b["C"], b["A"], b["B"], TOKENS, b["N"], b["K"]), 1),
                 ("dgrad_nt", lambda: pkg.gemm(h, pkg.DGRAD_NT, 0, b["dA"], b["dC"], b["B"], TOKENS, b["N"], b["K"]), 1),
                 ("wgrad_tn", lambda: pkg.gemm(h, pkg.WGRAD_TN, 1, b["dB"], b["A"], b["dC"], TOKENS, b["N"], b["K"]), 1)):
-            for _ in range(3):
-                call()
             reps = 10
             l0 = h.launches
-            e0.record()
-            for _ in range(reps):
-                call()
-            e1.record()
-            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    call()
+                side.synchronize()
+                l0 = h.launches
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(reps):
+                        call()
+                launches_in_graph = h.launches - l0
+                graph.replay()
+                side.synchronize()
+                e0.record(side)
+                graph.replay()
+                e1.record(side)
+                side.synchronize()
+            l0 = h.launches - launches_in_graph
             us = e0.elapsed_time(e1) / reps * 1e3
             fl = 2.0 * TOKENS * b["N"] * b["K"]
             rec = {"proj": b["name"], "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1),

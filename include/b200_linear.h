@@ -92,11 +92,15 @@ typedef struct {
     int waves_x100;
     int dp_tiles;
     int sk_items;
+    int cluster_split;  /* > 1: every tile is shared by a cluster of this many CTAs (or CTA pairs), one
+                           range of the contraction each, summed through distributed shared memory */
 } b200_linear_plan_t;
 int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
                           b200_linear_plan_t* plan);
 /* Force a plan for subsequent bf16 calls on this context (bn = -1 restores the heuristic).
- * splits: 0 = cut only the ragged last wave (automatic), 1 = cut nothing, >= 2 = cut every tile. */
+ * splits: 0 = cut only the ragged last wave (automatic), 1 = cut nothing, >= 2 = cut every tile
+ * (partials through the workspace), < 0 = share every tile among a cluster of |splits| CTAs (or
+ * pairs) that sum through distributed shared memory (|splits| * (1 + cta_pair) <= 8, |splits| <= bn/32). */
 int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits);
 
 /* Weight gradient dB[K,N] = bf16_rn(bf16_rn(A[M,K]^T * dC[M,N]) + dB) that allocates nothing.

@@ -59,6 +59,8 @@ struct b200_linear_ctx {
     int last_cuda = 0;
     int force_bn = -1, force_pair = 0, force_splits = 0;
     int use_pdl = 1;
+    int no_peer_split = 0;
+    int one_producer = 0;
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
 };
@@ -75,7 +77,8 @@ int cuda_fail(b200_linear_ctx* ctx, cudaError_t e) {
         if (e__ != cudaSuccess) return cuda_fail((ctx), e__); \
     } while (0)
 
-// bf16 2-D tensor map over a row-major [outer][inner] matrix, 128-byte swizzle.
+// bf16 2-D tensor map over a row-major [outer][inner] matrix; 128-byte swizzle for 64-element-wide
+// boxes, 64-byte swizzle for 32-element-wide ones.
 int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
                    uint32_t box_outer, CUtensorMap* out) {
     TmKey key{ptr, inner, outer, box_inner, box_outer};
@@ -89,7 +92,8 @@ int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
-                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         ctx->last_cuda = 100000 + static_cast<int>(r);
@@ -154,8 +158,8 @@ Decomp decompose(int Mo, int No, int Kc, int bn, int ctas, int slots, int force_
     if (splits >= 2) {
         const int per = ceil_div_i(d.kb_total, splits);
         splits = ceil_div_i(d.kb_total, per);
-        // worth it only if the cut saves at least ~6 blocks of main loop (or was asked for)
-        if (splits >= 2 && (force_splits >= 2 || d.kb_total - per >= 6)) {
+        // worth it only if the cut saves at least ~10 blocks of main loop (or was asked for)
+        if (splits >= 2 && (force_splits >= 2 || d.kb_total - per >= 10)) {
             d.dp_tiles = d.tiles - sk_tiles;
             d.sk_splits = splits;
             d.kb_per_sk = per;
@@ -165,20 +169,37 @@ Decomp decompose(int Mo, int No, int Kc, int bn, int ctas, int slots, int force_
     return d;
 }
 
-// Estimated duration in nanoseconds.  Per-block (BK = 64) main-loop costs are measured
-// averages on a B200 under sustained load; they already contain the L2->SM feed limit that
-// makes narrow tiles and single-CTA tiles slower per FLOP than 256-wide CTA-pair tiles.
+// Main-loop cost of one BK = 64 block of one work item, in nanoseconds: measured averages on a
+// B200 (graph replay, SM clock ~1.75 GHz).  Every configuration is bound by the L2 -> SM feed
+// (about 60 B/clk/SM without multicast), which is why 256-wide CTA-pair tiles, with the most
+// reuse per byte fetched, are the cheapest per FLOP.
+double per_block_ns(int bn, int ctas) {
+    if (ctas == 2) return bn == 256 ? 335.0 : 300.0;
+    return bn == 256 ? 400.0 : bn == 192 ? 335.0 : bn == 128 ? 255.0 : 200.0;
+}
+
+// Estimated duration in nanoseconds of the persistent schedule described by `d`.
 double plan_cost_ns(const Decomp& d, int bn, int ctas, int slots) {
-    double per_kb;
-    if (ctas == 2) per_kb = bn == 256 ? 420.0 : 300.0;
-    else per_kb = bn == 256 ? 490.0 : bn == 192 ? 385.0 : bn == 128 ? 300.0 : 230.0;
+    const double per_kb = per_block_ns(bn, ctas);
     const int dp_rounds = (d.dp_tiles + slots - 1) / slots;
     const int sk_rounds = (d.sk_items + slots - 1) / slots;
     double t = (static_cast<double>(dp_rounds) * d.kb_total + static_cast<double>(sk_rounds) * d.kb_per_sk) * per_kb;
-    t += 350.0 * (dp_rounds + sk_rounds);  // pipeline refill at item boundaries
-    t += 500.0 + 6.0 * bn;                 // the last epilogue is exposed
-    if (d.sk_items > 0) t += 1200.0 + 2.0 * d.sk_splits * bn;  // partial round trip + reduction
+    t += 300.0 * (dp_rounds + sk_rounds);  // pipeline refill at item boundaries
+    t += 600.0 + 4.0 * bn;                 // the last epilogue is exposed
+    if (d.sk_items > 0) {
+        // partial sums through L2: peers exchanging slices (all resident) or a last arriver adding whole tiles
+        const bool peer = d.sk_items <= slots && d.sk_splits <= bn / 32;
+        t += peer ? 5000.0 : 6000.0 + 1500.0 * d.sk_splits;
+    }
     return t;
+}
+
+// Clusters of `size` CTAs (one CTA per SM) that can be resident at once, measured on a 148-SM B200
+// with cudaOccupancyMaxActiveClusters and scaled to the SM count at hand.
+int max_resident_clusters(int size, int sm_count) {
+    static const int per148[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};
+    if (size < 1 || size > 8) return 0;
+    return per148[size] * sm_count / 148;
 }
 
 }  // namespace
@@ -216,7 +237,30 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
             plan->tiles = d.tiles;
             plan->dp_tiles = d.dp_tiles;
             plan->sk_items = d.sk_items;
+            plan->cluster_split = 0;
             plan->waves_x100 = static_cast<int>(100LL * (d.dp_tiles + d.sk_items) / slots);
+        }
+        // Small outputs: every tile shared by a cluster whose members split the contraction and add
+        // up through distributed shared memory -- only if all clusters are resident in one wave.
+        const int kb_total = ceil_div_i(Kc, BK);
+        for (int ks = 8 / ctas; ks >= 2; --ks) {
+            if (ks > bn / 32 || kb_total / ks < 4) continue;
+            if (d.tiles > max_resident_clusters(ks * ctas, sm_count)) continue;
+            const int per = ceil_div_i(kb_total, ks);
+            if (ceil_div_i(kb_total, per) != ks) continue;
+            const double cc = per * per_block_ns(bn, ctas) + 300.0 + 600.0 + 4.0 * bn + 3500.0;
+            if (cc < best) {
+                best = cc;
+                plan->bn = bn;
+                plan->cta_pair = ctas == 2;
+                plan->splits = 1;
+                plan->tiles = d.tiles;
+                plan->dp_tiles = d.tiles;
+                plan->sk_items = 0;
+                plan->cluster_split = ks;
+                plan->waves_x100 = static_cast<int>(100LL * d.tiles * ks / slots);
+            }
+            break;  // the largest admissible cluster is the candidate
         }
     }
     plan->m_fastest = Mo <= No ? 1 : 0;
@@ -266,8 +310,14 @@ int ensure_counters(b200_linear_ctx* ctx, int n) {
 
 template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
 int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
-               const GemmParams& gp, int grid) {
+               const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
     using Cfg = TileCfg<BN, CTAS>;
+    if (gp.ksplit > 1) {  // the receive space of the cluster exchange must fit the pipeline stages
+        const int maxg = (BN / 32 + gp.ksplit - 1) / gp.ksplit;
+        if ((gp.ksplit - 1) * maxg * 8 * BM * 16 > Cfg::STAGES * Cfg::STAGE_BYTES || gp.ksplit > BN / 32 ||
+            CTAS * gp.ksplit > 8)
+            return B200_E_BADARG;
+    }
     static bool configured = false;
     auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, BETA1, CTAS>;
     if (!configured) {
@@ -281,7 +331,7 @@ int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& 
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.x = CTAS * gp.ksplit;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     // The kernel's set-up may overlap the tail of the previous kernel in the stream; it waits
@@ -290,35 +340,35 @@ int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& 
     attr[1].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, gp));
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD32, gp));
     ctx->launches++;
     return B200_OK;
 }
 
 template <bool P_MN, bool Q_MN, bool BETA1>
 int launch_bn(b200_linear_ctx* ctx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-              const CUtensorMap& tmD, const GemmParams& gp, int grid) {
+              const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
     if (ctas == 2) {
         switch (bn) {
-            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, gp, grid);
-            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, gp, grid);
+            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
+            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
             default: return B200_E_BADARG;
         }
     }
     switch (bn) {
-        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
-        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
-        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
-        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, gp, grid);
+        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
         default: return B200_E_BADARG;
     }
 }
 
 template <bool P_MN, bool Q_MN>
 int launch_beta(b200_linear_ctx* ctx, int bn, int ctas, int beta1, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-                const CUtensorMap& tmD, const GemmParams& gp, int grid) {
-    return beta1 ? launch_bn<P_MN, Q_MN, true>(ctx, bn, ctas, tmP, tmQ, tmD, gp, grid)
-                 : launch_bn<P_MN, Q_MN, false>(ctx, bn, ctas, tmP, tmQ, tmD, gp, grid);
+                const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
+    return beta1 ? launch_bn<P_MN, Q_MN, true>(ctx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid)
+                 : launch_bn<P_MN, Q_MN, false>(ctx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid);
 }
 
 template <typename T>
@@ -345,18 +395,30 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
     else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
 
-    int bn = plan.bn, ctas = plan.cta_pair ? 2 : 1, force_splits = 0;
+    int bn = plan.bn, ctas = plan.cta_pair ? 2 : 1, force_splits = 0, ksplit = plan.cluster_split > 1 ? plan.cluster_split : 1;
     if (ctx->force_bn > 0) {
         bn = ctx->force_bn;
         ctas = ctx->force_pair ? 2 : 1;
         force_splits = ctx->force_splits;
+        ksplit = 1;
+        if (force_splits < 0) {  // cluster split: |splits| members per tile
+            ksplit = -force_splits;
+            force_splits = 1;
+            const int kb = ceil_div_i(Kc, BK);
+            if (ksplit > kb) ksplit = kb;
+            if (ksplit < 1) ksplit = 1;
+            const int per = ceil_div_i(kb, ksplit);
+            ksplit = ceil_div_i(kb, per);  // every member owns at least one block
+        }
     }
+    if (ksplit > 1) force_splits = 1;
     if (ctx->sm_count < ctas) return B200_E_NODEVICE;
-    const int max_slots = ctx->sm_count / ctas;  // CTAs (or CTA pairs) resident at once
-    const Decomp d = decompose(Mo, No, Kc, bn, ctas, max_slots, force_splits);
+    const int max_slots = ksplit > 1 ? 0x7FFFFFFF : ctx->sm_count / ctas;  // CTAs (or pairs) resident at once
+    const Decomp d = decompose(Mo, No, Kc, bn, ctas, ksplit > 1 ? 1 : max_slots, force_splits);
     const long long items = static_cast<long long>(d.dp_tiles) + d.sk_items;
-    if (items > 0x7FFFFFFFLL || static_cast<long long>(d.tiles) * (d.sk_splits > 1 ? d.sk_splits : 1) > 0x7FFFFFFFLL)
+    if (items * ksplit * ctas > 0x7FFFFFFFLL || static_cast<long long>(d.tiles) * (d.sk_splits > 1 ? d.sk_splits : 1) > 0x7FFFFFFFLL)
         return B200_E_TOOBIG;
+    // cluster split: one cluster per tile; otherwise a persistent grid of at most one CTA (pair) per SM
     const int slots = items < max_slots ? static_cast<int>(items) : max_slots;
 
     GemmParams gp;
@@ -364,14 +426,27 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
     gp.m_fastest = plan.m_fastest;
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
+    gp.ksplit = ksplit;
+    gp.one_producer = ctx->one_producer;
     gp.out = out;
     gp.status = ctx->status_dev;
     gp.prof = ctx->prof_dev;
     gp.dbg = ctx->dbg;
     gp.ws = nullptr;
     gp.sk_counters = nullptr;
+    gp.sk_peer = 0;
     if (d.sk_items > 0) {
-        rc = ensure_workspace(ctx, static_cast<size_t>(d.sk_items) * ctas * BM * bn * sizeof(float));
+        // The ranges of a split tile can exchange partial sums among themselves only if they are all
+        // running at once: each must be the first work item of its own CTA (pair) of a grid that fits.
+        const int groups = bn / 32;
+        gp.sk_peer = (d.sk_items <= max_slots && d.sk_splits <= groups && !ctx->no_peer_split) ? 1 : 0;
+        size_t ws_bytes = static_cast<size_t>(d.sk_items) * ctas * BM * bn * sizeof(float);
+        if (gp.sk_peer) {
+            const int maxg = (groups + d.sk_splits - 1) / d.sk_splits;
+            ws_bytes = static_cast<size_t>(d.tiles - d.dp_tiles) * ctas * d.sk_splits * (d.sk_splits - 1) * maxg *
+                       (8 * BM * 4) * sizeof(float);
+        }
+        rc = ensure_workspace(ctx, ws_bytes);
         if (rc) return rc;
         rc = ensure_counters(ctx, (d.tiles - d.dp_tiles) * ctas);
         if (rc) return rc;
@@ -398,11 +473,16 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     // Output map for the epilogue's TMA stores: [Mo][No] bf16, box = 64 columns x 32 rows.
     rc = get_tensor_map(ctx, out, No, Mo, 64, 32, &tmD);
     if (rc) return rc;
+    CUtensorMap tmD32 = tmD;  // 32-column blocks: the cluster-split and peer-split epilogues use it
+    if (ksplit > 1 || gp.sk_peer) {
+        rc = get_tensor_map(ctx, out, No, Mo, 32, 32, &tmD32);
+        if (rc) return rc;
+    }
 
-    const int grid = slots * ctas;
-    if (p_mn) return launch_beta<true, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, gp, grid);
-    if (q_mn) return launch_beta<false, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, gp, grid);
-    return launch_beta<false, false>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, gp, grid);
+    const int grid = slots * ctas * ksplit;
+    if (p_mn) return launch_beta<true, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    if (q_mn) return launch_beta<false, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    return launch_beta<false, false>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
 }
 
 template <typename T, bool P_MN, bool Q_MN>
@@ -492,6 +572,8 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     }
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
     if (const char* e = getenv("B200_LINEAR_PDL")) ctx->use_pdl = atoi(e) != 0;
+    if (const char* e = getenv("B200_LINEAR_PEER_SPLIT")) ctx->no_peer_split = atoi(e) == 0;
+    if (const char* e = getenv("B200_LINEAR_ONE_PRODUCER")) ctx->one_producer = atoi(e) != 0;
     if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
         delete ctx;
@@ -554,6 +636,40 @@ extern "C" const char* b200_linear_strerror(int code) {
 }
 
 #ifdef B200_PROFILE
+// Profiling builds only: how many clusters of `cluster` CTAs of the wgrad kernel can be resident.
+extern "C" int b200_linear_debug_max_clusters(int bn, int ctas, int cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = -1;
+    cudaError_t e;
+    if (bn == 256 && ctas == 1) {
+        auto k = gemm_bf16_sm100<256, true, true, true, 1>;
+        cfg.dynamicSmemBytes = TileCfg<256, 1>::SMEM_BYTES;
+        cfg.gridDim = dim3(cluster * 64, 1, 1);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.dynamicSmemBytes);
+        e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
+    } else if (bn == 256 && ctas == 2) {
+        auto k = gemm_bf16_sm100<256, true, true, true, 2>;
+        cfg.dynamicSmemBytes = TileCfg<256, 2>::SMEM_BYTES;
+        cfg.gridDim = dim3(cluster * 64, 1, 1);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.dynamicSmemBytes);
+        e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
+    } else {
+        auto k = gemm_bf16_sm100<128, true, true, true, 1>;
+        cfg.dynamicSmemBytes = TileCfg<128, 1>::SMEM_BYTES;
+        cfg.gridDim = dim3(cluster * 64, 1, 1);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.dynamicSmemBytes);
+        e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
+    }
+    return e == cudaSuccess ? n : -static_cast<int>(e);
+}
 extern "C" int b200_linear_debug_flags(b200_linear_ctx* ctx, int flags) {
     if (!ctx) return B200_E_BADARG;
     ctx->dbg = flags;
@@ -569,6 +685,7 @@ extern "C" int b200_linear_debug_prof(b200_linear_ctx* ctx, long long* out16) {
     CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     CU_TRY(ctx, cudaMemcpy(out16, ctx->prof_dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost));
     CU_TRY(ctx, cudaMemset(ctx->prof_dev + 16, 0, 16 * sizeof(long long)));
+    CU_TRY(ctx, cudaMemset(ctx->prof_dev + 20, 0xFF, sizeof(long long)));
     return B200_OK;
 }
 #endif
@@ -577,6 +694,7 @@ extern "C" int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair
     if (!ctx) return B200_E_BADARG;
     if (bn > 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return B200_E_BADARG;
     if (bn > 0 && cta_pair && bn != 128 && bn != 256) return B200_E_BADARG;
+    if (bn > 0 && splits < 0 && (-splits * (cta_pair ? 2 : 1) > 8 || -splits > bn / 32)) return B200_E_BADARG;
     ctx->force_bn = bn;
     ctx->force_pair = cta_pair;
     ctx->force_splits = splits;
@@ -703,6 +821,9 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
     gp.m_fastest = Mo <= No ? 1 : 0;
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
+    gp.ksplit = 1;
+    gp.sk_peer = 0;
+    gp.one_producer = 0;
     gp.p_3d = (Mo % 64) == 0;
     gp.q_3d = (No % 64) == 0;
     gp.out = dB;
@@ -755,6 +876,6 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, gp) != cudaSuccess) return B200_E_CUDA;
+    if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD, gp) != cudaSuccess) return B200_E_CUDA;
     return B200_OK;
 }

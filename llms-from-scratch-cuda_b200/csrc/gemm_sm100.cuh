@@ -48,7 +48,12 @@ struct GemmParams {
     int sk_splits;           // tiles [dp_tiles, m_tiles*n_tiles) are cut into this many ranges
     int kb_per_sk;           // ceil(kb_total/sk_splits); every range owns >= 1 block
     int sk_items;            // (m_tiles*n_tiles - dp_tiles) * sk_splits
+    int sk_peer;             // 1: the ranges of a split tile exchange partial sums among themselves (all resident
+                             //    at once); 0: they park whole partial tiles and the last arriver adds them up
+    int ksplit;              // > 1: a cluster of CTAS*ksplit CTAs shares each tile, every member takes one
+                             // range of the contraction and the sum is formed through distributed smem
     int p_3d, q_3d;          // MN-major operand described by a 3-D map: one copy per stage
+    int one_producer;        // 1: a single thread issues the copies of both operands
     void* out;               // bf16 [Mo,No]
     float* ws;               // split partials: sk_items * CTAS blocks of BM x BN fp32
     int* sk_counters;        // one arrival counter per (split tile, CTA of the pair); zero between launches
@@ -96,6 +101,7 @@ struct WorkItem {
     int kb0, kb1;       // contraction blocks [kb0, kb1)
     int sk_item;        // -1: whole tile; else index of this partial in the workspace
     int sk_tile;        // index of the split tile (counter index), when sk_item >= 0
+    int sk_split;       // which range of that tile
 };
 
 // The i-th work item of `slot` (split items first, then whole tiles); false when the slot is done.
@@ -107,6 +113,7 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int slot, int nslo
         w.sk_item = u;
         w.sk_tile = u / p.sk_splits;
         const int split = u - w.sk_tile * p.sk_splits;
+        w.sk_split = split;
         tile = p.dp_tiles + w.sk_tile;
         w.kb0 = split * p.kb_per_sk;
         w.kb1 = min(w.kb0 + p.kb_per_sk, p.kb_total);
@@ -115,6 +122,7 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int slot, int nslo
         if (tile >= p.dp_tiles) return false;
         w.sk_item = -1;
         w.sk_tile = 0;
+        w.sk_split = 0;
         w.kb0 = 0;
         w.kb1 = p.kb_total;
     }
@@ -126,6 +134,15 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int slot, int nslo
         w.n_blk = tile - w.m_blk * p.n_tiles;
     }
     return true;
+}
+
+// Cluster split: member `krank` of the cluster keeps only its own range of the contraction.
+__device__ __forceinline__ void narrow_to_krank(const GemmParams& p, int krank, WorkItem& w) {
+    if (p.ksplit > 1) {
+        const int per = (p.kb_total + p.ksplit - 1) / p.ksplit;
+        w.kb0 = krank * per;
+        w.kb1 = min(w.kb0 + per, p.kb_total);
+    }
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -143,6 +160,10 @@ struct alignas(8) GemmCtrl {
     unsigned long long tmem_empty[2];  // epilogue -> MMA: accumulator drained (pair: lives in the even CTA)
     unsigned long long sk_written;     // the 4 epilogue warps have stored their part of a partial tile
     unsigned long long sk_decided;     // "am I the last arriver" has been published in sk_last
+    unsigned long long sk_read;        // peer split: the 8 epilogue warps have read the other members' partials
+    unsigned long long old_bar[8];     // beta = 1: epilogue warp w's copy of the old output block has landed
+    unsigned long long ml_done;        // cluster split: the other members have finished their main loops
+    unsigned long long cs_recv;        // cluster split: the other members' slices of my columns have landed
     uint32_t tmem_base;
     int abort_flag;
     int sk_last;
@@ -194,11 +215,13 @@ __device__ __forceinline__ void add_partial32(uint32_t* acc, const float4 (&v)[8
 // store of a 32 x 64 box (TMA clips rows/columns beyond the matrix, so tails need no predicates).
 // The fp32 values come from TMEM (FROM_WS = false) or from the sum of `nsplits` partial tiles
 // in the workspace, added in the order 0..nsplits-1 (FROM_WS = true).
+// beta = 1: the old 32 x 64 block is fetched by TMA into the same staging buffer and updated in
+// place (each thread reads and rewrites only its own row), so global memory sees whole lines only.
 template <int BN, bool BETA1, bool FROM_WS>
-__device__ __forceinline__ void epilogue_store_bf16(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
+__device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
                                                     uint32_t taddr, const float* partials, size_t partial_stride,
-                                                    int nsplits, int q, int hsel, int row0, int lane, int n0) {
-    const int row = row0 + lane;
+                                                    int nsplits, int q, int hsel, int row0, int lane, int n0,
+                                                    uint32_t old_bar, uint32_t& old_phase, volatile int* abort_flag) {
 #pragma unroll 1
     for (int c = hsel; c < BN / 64; c += 2) {
         const int col0 = n0 + c * 64;
@@ -208,13 +231,13 @@ __device__ __forceinline__ void epilogue_store_bf16(const GemmParams& p, const C
             tmem_ld_32x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
             tmem_ld_32x32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
         }
-        uint4 old[8];
         if constexpr (BETA1) {
-            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.No + col0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                old[j] = (row < p.Mo && col0 + 8 * j < p.No) ? *reinterpret_cast<const uint4*>(src + 8 * j)
-                                                           : make_uint4(0, 0, 0, 0);
+            // the warp's previous store must have finished reading the staging buffer
+            if (lane == 0) {
+                tma_store_wait_read<0>();
+                mbar_arrive_expect_tx(old_bar, EPI_BUF_BYTES);
+                tma_load_2d(smem_u32(buf), tmD, old_bar, col0, row0);  // rows/cols beyond the matrix read as 0
+            }
         }
         if constexpr (FROM_WS) {
 #pragma unroll
@@ -239,25 +262,35 @@ __device__ __forceinline__ void epilogue_store_bf16(const GemmParams& p, const C
         } else {
             tmem_ld_wait();
         }
-        // the warp's previous store must have finished reading the staging buffer
-        if (lane == 0) tma_store_wait_read<0>();
-        __syncwarp();
+        if constexpr (BETA1) {
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) return false;
+            old_phase ^= 1;
+        } else {
+            // the warp's previous store must have finished reading the staging buffer
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             float v[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[8 * j + e]);
+            // 128-byte swizzle: 16-byte chunk j of row `lane` lives at chunk (j ^ (lane & 7))
+            uint4* slot = reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4));
             if constexpr (BETA1) {
                 // Same two roundings as the reference's cuBLAS path: bf16_rn(bf16_rn(acc) + old).
+                const uint4 o = *slot;
                 const uint32_t a0 = pack_bf16x2(v[0], v[1]), a1 = pack_bf16x2(v[2], v[3]);
                 const uint32_t a2 = pack_bf16x2(v[4], v[5]), a3 = pack_bf16x2(v[6], v[7]);
-                v[0] = bf16_lo(a0) + bf16_lo(old[j].x); v[1] = bf16_hi(a0) + bf16_hi(old[j].x);
-                v[2] = bf16_lo(a1) + bf16_lo(old[j].y); v[3] = bf16_hi(a1) + bf16_hi(old[j].y);
-                v[4] = bf16_lo(a2) + bf16_lo(old[j].z); v[5] = bf16_hi(a2) + bf16_hi(old[j].z);
-                v[6] = bf16_lo(a3) + bf16_lo(old[j].w); v[7] = bf16_hi(a3) + bf16_hi(old[j].w);
+                v[0] = bf16_lo(a0) + bf16_lo(o.x); v[1] = bf16_hi(a0) + bf16_hi(o.x);
+                v[2] = bf16_lo(a1) + bf16_lo(o.y); v[3] = bf16_hi(a1) + bf16_hi(o.y);
+                v[4] = bf16_lo(a2) + bf16_lo(o.z); v[5] = bf16_hi(a2) + bf16_hi(o.z);
+                v[6] = bf16_lo(a3) + bf16_lo(o.w); v[7] = bf16_hi(a3) + bf16_hi(o.w);
             }
-            // 128-byte swizzle: 16-byte chunk j of row `lane` lives at chunk (j ^ (lane & 7))
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            *slot =
                 make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                            pack_bf16x2(v[6], v[7]));
         }
@@ -268,15 +301,306 @@ __device__ __forceinline__ void epilogue_store_bf16(const GemmParams& p, const C
             tma_store_commit();
         }
     }
+    return true;
 }
 
-// Warp roles: 0 = TMA producer, 1 = MMA issuer (even CTA only in a pair), 2 = TMEM allocator,
-// 3 = idle, 4..11 = epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 only, so warps w and
+// Write one 32 x 32 block (this warp's rows, one 32-column group) of fp32 sums as bf16 through the
+// warp's staging buffer (64-byte swizzle) and a TMA store.  beta = 1: `begin` (called before the
+// sums are formed) starts a TMA load of the old block into the same buffer, `finish` updates it in place.
+template <bool BETA1>
+__device__ __forceinline__ void block32_begin(const CUtensorMap* tmD32, uint8_t* buf, uint32_t old_bar, int col0,
+                                              int row0, int lane) {
+    if (lane == 0) {
+        tma_store_wait_read<0>();  // the previous store of this warp has finished reading the buffer
+        if constexpr (BETA1) {
+            mbar_arrive_expect_tx(old_bar, 32 * 64);
+            tma_load_2d(smem_u32(buf), tmD32, old_bar, col0, row0);  // beyond the matrix reads as 0
+        }
+    }
+}
+template <bool BETA1>
+__device__ __forceinline__ bool block32_finish(const GemmParams& p, const CUtensorMap* tmD32, uint8_t* buf,
+                                               const float (&acc)[32], uint32_t old_bar, uint32_t& old_phase,
+                                               int col0, int row0, int lane, volatile int* abort_flag) {
+    if constexpr (BETA1) {
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return false;
+        old_phase ^= 1;
+    } else {
+        __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = acc[8 * j + e];
+        // 64-byte swizzle: 16-byte chunk j of row `lane` lives at chunk (j ^ ((lane >> 1) & 3))
+        uint4* slot16 = reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4));
+        if constexpr (BETA1) {
+            // Same two roundings as the reference's cuBLAS path: bf16_rn(bf16_rn(acc) + old).
+            const uint4 o = *slot16;
+            const uint32_t a0 = pack_bf16x2(v[0], v[1]), a1 = pack_bf16x2(v[2], v[3]);
+            const uint32_t a2 = pack_bf16x2(v[4], v[5]), a3 = pack_bf16x2(v[6], v[7]);
+            v[0] = bf16_lo(a0) + bf16_lo(o.x); v[1] = bf16_hi(a0) + bf16_hi(o.x);
+            v[2] = bf16_lo(a1) + bf16_lo(o.y); v[3] = bf16_hi(a1) + bf16_hi(o.y);
+            v[4] = bf16_lo(a2) + bf16_lo(o.z); v[5] = bf16_hi(a2) + bf16_hi(o.z);
+            v[6] = bf16_lo(a3) + bf16_lo(o.w); v[7] = bf16_hi(a3) + bf16_hi(o.w);
+        }
+        *slot16 = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                             pack_bf16x2(v[6], v[7]));
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && row0 < p.Mo) {
+        tma_store_2d(tmD32, smem_u32(buf), col0, row0);
+        tma_store_commit();
+    }
+    return true;
+}
+
+// Cluster split: the ksplit members of a cluster hold partial sums of the SAME output tile (one
+// range of the contraction each) in their TMEM.  The tile's 32-column groups are dealt out to the
+// members; every member sends each other member that member's groups of its own partial sum
+// (st.async into the receiver's shared memory, counted on the receiver's barrier), then adds up
+// what it received for its own groups -- in member order 0..ksplit-1, whatever the arrival order --
+// applies beta and writes those columns.  Nothing goes through global memory.
+// The pipeline stages double as receive space: by then this CTA's main loop has finished, and a
+// member only starts sending after every member has said so (ml_done).
+// Returns false if a bounded wait ran out.
+template <int BN, bool BETA1, int CTAS>
+__device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, GemmCtrl* ctrl, uint8_t* recv,
+                                                       const CUtensorMap* tmD32, uint8_t* buf, uint32_t taddr, int q,
+                                                       int hsel, int lane, int warp, int row0, int n0, int krank,
+                                                       int rank, uint32_t old_bar, uint32_t& old_phase,
+                                                       volatile int* abort_flag) {
+    constexpr int G = BN / 32;                    // 32-column groups of the tile
+    const int S = p.ksplit;
+    const int maxg = (G + S - 1) / S;             // groups per member, upper bound
+    const int my_g0 = krank * G / S, my_g1 = (krank + 1) * G / S;
+    const uint32_t recv_bar = smem_u32(&ctrl->cs_recv);
+    const uint32_t recv_base = smem_u32(recv);
+    const int trow = q * 32 + lane;               // row of the tile this thread owns
+
+    PROF_T(tc0);
+    if (warp == 4 && lane == 0) {
+        mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((S - 1) * (my_g1 - my_g0)) * 32u * BM * 4u);
+        for (int d = 0; d < S; ++d)
+            if (d != krank) mbar_arrive_cluster(smem_u32(&ctrl->ml_done), static_cast<uint32_t>(d * CTAS + rank));
+    }
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait<true>(smem_u32(&ctrl->ml_done), 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+
+    PROF_T(tc1);
+    // send: my partial sums of every other member's column groups
+    for (int dd = 1; dd < S; ++dd) {
+        const int d = (krank + dd) % S;           // start with the next member: spreads the traffic
+        const int slot = krank < d ? krank : krank - 1;
+        const uint32_t target = static_cast<uint32_t>(d * CTAS + rank);
+        const uint32_t r_base = map_to_cta(recv_base, target);
+        const uint32_t r_bar = map_to_cta(recv_bar, target);
+        const int g0 = d * G / S, g1 = (d + 1) * G / S;
+#pragma unroll 1
+        for (int g = g0 + hsel; g < g1; g += 2) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + g * 32, r);
+            tmem_ld_wait();
+            const uint32_t dst = r_base + static_cast<uint32_t>(((slot * maxg + (g - g0)) * 8) * BM + trow) * 16u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                st_async_v4(dst + static_cast<uint32_t>(j * BM) * 16u, r[4 * j], r[4 * j + 1], r[4 * j + 2],
+                            r[4 * j + 3], r_bar);
+        }
+    }
+
+    PROF_T(tc2);
+    // receive, then sum my own column groups in member order
+    if (lane == 0) ok = mbar_wait<true>(recv_bar, 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+    PROF_T(tc3);
+    // The output goes out in 32 x 32 blocks through the warp's staging buffer (64-byte swizzle) and
+    // a TMA store; with beta = 1 the old block comes in by TMA first and is updated in place.
+#pragma unroll 1
+    for (int g = my_g0 + hsel; g < my_g1; g += 2) {
+        const int col0 = n0 + g * 32;
+        if (col0 >= p.No) break;  // whole group beyond the matrix (warp-uniform)
+        block32_begin<BETA1>(tmD32, buf, old_bar, col0, row0, lane);
+        uint32_t own[32];
+        tmem_ld_32x32(taddr + g * 32, own);
+        tmem_ld_wait();
+        float acc[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+        for (int k = 0; k < S; ++k) {
+            if (k == krank) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) acc[e] += __uint_as_float(own[e]);
+            } else {
+                const int slot = k < krank ? k : k - 1;
+                const uint8_t* src = recv + static_cast<size_t>(((slot * maxg + (g - my_g0)) * 8) * BM + trow) * 16;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float4 v = *reinterpret_cast<const float4*>(src + static_cast<size_t>(j * BM) * 16);
+                    acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
+                }
+            }
+        }
+        if (!block32_finish<BETA1>(p, tmD32, buf, acc, old_bar, old_phase, col0, row0, lane, abort_flag)) return false;
+    }
+    PROF_T(tc4);
+    if (warp == 4 && lane == 0) {
+        PROF_MAX(16, tc1 - tc0); PROF_MAX(17, tc2 - tc1); PROF_MAX(18, tc3 - tc2); PROF_MAX(19, tc4 - tc3);
+    }
+    return true;
+}
+
+// Peer split: the same exchange as the cluster split, for the ranges of a split tile that run on
+// CTAs anywhere on the GPU: partial sums travel through the workspace (L2) instead of distributed
+// shared memory.  Member `me` of the tile's `S` ranges stores, for every other member, its partial
+// sums of that member's column groups; publishes them with one counter increment; waits (bounded)
+// until all S members have published; then sums its own groups (own part from TMEM, the others'
+// from the workspace, in member order) and writes them.  Each member reads and writes (S-1)/S of a
+// tile instead of one member reading S whole tiles.
+// Requires all members of a tile to be resident at once: the host only selects this mode when the
+// split work items are the first item of distinct CTAs of a grid that fits the GPU.
+// `region` = this tile's exchange space for this CTA rank: S * (S-1) * maxg blocks of BM x 32 fp32.
+template <int BN, bool BETA1>
+__device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtrl* ctrl, float* region, int* counter,
+                                                    const CUtensorMap* tmD32, uint8_t* buf, uint32_t taddr, int q,
+                                                    int hsel, int lane, int warp, int row0, int n0, int me,
+                                                    uint32_t old_bar, uint32_t& old_phase, uint32_t sk_phase,
+                                                    volatile int* abort_flag) {
+    constexpr int G = BN / 32;
+    constexpr int BLOCK_FLOATS = 8 * BM * 4;      // one 32-column group of a tile: 8 float4 x 128 rows
+    const int S = p.sk_splits;
+    const int maxg = (G + S - 1) / S;
+    const int my_g0 = me * G / S, my_g1 = (me + 1) * G / S;
+    const int trow = q * 32 + lane;
+    auto block_of = [&](int dest, int slot, int gi) {
+        return region + static_cast<size_t>((dest * (S - 1) + slot) * maxg + gi) * BLOCK_FLOATS;
+    };
+    PROF_T(tc0);
+    for (int dd = 1; dd < S; ++dd) {
+        const int d = (me + dd) % S;
+        const int slot = me < d ? me : me - 1;
+        const int g0 = d * G / S, g1 = (d + 1) * G / S;
+#pragma unroll 1
+        for (int g = g0 + hsel; g < g1; g += 2) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + g * 32, r);
+            tmem_ld_wait();
+            float* dst = block_of(d, slot, g - g0) + trow * 4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(dst + j * BM * 4) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+    }
+    PROF_T(tc1);
+    // publish, then wait for the other members
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctrl->sk_written));
+    if (warp == 4 && lane == 0) {
+        int seen = 0;
+        if (mbar_wait(smem_u32(&ctrl->sk_written), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER)) {
+            __threadfence();
+            atomicAdd(counter, 1);
+            const long long t0 = clock64();
+            while (true) {
+                seen = *reinterpret_cast<volatile int*>(counter);
+                if (seen >= S) break;
+                if (*abort_flag) break;
+                if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                    *abort_flag = 1;
+                    atomicCAS(p.status, 0, DEV_TIMEOUT_PEER);
+                    break;
+                }
+            }
+            __threadfence();
+        }
+        ctrl->sk_last = seen >= S;
+        mbar_arrive(smem_u32(&ctrl->sk_decided));
+    }
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(smem_u32(&ctrl->sk_decided), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER);
+    ok = __shfl_sync(0xffffffffu, ok, 0) && ctrl->sk_last;
+    if (!ok) return false;
+    __threadfence();
+    PROF_T(tc2);
+#pragma unroll 1
+    for (int g = my_g0 + hsel; g < my_g1; g += 2) {
+        const int col0 = n0 + g * 32;
+        if (col0 >= p.No) break;  // whole group beyond the matrix (warp-uniform)
+        block32_begin<BETA1>(tmD32, buf, old_bar, col0, row0, lane);
+        uint32_t own[32];
+        tmem_ld_32x32(taddr + g * 32, own);
+        float acc[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+        tmem_ld_wait();
+        // members in order; the two next partial blocks are in flight while one is added
+        int k = 0;
+        while (k < S) {
+            if (k == me) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) acc[e] += __uint_as_float(own[e]);
+                ++k;
+                continue;
+            }
+            const int k2 = (k + 1 == me) ? k + 2 : k + 1;  // the next member that is not me
+            const bool two = k2 < S && k + 1 != me;         // k and k+1 are both others: load both
+            float4 va[8], vb[8];
+            const float* sa = block_of(me, k < me ? k : k - 1, g - my_g0) + trow * 4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) va[j] = __ldcg(reinterpret_cast<const float4*>(sa + j * BM * 4));
+            if (two) {
+                const float* sb = block_of(me, (k + 1) < me ? k + 1 : k, g - my_g0) + trow * 4;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) vb[j] = __ldcg(reinterpret_cast<const float4*>(sb + j * BM * 4));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                acc[4 * j] += va[j].x; acc[4 * j + 1] += va[j].y; acc[4 * j + 2] += va[j].z; acc[4 * j + 3] += va[j].w;
+            }
+            if (two) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    acc[4 * j] += vb[j].x; acc[4 * j + 1] += vb[j].y; acc[4 * j + 2] += vb[j].z; acc[4 * j + 3] += vb[j].w;
+                }
+                k += 2;
+            } else {
+                k += 1;
+            }
+            (void)k2;
+        }
+        if (!block32_finish<BETA1>(p, tmD32, buf, acc, old_bar, old_phase, col0, row0, lane, abort_flag)) return false;
+    }
+    PROF_T(tc3);
+    // everybody has read: the member that counts last puts the counter back to zero
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctrl->sk_read));
+    if (warp == 4 && lane == 0) {
+        if (mbar_wait(smem_u32(&ctrl->sk_read), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER)) {
+            const int prev = atomicAdd(counter, 1);
+            if (prev == 2 * S - 1) atomicExch(counter, 0);
+        }
+        PROF_MAX(16, tc1 - tc0); PROF_MAX(17, tc2 - tc1); PROF_MAX(18, tc3 - tc2);
+    }
+    return true;
+}
+
+// Warp roles: 0 = TMA producer for P, 3 = TMA producer for Q, 1 = MMA issuer (even CTA only in a
+// pair), 2 = TMEM allocator, 4..11 = epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 only, so warps w and
 // w+4 share a lane quarter and split its columns between them.
 template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD32,
+                const GemmParams p) {
     using Cfg = TileCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr bool PAIR = CTAS == 2;
@@ -292,15 +616,24 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     const long long t_kernel = clock64();
     unsigned long long g_kernel;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_kernel));
+    if (threadIdx.x == 0 && p.prof) {
+        atomicMin((unsigned long long*)&p.prof[20], g_kernel);
+        atomicMax((unsigned long long*)&p.prof[21], g_kernel);
+    }
 #endif
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // position in the CTA pair
-    const int slot = blockIdx.x / CTAS, nslots = gridDim.x / CTAS;
+    const uint32_t ctarank = cluster_ctarank();          // 0 when launched without a cluster
+    const uint32_t rank = ctarank % CTAS;                // position in the CTA pair
+    const uint32_t leader = ctarank - rank;              // cluster rank of the pair's MMA-issuing CTA
+    const int krank = static_cast<int>(ctarank / CTAS);  // which range of the contraction (cluster split)
+    const int cluster_ctas = CTAS * p.ksplit;
+    const int slot = blockIdx.x / cluster_ctas, nslots = gridDim.x / cluster_ctas;
+    const bool clustered = PAIR || p.ksplit > 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->full[s]), 1);
+            mbar_init(smem_u32(&ctrl->full[s]), p.one_producer ? 1 : 2);  // one arrival (+ byte count) per producer thread
             mbar_init(smem_u32(&ctrl->empty[s]), 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -309,6 +642,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         }
         mbar_init(smem_u32(&ctrl->sk_written), EPI_WARPS);
         mbar_init(smem_u32(&ctrl->sk_decided), 1);
+        mbar_init(smem_u32(&ctrl->sk_read), EPI_WARPS);
+        for (int w8 = 0; w8 < EPI_WARPS; ++w8) mbar_init(smem_u32(&ctrl->old_bar[w8]), 1);
+        mbar_init(smem_u32(&ctrl->ml_done), p.ksplit > 1 ? p.ksplit - 1 : 1);
+        mbar_init(smem_u32(&ctrl->cs_recv), 1);
         ctrl->abort_flag = 0;
         ctrl->sk_last = 0;
         fence_mbar_init();
@@ -317,6 +654,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         tma_prefetch_desc(&tmP);
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmD);
+        if (p.ksplit > 1 || p.sk_peer) tma_prefetch_desc(&tmD32);
     }
     if (warp == 2) {
         tmem_alloc<CTAS>(smem_u32(&ctrl->tmem_base), Cfg::TMEM_COLS);
@@ -324,7 +662,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     }
     tc_fence_before();
     __syncthreads();
-    if constexpr (PAIR) {  // the partner's barriers must exist before anything signals them
+    if (clustered) {  // the other CTAs' barriers must exist before anything signals them
         cluster_arrive_release();
         cluster_wait_acquire();
     }
@@ -337,14 +675,36 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     griddep_launch_dependents();
     if (threadIdx.x == 0) PROF_MARK(0);
 
-    if (warp == 0) {
-        // ------------------------------------------------------ TMA producer
-        if (lane == 0) {
+    if (warp == 0 || warp == 3) {
+        // ---------------------------------------------- TMA producers: warp 0 feeds P, warp 3 feeds Q
+        // (with p.one_producer, warp 0 feeds both and warp 3 idles)
+        const bool one = p.one_producer != 0;
+        if (lane == 0 && !(one && warp == 3)) {
+            const bool do_p = warp == 0, do_q = one || warp == 3;
             uint32_t stage = 0, phase = 0;
             uint32_t issued = 0;  // number of stage fills issued so far
             bool ok = true;
             WorkItem w;
+            auto issue = [&](bool is_q, uint32_t dst, uint32_t bar, int r0, int c0) {
+                const CUtensorMap* tm = is_q ? &tmQ : &tmP;
+                const bool mn = is_q ? Q_MN : P_MN;
+                const bool as3d = is_q ? (p.q_3d != 0) : (p.p_3d != 0);
+                const int panels = is_q ? Cfg::B_ROWS / 64 : BM / 64;
+                if (!mn) {            // global [rows][Kc]: box = BK contraction x rows
+                    if constexpr (PAIR) tma_load_2d_pair(dst, tm, bar, c0, r0);
+                    else tma_load_2d(dst, tm, bar, c0, r0);
+                } else if (as3d) {    // global [Kc][rows]: all 64-wide column panels in one copy
+                    if constexpr (PAIR) tma_load_3d_pair(dst, tm, bar, 0, c0, r0 >> 6);
+                    else tma_load_3d(dst, tm, bar, 0, c0, r0 >> 6);
+                } else {              // one copy per 64-wide column panel
+                    for (int j = 0; j < panels; ++j) {
+                        if constexpr (PAIR) tma_load_2d_pair(dst + j * (64 * BK * 2), tm, bar, r0 + 64 * j, c0);
+                        else tma_load_2d(dst + j * (64 * BK * 2), tm, bar, r0 + 64 * j, c0);
+                    }
+                }
+            };
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+                narrow_to_krank(p, krank, w);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
                 const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -354,56 +714,27 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                         break;
                     }
                     const uint32_t local_bar = smem_u32(&ctrl->full[stage]);
-                    const uint32_t bar = PAIR ? map_to_cta(local_bar, 0) : local_bar;
+                    const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
-                    const uint32_t sQ = sP + Cfg::A_BYTES;
                     if (rank == 0)
-                        mbar_arrive_expect_tx(local_bar, DBG(8) ? CTAS * Cfg::A_BYTES : CTAS * Cfg::STAGE_BYTES);
+                        mbar_arrive_expect_tx(local_bar, CTAS * ((do_p ? Cfg::A_BYTES : 0) + (do_q ? Cfg::B_BYTES : 0)));
                     const int c0 = kb * BK;
-                    auto load2 = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
-                        if constexpr (PAIR) tma_load_2d_pair(dst, tm, bar, x, y);
-                        else tma_load_2d(dst, tm, bar, x, y);
-                    };
-                    auto load3 = [&](uint32_t dst, const CUtensorMap* tm, int y, int z) {
-                        if constexpr (PAIR) tma_load_3d_pair(dst, tm, bar, 0, y, z);
-                        else tma_load_3d(dst, tm, bar, 0, y, z);
-                    };
-                    if constexpr (P_MN) {  // global [Kc][Mo]: 64-wide column panels of BK contraction rows
-                        if (p.p_3d) {
-                            load3(sP, &tmP, c0, m0 >> 6);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < BM / 64; ++j) load2(sP + j * (64 * BK * 2), &tmP, m0 + 64 * j, c0);
-                        }
-                    } else {               // global [Mo][Kc]: box = BK contraction x BM rows
-                        load2(sP, &tmP, c0, m0);
-                    }
-                    if (DBG(8)) {
-                    } else if constexpr (Q_MN) {
-                        if (p.q_3d) {
-                            load3(sQ, &tmQ, c0, n0 >> 6);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < Cfg::B_ROWS / 64; ++j)
-                                load2(sQ + j * (64 * BK * 2), &tmQ, n0 + 64 * j, c0);
-                        }
-                    } else {
-                        load2(sQ, &tmQ, c0, n0);
-                    }
-                    if (issued == 0) PROF_MARK(1);
+                    if (do_p) issue(false, sP, bar, m0, c0);
+                    if (do_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
+                    if (issued == 0 && do_p) PROF_MARK(1);
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
-            if (!ok && rank == 0) {
+            if (!ok && rank == 0 && do_p) {
                 // Abort path: let every copy counted on this CTA's barriers land before exit.
                 const uint32_t n_back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
-                uint32_t s = stage, ph = phase;
+                uint32_t s2 = stage, ph = phase;
                 for (uint32_t i = 0; i < n_back; ++i) {
-                    if (s == 0) { s = STAGES; ph ^= 1; }
-                    --s;
+                    if (s2 == 0) { s2 = STAGES; ph ^= 1; }
+                    --s2;
                     const long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&ctrl->full[s]), ph)) {
+                    while (!mbar_try_wait(smem_u32(&ctrl->full[s2]), ph)) {
                         if (clock64() - t0 > WAIT_LIMIT_CYCLES / 8) {
                             atomicCAS(p.status, 0, DEV_TIMEOUT_DRAIN);
                             break;
@@ -424,7 +755,12 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             WorkItem w;
+            const uint64_t descP0 = umma_smem_desc(smem_u32(tiles), P_LBO, 1024);
+            const uint64_t descQ0 = umma_smem_desc(smem_u32(tiles) + Cfg::A_BYTES, Q_LBO, 1024);
+            const uint16_t pair_mask = static_cast<uint16_t>(3u << leader);
+            (void)pair_mask;
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+                narrow_to_krank(p, krank, w);
                 const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
                 if (!mbar_wait<PAIR>(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
                                      DEV_TIMEOUT_TMEM_E)) {
@@ -441,32 +777,35 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     }
                     tc_fence_after();
                     if (i == 0 && kb == w.kb0) PROF_MARK(2);
-                    const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
-                    const uint32_t sQ = sP + Cfg::A_BYTES;
+                    // only the 14-bit start-address field of a descriptor changes from stage to stage and
+                    // from one UMMA_K step to the next: add to the low word
+                    const uint32_t st_off = (stage * Cfg::STAGE_BYTES) >> 4;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t dP = umma_smem_desc(sP + k * P_STEP, P_LBO, 1024);
-                        const uint64_t dQ = umma_smem_desc(sQ + k * Q_STEP, Q_LBO, 1024);
+                        const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
+                        const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
                         if (DBG(4) && k > 0) continue;
                         umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
                     }
                     // frees the stage (in both CTAs of a pair) when the MMAs retire
-                    if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
+                    if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
                     else umma_commit(smem_u32(&ctrl->empty[stage]));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) {
-                    if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->tmem_full[acc]), 3);
+                    if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->tmem_full[acc]), pair_mask);
                     else umma_commit(smem_u32(&ctrl->tmem_full[acc]));
                 }
             }
             PROF_MARK(3);
+            PROF_MAX(22, clock64() - t_kernel);
         }
     } else if (warp >= 4) {
         // ---------------------------------------------------------- epilogue
         const int q = warp & 3;            // TMEM lane quarter
         const int hsel = (warp - 4) >> 2;  // which half of the column chunks
-        uint32_t sk_phase = 0;
+        uint32_t sk_phase = 0, old_phase = 0;
+        const uint32_t old_bar = smem_u32(&ctrl->old_bar[warp - 4]);
         bool ok = true;
         WorkItem w;
         for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
@@ -484,15 +823,33 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    if constexpr (PAIR) mbar_arrive_cluster(smem_u32(&ctrl->tmem_empty[acc]), 0);
+                    if constexpr (PAIR) mbar_arrive_cluster(smem_u32(&ctrl->tmem_empty[acc]), leader);
                     else mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
                 }
             };
-            if (w.sk_item < 0) {
-                if (!DBG(1))
-                    epilogue_store_bf16<BN, BETA1, false>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
-                                                          w.n_blk * BN);
+            if (p.ksplit > 1) {
+                ok = epilogue_cluster_split<BN, BETA1, CTAS>(p, ctrl, tiles, &tmD32, my_buf, taddr, q, hsel, lane, warp,
+                                                             row0, w.n_blk * BN, krank, static_cast<int>(rank), old_bar,
+                                                             old_phase, abort_flag);
                 release_acc();
+                if (!ok) break;
+            } else if (w.sk_item < 0) {
+                if (!DBG(1))
+                    ok = epilogue_store_bf16<BN, BETA1, false>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
+                                                               w.n_blk * BN, old_bar, old_phase, abort_flag);
+                release_acc();
+                if (!ok) break;
+            } else if (p.sk_peer) {
+                constexpr int G = BN / 32;
+                const int maxg = (G + p.sk_splits - 1) / p.sk_splits;
+                float* region = p.ws + (static_cast<size_t>(w.sk_tile) * CTAS + rank) * p.sk_splits * (p.sk_splits - 1) *
+                                           maxg * (8 * BM * 4);
+                ok = epilogue_peer_split<BN, BETA1>(p, ctrl, region, p.sk_counters + w.sk_tile * CTAS + rank, &tmD32,
+                                                    my_buf, taddr, q, hsel, lane, warp, row0, w.n_blk * BN, w.sk_split,
+                                                    old_bar, old_phase, sk_phase, abort_flag);
+                sk_phase ^= 1;
+                release_acc();
+                if (!ok) break;
             } else {
                 // One range of a split tile: park the partial, count the arrival, and if every
                 // other range of this tile has already arrived, reduce them all and write the tile.
@@ -528,9 +885,11 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     __threadfence();
                     const float* first = p.ws + (static_cast<size_t>(w.sk_tile) * p.sk_splits * CTAS + rank) *
                                                     Cfg::PARTIAL_FLOATS;
-                    epilogue_store_bf16<BN, BETA1, true>(p, &tmD, my_buf, 0, first,
-                                                         static_cast<size_t>(CTAS) * Cfg::PARTIAL_FLOATS, p.sk_splits, q,
-                                                         hsel, row0, lane, w.n_blk * BN);
+                    ok = epilogue_store_bf16<BN, BETA1, true>(p, &tmD, my_buf, 0, first,
+                                                              static_cast<size_t>(CTAS) * Cfg::PARTIAL_FLOATS, p.sk_splits,
+                                                              q, hsel, row0, lane, w.n_blk * BN, old_bar, old_phase,
+                                                              abort_flag);
+                    if (!ok) break;
                     PROF_T(ts4);
                     if (warp == 4 && lane == 0) PROF_MAX(19, ts4 - ts3);
                 }
@@ -547,7 +906,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // ------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if constexpr (PAIR) {  // neither CTA may leave while the other can still touch its smem/TMEM
+    if (clustered) {  // no CTA may leave while another can still touch its smem/TMEM
         cluster_arrive_release();
         cluster_wait_acquire();
     }

@@ -296,6 +296,15 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t fmt, uint32_t m, uint
            ((m >> 4) << 24);
 }
 
+// 16-byte store into another CTA's shared memory (`dst`, `bar`: shared::cluster addresses of
+// that CTA); the destination barrier's transaction count drops by 16 when the data has landed.
+__device__ __forceinline__ void st_async_v4(uint32_t dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d,
+                                            uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst),
+                 "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar)
+                 : "memory");
+}
+
 // ------------------------------------------------ programmatic dependent launch
 __device__ __forceinline__ void griddep_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -69,6 +69,32 @@ def test_every_tile_shape_and_split(pkg, handle, which, bn, pair):
         handle.force_plan(-1, 0, 0)
 
 
+@pytest.mark.parametrize("bn,pair,members", [(256, 0, 2), (256, 0, 3), (256, 0, 8), (192, 0, 3), (128, 0, 4), (64, 0, 2),
+                                             (256, 1, 2), (256, 1, 3), (256, 1, 4), (128, 1, 4)])
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_cluster_split_through_distributed_shared_memory(pkg, handle, which, bn, pair, members):
+    """Every tile shared by a cluster whose members each take one range of the contraction and add
+    their partial sums up through distributed shared memory (no global-memory round trip)."""
+    g = torch.Generator(device=DEV).manual_seed(77)
+    dt = torch.bfloat16
+    try:
+        for (M, N, K) in [(512, 256, 512), (1000, 264, 520), (2048, 768, 768)]:
+            ins, outs = _shapes(which, M, N, K)
+            x = torch.randn(ins[0], device=DEV, generator=g).to(dt)
+            y = torch.randn(ins[1], device=DEV, generator=g).to(dt)
+            old = torch.randn(outs, device=DEV, generator=g).to(dt)
+            for beta in (0, 1):
+                handle.force_plan(bn, pair, -members)
+                got = _run(pkg, handle, which, beta, x, y, old, M, N, K)
+                want = _ref64(which, beta, x, y, old)
+                err = ((got.double() - want).abs().max() / want.abs().max()).item()
+                assert err <= 1e-2, (which, bn, pair, members, beta, M, N, K, err)
+                again = _run(pkg, handle, which, beta, x, y, old, M, N, K)
+                assert torch.equal(got, again)  # member order, not arrival order, fixes the sum
+    finally:
+        handle.force_plan(-1, 0, 0)
+
+
 def test_identity_weight_is_exact(pkg, handle):
     """B = I: forward returns A and dgrad returns dC bit for bit; A = I: wgrad returns dC + old."""
     dt = torch.bfloat16

@@ -35,15 +35,26 @@ def test_plan_invariants(pkg, which):
             assert p.dp_tiles % slots == 0     # only the ragged last wave is cut
             assert p.sk_items <= slots         # and its pieces fit one wave
         assert p.m_fastest in (0, 1)
+        if p.cluster_split > 1:
+            ctas = 2 if p.cta_pair else 1
+            assert p.splits == 1 and p.sk_items == 0
+            assert p.cluster_split * ctas <= 8           # portable cluster size
+            assert p.cluster_split <= p.bn // 32         # every member owns at least one column group
+            assert p.cluster_split <= kb
+            assert p.tiles * p.cluster_split * ctas <= 148  # one wave
 
 
 def test_small_weight_gradients_split_the_token_dimension(pkg):
     # dW of the 125M projections: the output alone gives far fewer tiles than SMs
     for N, K in ((768, 768), (256, 768), (2048, 768), (768, 2048)):
         p = pkg.plan_bf16(2, 1, 8192, N, K, 148)
-        assert p.splits > 1 and p.dp_tiles == 0
-        busy = p.sk_items * (2 if p.cta_pair else 1)
-        assert busy >= 74, (N, K, p.bn, p.cta_pair, p.splits)
+        ctas = 2 if p.cta_pair else 1
+        if p.cluster_split > 1:
+            busy = p.tiles * p.cluster_split * ctas
+            assert busy >= 48, (N, K, p.bn, p.cta_pair, p.cluster_split)
+        else:
+            assert p.splits > 1 and p.dp_tiles == 0
+            assert p.sk_items * ctas >= 74, (N, K, p.bn, p.cta_pair, p.splits)
 
 
 def test_unaligned_pitch_goes_to_cuda_core_kernel(pkg):
