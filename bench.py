@@ -258,13 +258,19 @@ def run_ours(args):
             if dominant is None or us > dominant["us"]:
                 dominant = dict(rec, flop=fl)
     h.sync()
+    h.set_stream(torch.cuda.current_stream())
+    in_step = None
+    if args.breakdown:
+        calls = [(b["name"] + ":fwd", (lambda b=b: pkg.matmul_forward(h, b["C"], b["A"], b["B"], TOKENS, b["N"], b["K"]))) for b in bufs]
+        calls += [(b["name"] + ":bwd", (lambda b=b: pkg.matmul_backward(h, b["dA"], b["dB"], b["dC"], b["A"], b["B"], TOKENS, b["N"], b["K"]))) for b in reversed(bufs)]
+        in_step = step_breakdown(torch, calls)
     peaks = measured_peaks()
     total_us = sum(r["us"] for r in per)
     roofline = {"bound": "tensor", "kernel": "gemm_bf16_sm100 (%s %s, M=8192)" % (dominant["proj"], dominant["gemm"]),
                 "achieved": round(dominant["flop"] / dominant["us"] / 1e6, 1), "peak": peaks["bf16_tflops"],
                 "unit": "TFLOP/s", "frac": round(dominant["flop"] / dominant["us"] / 1e6 / peaks["bf16_tflops"], 4),
                 "peak_source": peaks["source"] + " (burst: kernel timed alone)",
-                "share_of_step": round(dominant["us"] / total_us, 3), "traffic": None,
+                "share_of_step": round(dominant["us"] / total_us, 3), "traffic": ncu_traffic(dominant),
                 "step_frac_of_sustained": round(value / world / peaks["bf16_tflops_sustained"], 4)}
 
     cpu = cpu_baseline_port()
@@ -282,9 +288,42 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "what": "A and dC of every projection copied from pinned host memory, 24 GEMMs through the C ABI, every dA read back"},
             "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per}
+    if in_step:
+        line["in_step_us"] = in_step
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def ncu_traffic(rec):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the
+    committed ncu capture of its 2048-token case (profiles/gemm_bf16_sm100_lm_head_fwd_tokens2048.md:
+    130.4 MB for 183.0 MB of algorithmic bytes), scaled to the launch at hand by the algorithmic bytes
+    (traffic grows in proportion: every operand byte is read from DRAM once, the output written once)."""
+    if rec["proj"] != "lm_head" or rec["gemm"] != "fwd_nn":
+        return None
+    n, k = 32000, 768
+    algorithmic = 2.0 * (TOKENS * k + k * n + TOKENS * n)
+    return int(130.4e6 / 183.0e6 * algorithmic)
+
+
+def step_breakdown(torch, calls, steps=20):
+    """Device time of every call of the step, measured inside the running step (events between calls)."""
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(calls) + 1)] for _ in range(steps)]
+    for _, fn in calls:
+        fn()
+    torch.cuda.synchronize()
+    for s_ in range(steps):
+        ev[s_][0].record()
+        for i, (_, fn) in enumerate(calls):
+            fn()
+            ev[s_][i + 1].record()
+    torch.cuda.synchronize()
+    out = {}
+    for i, (name, _) in enumerate(calls):
+        out[name] = round(sum(ev[s_][i].elapsed_time(ev[s_][i + 1]) for s_ in range(steps)) / steps * 1e3, 2)
+    out["total"] = round(sum(out.values()), 2)
+    return out
 
 
 def cpu_baseline_port(seconds_hint=15.0):
@@ -386,6 +425,10 @@ def run_reference(args):
             us = e0.elapsed_time(e1) / 10 * 1e3
             fl = 2.0 * TOKENS * b["N"] * b["K"] * (1 if kind == "fwd_nn" else 2)
             per.append({"proj": b["name"], "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1)})
+    if args.breakdown:
+        calls = [(b["name"] + ":fwd", (lambda b=b: lib.ref_matmul_forward_bf16(hd, b["C"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"]))) for b in bufs]
+        calls += [(b["name"] + ":bwd", (lambda b=b: lib.ref_matmul_backward_bf16(hd, b["dA"].data_ptr(), b["dB"].data_ptr(), b["dC"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"]))) for b in reversed(bufs)]
+        base["in_step_us"] = step_breakdown(torch, calls)
     base.update({"value": round(value, 2), "dtype": "bf16", "ms_per_step": round(ms / args.steps, 4),
                  "config": {"workload": "configs[1]: decoder-layer projections (Q,K,V,O,gate,up,down) + LM head 768->32000, "
                                         "M=8192 tokens (B16xT512), fwd + dgrad + wgrad(beta=1), 24 GEMMs/step",
@@ -440,6 +483,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--breakdown", action="store_true", help="also time every call inside the running step")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -59,7 +59,8 @@ const char* b200_linear_strerror(int code);
 int b200_linear_forward_bf16(b200_linear_ctx* ctx, void* C, const void* A, const void* B, int M, int N,
                              int K);
 /* Replaces matmul_backward(handle, dA, dB, dC, A, B, M,N,K), cuda/matmul.cu:73-104, declared
- * cuda/kernels.cuh:350.  dA = bf16_rn(dC*B^T);  dB = bf16_rn(float(dB) + A^T*dC)  (beta = 1).
+ * cuda/kernels.cuh:350.  dA = bf16_rn(dC*B^T);  dB = bf16_rn(bf16_rn(A^T*dC) + float(dB))  (beta = 1,
+ * the product rounded to bf16 before the old gradient is added, exactly as the reference's cuBLAS does).
  * dA or dB may be NULL to skip that product. */
 int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* dB, const void* dC, const void* A,
                               const void* B, int M, int N, int K);

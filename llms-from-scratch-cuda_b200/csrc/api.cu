@@ -50,6 +50,10 @@ struct b200_linear_ctx {
     cudaStream_t stream = nullptr;
     float* ws = nullptr;  // split-K workspace
     size_t ws_bytes = 0;
+    float* ws2 = nullptr;  // second workspace + counters: for a kernel that overlaps the previous one
+    size_t ws2_bytes = 0;
+    int* sk_counters2 = nullptr;
+    int sk_counters2_len = 0;
     int* status_dev = nullptr;
     int* sk_counters = nullptr;     // arrival counters of split tiles (zero between launches)
     int sk_counters_len = 0;
@@ -61,6 +65,7 @@ struct b200_linear_ctx {
     int use_pdl = 1;
     int no_peer_split = 0;
     int one_producer = 0;
+    int overlap_backward = 1;
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
 };
@@ -104,14 +109,16 @@ int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64
     return B200_OK;
 }
 
-int ensure_workspace(b200_linear_ctx* ctx, size_t bytes) {
-    if (bytes <= ctx->ws_bytes) return B200_OK;
-    if (ctx->ws) CU_TRY(ctx, cudaFree(ctx->ws));
-    ctx->ws = nullptr;
-    ctx->ws_bytes = 0;
+int ensure_workspace(b200_linear_ctx* ctx, size_t bytes, int set = 0) {
+    float*& ws = set ? ctx->ws2 : ctx->ws;
+    size_t& have = set ? ctx->ws2_bytes : ctx->ws_bytes;
+    if (bytes <= have) return B200_OK;
+    if (ws) CU_TRY(ctx, cudaFree(ws));
+    ws = nullptr;
+    have = 0;
     size_t want = bytes + (bytes >> 2);
-    CU_TRY(ctx, cudaMalloc(&ctx->ws, want));
-    ctx->ws_bytes = want;
+    CU_TRY(ctx, cudaMalloc(&ws, want));
+    have = want;
     return B200_OK;
 }
 
@@ -296,15 +303,17 @@ int get_panel_map(b200_linear_ctx* ctx, const void* ptr, uint64_t rows, uint64_t
     return B200_OK;
 }
 
-int ensure_counters(b200_linear_ctx* ctx, int n) {
-    if (n <= ctx->sk_counters_len) return B200_OK;
-    if (ctx->sk_counters) CU_TRY(ctx, cudaFree(ctx->sk_counters));
-    ctx->sk_counters = nullptr;
-    ctx->sk_counters_len = 0;
+int ensure_counters(b200_linear_ctx* ctx, int n, int set = 0) {
+    int*& counters = set ? ctx->sk_counters2 : ctx->sk_counters;
+    int& have = set ? ctx->sk_counters2_len : ctx->sk_counters_len;
+    if (n <= have) return B200_OK;
+    if (counters) CU_TRY(ctx, cudaFree(counters));
+    counters = nullptr;
+    have = 0;
     const int want = n + 1024;
-    CU_TRY(ctx, cudaMalloc(&ctx->sk_counters, want * sizeof(int)));
-    CU_TRY(ctx, cudaMemset(ctx->sk_counters, 0, want * sizeof(int)));
-    ctx->sk_counters_len = want;
+    CU_TRY(ctx, cudaMalloc(&counters, want * sizeof(int)));
+    CU_TRY(ctx, cudaMemset(counters, 0, want * sizeof(int)));
+    have = want;
     return B200_OK;
 }
 
@@ -376,8 +385,13 @@ int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, 
                 int K);
 
 // One bf16 product on the tensor cores (or the CUDA-core kernel for TMA-unfriendly pitches).
+// overlap_prev = 1: the caller vouches that this product neither reads what the kernel launched just
+// before it on the stream writes, nor writes what that kernel touches (the weight gradient after the
+// input gradient of the same matmul_backward).  The kernel then starts on whatever SMs that kernel
+// has already left and only waits for it before it finishes itself, so that completion order, and with it
+// every later kernel's view of memory, stays what the stream promises.
 int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x, const void* y, int M,
-              int N, int K) {
+              int N, int K, int overlap_prev = 0) {
     if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2)
         return B200_E_BADARG;
     b200_linear_plan_t plan;
@@ -427,6 +441,7 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     gp.m_fastest = plan.m_fastest;
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
     gp.ksplit = ksplit;
+    gp.late_wait = (overlap_prev && ctx->use_pdl && ctx->overlap_backward) ? 1 : 0;
     gp.one_producer = ctx->one_producer;
     gp.out = out;
     gp.status = ctx->status_dev;
@@ -446,12 +461,13 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
             ws_bytes = static_cast<size_t>(d.tiles - d.dp_tiles) * ctas * d.sk_splits * (d.sk_splits - 1) * maxg *
                        (8 * BM * 4) * sizeof(float);
         }
-        rc = ensure_workspace(ctx, ws_bytes);
+        const int set = overlap_prev ? 1 : 0;  // never share scratch with a kernel that may still be running
+        rc = ensure_workspace(ctx, ws_bytes, set);
         if (rc) return rc;
-        rc = ensure_counters(ctx, (d.tiles - d.dp_tiles) * ctas);
+        rc = ensure_counters(ctx, (d.tiles - d.dp_tiles) * ctas, set);
         if (rc) return rc;
-        gp.ws = ctx->ws;
-        gp.sk_counters = ctx->sk_counters;
+        gp.ws = set ? ctx->ws2 : ctx->ws;
+        gp.sk_counters = set ? ctx->sk_counters2 : ctx->sk_counters;
     }
 
     // Operand P has Mo rows, operand Q has No rows; x,y map onto them per product.
@@ -574,6 +590,7 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     if (const char* e = getenv("B200_LINEAR_PDL")) ctx->use_pdl = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_PEER_SPLIT")) ctx->no_peer_split = atoi(e) == 0;
     if (const char* e = getenv("B200_LINEAR_ONE_PRODUCER")) ctx->one_producer = atoi(e) != 0;
+    if (const char* e = getenv("B200_LINEAR_OVERLAP_BACKWARD")) ctx->overlap_backward = atoi(e) != 0;
     if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
         delete ctx;
@@ -595,6 +612,8 @@ extern "C" int b200_linear_destroy(b200_linear_ctx* ctx) {
     cudaFree(ctx->ws);
     cudaFree(ctx->status_dev);
     if (ctx->sk_counters) cudaFree(ctx->sk_counters);
+    if (ctx->ws2) cudaFree(ctx->ws2);
+    if (ctx->sk_counters2) cudaFree(ctx->sk_counters2);
     if (ctx->prof_dev) cudaFree(ctx->prof_dev);
     delete ctx;
     return B200_OK;
@@ -615,6 +634,7 @@ extern "C" int b200_linear_sync(b200_linear_ctx* ctx, int* device_code) {
     if (code != 0) {
         CU_TRY(ctx, cudaMemset(ctx->status_dev, 0, sizeof(int)));
         if (ctx->sk_counters) CU_TRY(ctx, cudaMemset(ctx->sk_counters, 0, ctx->sk_counters_len * sizeof(int)));
+        if (ctx->sk_counters2) CU_TRY(ctx, cudaMemset(ctx->sk_counters2, 0, ctx->sk_counters2_len * sizeof(int)));
         return B200_E_DEVICE_WAIT;
     }
     return B200_OK;
@@ -721,7 +741,8 @@ extern "C" int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* d
         int rc = gemm_bf16(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K);
         if (rc) return rc;
     }
-    if (dB) return gemm_bf16(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K);
+    // dB does not depend on dA: let the second kernel fill the SMs the first one leaves
+    if (dB) return gemm_bf16(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K, dA ? 1 : 0);
     return B200_OK;
 }
 extern "C" int b200_linear_forward_f32(b200_linear_ctx* ctx, float* C, const float* A, const float* B, int M,
@@ -822,6 +843,7 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     gp.m_fastest = Mo <= No ? 1 : 0;
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
     gp.ksplit = 1;
+    gp.late_wait = 0;
     gp.sk_peer = 0;
     gp.one_producer = 0;
     gp.p_3d = (Mo % 64) == 0;

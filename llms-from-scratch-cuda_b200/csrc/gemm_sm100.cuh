@@ -50,6 +50,8 @@ struct GemmParams {
     int sk_items;            // (m_tiles*n_tiles - dp_tiles) * sk_splits
     int sk_peer;             // 1: the ranges of a split tile exchange partial sums among themselves (all resident
                              //    at once); 0: they park whole partial tiles and the last arriver adds them up
+    int late_wait;           // 1: independent of the previous kernel in the stream: run beside its tail and
+                             //    wait for it only before finishing (completion order stays stream order)
     int ksplit;              // > 1: a cluster of CTAS*ksplit CTAs shares each tile, every member takes one
                              // range of the contraction and the sum is formed through distributed smem
     int p_3d, q_3d;          // MN-major operand described by a 3-D map: one copy per stage
@@ -671,7 +673,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // Programmatic dependent launch: everything above overlapped the tail of the previous kernel
     // in the stream; its results (and its reads of our output buffers) are complete only after
     // this wait.  The next kernel may start its own set-up as soon as our CTAs make room.
-    griddep_wait();
+    if (!p.late_wait) griddep_wait();
     griddep_launch_dependents();
     if (threadIdx.x == 0) PROF_MARK(0);
 
@@ -915,6 +917,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
     }
+    // A kernel that ran beside its predecessor must not finish before it: whoever waits for this
+    // kernel next is entitled to see the predecessor's results as well.
+    if (p.late_wait && threadIdx.x == 0) griddep_wait();
 #ifdef B200_PROFILE
     if (threadIdx.x == 0) {
         unsigned long long g_end;

@@ -1,0 +1,26 @@
+"""The drop-in claim end to end: the reference's unmodified training program, relinked against this
+library (no cuBLAS), follows the reference build's loss curve on the README's overfit recipe."""
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_overfit_loss_curve_matches_reference_build():
+    from oracle import train_dropin
+    ref, ours = train_dropin.binaries()
+    if not ref or not ours:
+        pytest.skip("oracle/_ref/train_* not built (reference checkout absent at build time)")
+    res = train_dropin.overfit(steps=200, repeats_ref=2)
+    a, b = (r["losses"] for r in res["reference"])
+    o = res["b200"]["losses"]
+    assert res["b200"]["rc"] == 0 and all(r["rc"] == 0 for r in res["reference"]), res["b200"]["tail"]
+    assert set(o) == set(a) and 200 in o and 1 in o
+    for step in sorted(o):
+        ref_mid = 0.5 * (a[step] + b[step])
+        spread = abs(a[step] - b[step])  # the reference's own run-to-run spread (float atomics in its kernels)
+        if ref_mid > 0.05:
+            assert abs(o[step] - ref_mid) <= 0.01 * ref_mid + spread, (step, o[step], a[step], b[step])
+        else:
+            # the program prints four decimals: agree to that resolution
+            assert abs(o[step] - ref_mid) <= 2e-4 + spread, (step, o[step], a[step], b[step])
+    assert o[1] > 10.0 and o[200] <= 2e-4  # it starts at ln(32000) and it has overfitted by step 200
