@@ -474,6 +474,107 @@ def run_only(args):
                       "tflops": round(2.0 * M * n * k / us / 1e6, 1), "launches": h.launches}))
 
 
+SWEEP_M = [512, 2048, 8192, 16384, 65536]
+SWEEP_NK = [768, 1280, 2048, 4096, 8192, 32000, 128256]
+
+
+def run_sweep(args):
+    """Shape / layout / dtype / beta sweep (BASELINE.json configs[4]), this library and the reference's
+    cuBLAS build in the same process, every case timed as 5 launches captured in a CUDA graph.  The grid is
+    thinned to fit a time budget: cases are ordered by FLOPs and skipped (and listed) once the budget is
+    spent or when a case would need more than --sweep-gb of device memory."""
+    import ctypes
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    h = pkg.Handle()
+    side = torch.cuda.Stream()
+    h.set_stream(side)
+    ref = None
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_matmul.so")
+    if os.path.exists(path):
+        ref = ctypes.CDLL(path)
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        ref.ref_create.argtypes = [ctypes.POINTER(vp)]
+        ref.ref_create_fp32.argtypes = [ctypes.POINTER(vp)]
+        ref.ref_set_stream.argtypes = [vp, vp]
+        for n in ("ref_matmul_forward_bf16", "ref_matmul_forward_f32"):
+            getattr(ref, n).argtypes = [vp, vp, vp, vp, ci, ci, ci]
+            getattr(ref, n).restype = None
+        for n in ("ref_matmul_backward_bf16", "ref_matmul_backward_f32"):
+            getattr(ref, n).argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci]
+            getattr(ref, n).restype = None
+        hb, hf = vp(), vp()
+        ref.ref_create(ctypes.byref(hb))
+        ref.ref_create_fp32(ctypes.byref(hf))
+        ref.ref_set_stream(hb, vp(side.cuda_stream))
+        ref.ref_set_stream(hf, vp(side.cuda_stream))
+    peaks = measured_peaks()
+
+    def tgraph(fn, reps=5):
+        with torch.cuda.stream(side):
+            fn()
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(reps):
+                    fn()
+            g.replay()
+            side.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            g.replay()
+            e1.record(side)
+            side.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    cases = []
+    for M in SWEEP_M:
+        for N in SWEEP_NK:
+            for K in SWEEP_NK:
+                cases.append((2.0 * M * N * K, M, N, K))
+    cases.sort()
+    t_start = time.time()
+    skipped = []
+    for flop, M, N, K in cases:
+        for dt, sfx in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+            es = 2 if sfx == "bf16" else 4
+            gb = es * (M * K + K * N + M * N) * 2 / 1e9  # operands + outputs + gradients, roughly
+            if gb > args.sweep_gb or (sfx == "f32" and flop > args.sweep_f32_flop) or time.time() - t_start > args.sweep_seconds:
+                skipped.append([sfx, M, N, K])
+                continue
+            g = torch.Generator(device=dev).manual_seed(M + N + K)
+            A = torch.randn(M, K, device=dev, generator=g).to(dt)
+            B = torch.randn(K, N, device=dev, generator=g).to(dt)
+            dC = torch.randn(M, N, device=dev, generator=g).to(dt)
+            for which, name, x, y, shape in ((0, "NN", A, B, (M, N)), (1, "NT", dC, B, (M, K)), (2, "TN", A, dC, (K, N))):
+                for beta in (0, 1):
+                    out = torch.randn(shape, device=dev, generator=g).to(dt)
+                    us = tgraph(lambda: pkg.gemm(h, which, beta, out, x, y, M, N, K))
+                    rec = {"dtype": sfx, "layout": name, "beta": beta, "M": M, "N": N, "K": K, "us": round(us, 1),
+                           "tflops": round(flop / us / 1e6, 1)}
+                    if sfx == "bf16":
+                        rec["frac_of_measured_peak"] = round(flop / us / 1e6 / peaks["bf16_tflops"], 3)
+                    # the reference's API has no beta argument: forward = NN beta0, backward = NT beta0 + TN beta1
+                    if ref is not None and ((which == 0 and beta == 0) or (which == 1 and beta == 0)):
+                        hh = hb if sfx == "bf16" else hf
+                        if which == 0:
+                            fn = getattr(ref, "ref_matmul_forward_" + sfx)
+                            rus = tgraph(lambda: fn(hh, out.data_ptr(), A.data_ptr(), B.data_ptr(), M, N, K))
+                            rec["reference_us"] = round(rus, 1)
+                        else:
+                            fn = getattr(ref, "ref_matmul_backward_" + sfx)
+                            dB = torch.zeros(K, N, device=dev, dtype=dt)
+                            rus = tgraph(lambda: fn(hh, out.data_ptr(), dB.data_ptr(), dC.data_ptr(), A.data_ptr(), B.data_ptr(), M, N, K))
+                            rec["reference_backward_us (NT+TN)"] = round(rus, 1)
+                    print(json.dumps(rec), flush=True)
+            del A, B, dC
+    h.sync()
+    print(json.dumps({"skipped": skipped, "seconds": round(time.time() - t_start, 1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None, help="profile mode: <projection>:<fwd_nn|dgrad_nt|wgrad_tn>")
@@ -484,10 +585,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--breakdown", action="store_true", help="also time every call inside the running step")
+    ap.add_argument("--sweep", action="store_true", help="shape/layout/dtype/beta sweep against the reference's cuBLAS")
+    ap.add_argument("--sweep-seconds", type=float, default=240.0)
+    ap.add_argument("--sweep-gb", type=float, default=40.0)
+    ap.add_argument("--sweep-f32-flop", type=float, default=3e12)
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.only:
+    if args.sweep:
+        run_sweep(args)
+    elif args.only:
         run_only(args)
     elif args.impl == "reference":
         run_reference(args)
