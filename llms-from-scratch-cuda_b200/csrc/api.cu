@@ -13,6 +13,7 @@
 #include "../../include/b200_linear.h"
 #include "gemm_sm100.cuh"
 #include "gemm_simt.cuh"
+#include "gemm_tf32x3_sm100.cuh"
 
 using namespace b200;
 
@@ -66,6 +67,7 @@ struct b200_linear_ctx {
     int no_peer_split = 0;
     int one_producer = 0;
     int overlap_backward = 1;
+    int fp32_simt = 0;  // 1: fp32 products on the CUDA cores only (exact fp32 FMA arithmetic)
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
 };
@@ -99,6 +101,56 @@ int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64
     CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        ctx->last_cuda = 100000 + static_cast<int>(r);
+        return B200_E_CUDA;
+    }
+    if (ctx->tm_cache.size() > 8192) ctx->tm_cache.clear();
+    ctx->tm_cache.emplace(key, *out);
+    return B200_OK;
+}
+
+// fp32 2-D tensor map over a row-major [outer][inner] matrix, box {32 elements = 128 bytes, box_outer}.
+int get_tensor_map_f32(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_outer,
+                       CUtensorMap* out, bool atom32 = false) {
+    TmKey key{ptr, inner, outer, (atom32 ? 0x48000u : 0x40000u) + 32u, box_outer};
+    auto it = ctx->tm_cache.find(key);
+    if (it != ctx->tm_cache.end()) {
+        *out = it->second;
+        return B200_OK;
+    }
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * 4};
+    cuuint32_t box[2] = {32, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        ctx->last_cuda = 100000 + static_cast<int>(r);
+        return B200_E_CUDA;
+    }
+    if (ctx->tm_cache.size() > 8192) ctx->tm_cache.clear();
+    ctx->tm_cache.emplace(key, *out);
+    return B200_OK;
+}
+// fp32 MN-major operand [Kc][rows] (rows a multiple of 32) seen as {32 elements, Kc, rows/32 panels}.
+int get_panel_map_f32(b200_linear_ctx* ctx, const void* ptr, uint64_t rows, uint64_t kc, uint32_t panels,
+                      CUtensorMap* out) {
+    TmKey key{ptr, rows, kc, 0x50000u + panels, T32_BK};
+    auto it = ctx->tm_cache.find(key);
+    if (it != ctx->tm_cache.end()) {
+        *out = it->second;
+        return B200_OK;
+    }
+    cuuint64_t dims[3] = {32, kc, rows / 32};
+    cuuint64_t strides[2] = {rows * 4, 128};
+    cuuint32_t box[3] = {32, T32_BK, panels};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         ctx->last_cuda = 100000 + static_cast<int>(r);
@@ -567,6 +619,93 @@ int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, 
 
 }  // namespace
 
+namespace {
+
+template <int BN, bool P_MN, bool Q_MN, bool BETA1>
+int launch_tf32x3(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
+                  const GemmParams& gp, int grid) {
+    using Cfg = T32Cfg<BN>;
+    static bool configured = false;
+    auto kern = gemm_tf32x3_sm100<BN, P_MN, Q_MN, BETA1>;
+    if (!configured) {
+        CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(T32_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, gp));
+    ctx->launches++;
+    return B200_OK;
+}
+
+template <bool P_MN, bool Q_MN>
+int launch_tf32x3_variants(b200_linear_ctx* ctx, int bn, int beta1, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+                           const CUtensorMap& tmD, const GemmParams& gp, int grid) {
+    if (bn == 128)
+        return beta1 ? launch_tf32x3<128, P_MN, Q_MN, true>(ctx, tmP, tmQ, tmD, gp, grid)
+                     : launch_tf32x3<128, P_MN, Q_MN, false>(ctx, tmP, tmQ, tmD, gp, grid);
+    return beta1 ? launch_tf32x3<64, P_MN, Q_MN, true>(ctx, tmP, tmQ, tmD, gp, grid)
+                 : launch_tf32x3<64, P_MN, Q_MN, false>(ctx, tmP, tmQ, tmD, gp, grid);
+}
+
+// One fp32 product: on the tensor cores (3xTF32, fp32-grade accuracy) when TMA can describe the
+// operands, else on the CUDA cores.
+int gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x, const float* y, int M, int N,
+             int K) {
+    if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2) return B200_E_BADARG;
+    const bool aligned16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
+                             reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    if (ctx->fp32_simt || !aligned16 || (N % 4) != 0 || (K % 4) != 0)
+        return launch_simt<float>(ctx, which, beta1, out, x, y, M, N, K);
+    int Mo, No, Kc;
+    bool p_mn, q_mn;
+    if (which == B200_GEMM_FWD_NN) { Mo = M; No = N; Kc = K; p_mn = false; q_mn = true; }
+    else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
+    else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
+    const int bn = No > 64 ? 128 : 64;
+    GemmParams gp = {};
+    gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
+    gp.m_tiles = ceil_div_i(Mo, BM);
+    gp.n_tiles = ceil_div_i(No, bn);
+    gp.kb_total = ceil_div_i(Kc, T32_BK);
+    gp.m_fastest = Mo <= No ? 1 : 0;
+    const long long tiles = 1LL * gp.m_tiles * gp.n_tiles;
+    if (tiles > 0x7FFFFFFFLL) return B200_E_TOOBIG;
+    gp.dp_tiles = static_cast<int>(tiles);
+    gp.sk_splits = 1; gp.kb_per_sk = gp.kb_total; gp.sk_items = 0; gp.sk_peer = 0; gp.ksplit = 1; gp.late_wait = 0;
+    gp.one_producer = 0;
+    gp.out = out;
+    gp.status = ctx->status_dev;
+    gp.p_3d = p_mn && (Mo % 32) == 0;
+    gp.q_3d = q_mn && (No % 32) == 0;
+    CUtensorMap tmP, tmQ, tmD;
+    int rc;
+    if (gp.p_3d) rc = get_panel_map_f32(ctx, x, Mo, Kc, BM / 32, &tmP);
+    else if (p_mn) rc = get_tensor_map_f32(ctx, x, Mo, Kc, T32_BK, &tmP, true);
+    else rc = get_tensor_map_f32(ctx, x, Kc, Mo, BM, &tmP);
+    if (rc) return rc;
+    if (gp.q_3d) rc = get_panel_map_f32(ctx, y, No, Kc, bn / 32, &tmQ);
+    else if (q_mn) rc = get_tensor_map_f32(ctx, y, No, Kc, T32_BK, &tmQ, true);
+    else rc = get_tensor_map_f32(ctx, y, Kc, No, bn, &tmQ);
+    if (rc) return rc;
+    rc = get_tensor_map_f32(ctx, out, No, Mo, 32, &tmD);
+    if (rc) return rc;
+    const int grid = tiles < ctx->sm_count ? static_cast<int>(tiles) : ctx->sm_count;
+    if (p_mn) return launch_tf32x3_variants<true, true>(ctx, bn, beta1, tmP, tmQ, tmD, gp, grid);
+    if (q_mn) return launch_tf32x3_variants<false, true>(ctx, bn, beta1, tmP, tmQ, tmD, gp, grid);
+    return launch_tf32x3_variants<false, false>(ctx, bn, beta1, tmP, tmQ, tmD, gp, grid);
+}
+
+}  // namespace
+
 // ------------------------------------------------------------ C entry points
 extern "C" int b200_linear_create(b200_linear_ctx** out) {
     if (!out) return B200_E_BADARG;
@@ -591,6 +730,7 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     if (const char* e = getenv("B200_LINEAR_PEER_SPLIT")) ctx->no_peer_split = atoi(e) == 0;
     if (const char* e = getenv("B200_LINEAR_ONE_PRODUCER")) ctx->one_producer = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_OVERLAP_BACKWARD")) ctx->overlap_backward = atoi(e) != 0;
+    if (const char* e = getenv("B200_LINEAR_FP32_SIMT")) ctx->fp32_simt = atoi(e) != 0;
     if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
         delete ctx;
@@ -727,7 +867,7 @@ extern "C" int b200_linear_gemm_bf16(b200_linear_ctx* ctx, int which, int beta1,
 }
 extern "C" int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x,
                                     const float* y, int M, int N, int K) {
-    return launch_simt<float>(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K);
+    return gemm_f32(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K);
 }
 
 extern "C" int b200_linear_forward_bf16(b200_linear_ctx* ctx, void* C, const void* A, const void* B, int M,
@@ -747,16 +887,16 @@ extern "C" int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* d
 }
 extern "C" int b200_linear_forward_f32(b200_linear_ctx* ctx, float* C, const float* A, const float* B, int M,
                                        int N, int K) {
-    return launch_simt<float>(ctx, B200_GEMM_FWD_NN, 0, C, A, B, M, N, K);
+    return gemm_f32(ctx, B200_GEMM_FWD_NN, 0, C, A, B, M, N, K);
 }
 extern "C" int b200_linear_backward_f32(b200_linear_ctx* ctx, float* dA, float* dB, const float* dC,
                                         const float* A, const float* B, int M, int N, int K) {
     if (!dA && !dB) return B200_E_BADARG;
     if (dA) {
-        int rc = launch_simt<float>(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K);
+        int rc = gemm_f32(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K);
         if (rc) return rc;
     }
-    if (dB) return launch_simt<float>(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K);
+    if (dB) return gemm_f32(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K);
     return B200_OK;
 }
 

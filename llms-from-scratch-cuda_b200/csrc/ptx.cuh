@@ -281,12 +281,13 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
 //   bits 32-45 stride byte offset >> 4 bits 46-47 descriptor version (1 on sm_100)
 //   bits 61-63 layout type (2 = 128-byte swizzle)
+//              (1 = 128-byte swizzle in 32-byte units: the only layout for MN-major 32-bit operands)
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout_type = 2) {
     return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) |
            (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
            (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) |
-           (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+           (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(layout_type) << 61);
 }
 // Instruction descriptor, dense, fp32 accumulator.
 //   fmt: 0 = f16, 1 = bf16, 2 = tf32.  *_mn: 1 when the operand is MN-major in smem.
