@@ -95,6 +95,7 @@ typedef struct {
     int sk_items;
     int cluster_split;  /* > 1: every tile is shared by a cluster of this many CTAs (or CTA pairs), one
                            range of the contraction each, summed through distributed shared memory */
+    int est_ns;         /* the cost model's estimate of the kernel's duration on sm_count SMs, nanoseconds */
 } b200_linear_plan_t;
 int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
                           b200_linear_plan_t* plan);

@@ -70,6 +70,7 @@ struct b200_linear_ctx {
     int fp32_simt = 0;  // 1: fp32 products on the CUDA cores only (exact fp32 FMA arithmetic)
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
+    std::unordered_map<unsigned long long, int> backward_split;  // (M,N,K) -> SM shares of dgrad | wgrad
 };
 
 namespace {
@@ -297,6 +298,7 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
             plan->dp_tiles = d.dp_tiles;
             plan->sk_items = d.sk_items;
             plan->cluster_split = 0;
+            plan->est_ns = static_cast<int>(c);
             plan->waves_x100 = static_cast<int>(100LL * (d.dp_tiles + d.sk_items) / slots);
         }
         // Small outputs: every tile shared by a cluster whose members split the contraction and add
@@ -317,6 +319,7 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
                 plan->dp_tiles = d.tiles;
                 plan->sk_items = 0;
                 plan->cluster_split = ks;
+                plan->est_ns = static_cast<int>(cc);
                 plan->waves_x100 = static_cast<int>(100LL * d.tiles * ks / slots);
             }
             break;  // the largest admissible cluster is the candidate
@@ -436,6 +439,42 @@ template <typename T>
 int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, const T* y, int M, int N,
                 int K);
 
+// SM shares for the two independent kernels of one matmul_backward (0, 0 = one after the other on all SMs).
+void split_sms_for_backward(b200_linear_ctx* ctx, int M, int N, int K, int* sm_dgrad, int* sm_wgrad) {
+    *sm_dgrad = 0;
+    *sm_wgrad = 0;
+    if ((N % 8) != 0 || (K % 8) != 0) return;
+    const unsigned long long key = (static_cast<unsigned long long>(M) << 42) ^ (static_cast<unsigned long long>(N) << 21) ^
+                                   static_cast<unsigned long long>(K);
+    auto it = ctx->backward_split.find(key);
+    if (it != ctx->backward_split.end()) {
+        *sm_dgrad = it->second >> 16;
+        *sm_wgrad = it->second & 0xFFFF;
+        return;
+    }
+    b200_linear_plan_t pd, pw;
+    b200_linear_plan_bf16(B200_GEMM_DGRAD_NT, 0, M, N, K, ctx->sm_count, &pd);
+    b200_linear_plan_bf16(B200_GEMM_WGRAD_TN, 1, M, N, K, ctx->sm_count, &pw);
+    // one after the other: two set-ups and two tails are exposed (the estimates contain one each)
+    double best = static_cast<double>(pd.est_ns) + pw.est_ns + 2500.0;
+    int best_d = 0, best_w = 0;
+    for (int sd = 8; sd <= ctx->sm_count - 8; sd += 4) {
+        const int sw = (ctx->sm_count - sd) & ~1;
+        b200_linear_plan_bf16(B200_GEMM_DGRAD_NT, 0, M, N, K, sd, &pd);
+        b200_linear_plan_bf16(B200_GEMM_WGRAD_TN, 1, M, N, K, sw, &pw);
+        const double t = (pd.est_ns > pw.est_ns ? pd.est_ns : pw.est_ns) * 1.05;  // both feed from the same L2
+        if (t < best) {
+            best = t;
+            best_d = sd;
+            best_w = sw;
+        }
+    }
+    if (ctx->backward_split.size() > 4096) ctx->backward_split.clear();
+    ctx->backward_split.emplace(key, (best_d << 16) | best_w);
+    *sm_dgrad = best_d;
+    *sm_wgrad = best_w;
+}
+
 // One bf16 product on the tensor cores (or the CUDA-core kernel for TMA-unfriendly pitches).
 // overlap_prev = 1: the caller vouches that this product neither reads what the kernel launched just
 // before it on the stream writes, nor writes what that kernel touches (the weight gradient after the
@@ -443,11 +482,13 @@ int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, 
 // has already left and only waits for it before it finishes itself, so that completion order, and with it
 // every later kernel's view of memory, stays what the stream promises.
 int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x, const void* y, int M,
-              int N, int K, int overlap_prev = 0) {
+              int N, int K, int overlap_prev = 0, int sm_limit = 0) {
     if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2)
         return B200_E_BADARG;
+    // sm_limit > 0: plan for, and occupy, only that many SMs (a concurrent kernel has the others)
+    const int sm_count = (sm_limit > 0 && sm_limit < ctx->sm_count) ? sm_limit : ctx->sm_count;
     b200_linear_plan_t plan;
-    int rc = b200_linear_plan_bf16(which, beta1, M, N, K, ctx->sm_count, &plan);
+    int rc = b200_linear_plan_bf16(which, beta1, M, N, K, sm_count, &plan);
     if (rc) return rc;
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
                              reinterpret_cast<uintptr_t>(y)) & 15) == 0;
@@ -478,8 +519,8 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
         }
     }
     if (ksplit > 1) force_splits = 1;
-    if (ctx->sm_count < ctas) return B200_E_NODEVICE;
-    const int max_slots = ksplit > 1 ? 0x7FFFFFFF : ctx->sm_count / ctas;  // CTAs (or pairs) resident at once
+    if (sm_count < ctas) return B200_E_NODEVICE;
+    const int max_slots = ksplit > 1 ? 0x7FFFFFFF : sm_count / ctas;  // CTAs (or pairs) resident at once
     const Decomp d = decompose(Mo, No, Kc, bn, ctas, ksplit > 1 ? 1 : max_slots, force_splits);
     const long long items = static_cast<long long>(d.dp_tiles) + d.sk_items;
     if (items * ksplit * ctas > 0x7FFFFFFFLL || static_cast<long long>(d.tiles) * (d.sk_splits > 1 ? d.sk_splits : 1) > 0x7FFFFFFFLL)
@@ -839,13 +880,21 @@ extern "C" int b200_linear_debug_flags(b200_linear_ctx* ctx, int flags) {
 extern "C" int b200_linear_debug_prof(b200_linear_ctx* ctx, long long* out16) {
     if (!ctx || !out16) return B200_E_BADARG;
     if (!ctx->prof_dev) {
-        CU_TRY(ctx, cudaMalloc(&ctx->prof_dev, 32 * sizeof(long long)));
-        CU_TRY(ctx, cudaMemset(ctx->prof_dev, 0, 32 * sizeof(long long)));
+        CU_TRY(ctx, cudaMalloc(&ctx->prof_dev, (64 + 16 * 512) * sizeof(long long)));
+        CU_TRY(ctx, cudaMemset(ctx->prof_dev, 0, (64 + 16 * 512) * sizeof(long long)));
     }
     CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     CU_TRY(ctx, cudaMemcpy(out16, ctx->prof_dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost));
     CU_TRY(ctx, cudaMemset(ctx->prof_dev + 16, 0, 16 * sizeof(long long)));
     CU_TRY(ctx, cudaMemset(ctx->prof_dev + 20, 0xFF, sizeof(long long)));
+    return B200_OK;
+}
+// per-CTA timeline of the last launches: 16 global-timer stamps for each of the first 512 CTAs
+extern "C" int b200_linear_debug_timeline(b200_linear_ctx* ctx, long long* out, int clear) {
+    if (!ctx || !out || !ctx->prof_dev) return B200_E_BADARG;
+    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CU_TRY(ctx, cudaMemcpy(out, ctx->prof_dev + 64, 16 * 512 * sizeof(long long), cudaMemcpyDeviceToHost));
+    if (clear) CU_TRY(ctx, cudaMemset(ctx->prof_dev + 64, 0, 16 * 512 * sizeof(long long)));
     return B200_OK;
 }
 #endif
@@ -876,13 +925,20 @@ extern "C" int b200_linear_forward_bf16(b200_linear_ctx* ctx, void* C, const voi
 }
 extern "C" int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* dB, const void* dC,
                                          const void* A, const void* B, int M, int N, int K) {
-    if (!dA && !dB) return B200_E_BADARG;
+    if (!ctx || (!dA && !dB)) return B200_E_BADARG;
+    // dB does not depend on dA.  The two kernels therefore run side by side, each planned for its own
+    // share of the SMs (the split that the cost model says finishes soonest), unless running them one
+    // after the other on the whole GPU is estimated to be faster.  The second kernel starts as soon as
+    // the first one's CTAs are all resident and waits for the first only before it exits.
+    int sm_dgrad = 0, sm_wgrad = 0;
+    if (dA && dB && M > 0 && N > 0 && K > 0 && ctx->use_pdl && ctx->overlap_backward && ctx->force_bn <= 0 &&
+        ctx->sm_count >= 16)
+        split_sms_for_backward(ctx, M, N, K, &sm_dgrad, &sm_wgrad);
     if (dA) {
-        int rc = gemm_bf16(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K);
+        int rc = gemm_bf16(ctx, B200_GEMM_DGRAD_NT, 0, dA, dC, B, M, N, K, 0, sm_dgrad);
         if (rc) return rc;
     }
-    // dB does not depend on dA: let the second kernel fill the SMs the first one leaves
-    if (dB) return gemm_bf16(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K, dA ? 1 : 0);
+    if (dB) return gemm_bf16(ctx, B200_GEMM_WGRAD_TN, 1, dB, A, dC, M, N, K, dA ? 1 : 0, sm_wgrad);
     return B200_OK;
 }
 extern "C" int b200_linear_forward_f32(b200_linear_ctx* ctx, float* C, const float* A, const float* B, int M,

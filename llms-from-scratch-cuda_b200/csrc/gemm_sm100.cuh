@@ -66,7 +66,14 @@ struct GemmParams {
 
 #ifdef B200_PROFILE
 #define PROF_WRITE(idx, val) do { if (p.prof && blockIdx.x == 0) p.prof[idx] = (val); } while (0)
-#define PROF_MARK(idx) PROF_WRITE(idx, clock64() - t_kernel)
+__device__ __forceinline__ unsigned long long prof_globaltimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// per-CTA timeline in nanoseconds of the global timer: prof[64 + 16 * block + idx]
+#define PROF_MARK(idx) do { PROF_WRITE(idx, clock64() - t_kernel); \
+    if (p.prof && blockIdx.x < 512) p.prof[64 + 16 * blockIdx.x + (idx)] = (long long)prof_globaltimer(); } while (0)
 #define PROF_T(name) const long long name = clock64()
 #define PROF_MAX(idx, val) do { if (p.prof) atomicMax((unsigned long long*)&p.prof[idx], (unsigned long long)(val)); } while (0)
 #define DBG(bit) (p.dbg & (bit))
@@ -616,6 +623,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
 
 #ifdef B200_PROFILE
     const long long t_kernel = clock64();
+    if (threadIdx.x == 0) PROF_MARK(8);
     unsigned long long g_kernel;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_kernel));
     if (threadIdx.x == 0 && p.prof) {
@@ -685,6 +693,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             const bool do_p = warp == 0, do_q = one || warp == 3;
             uint32_t stage = 0, phase = 0;
             uint32_t issued = 0;  // number of stage fills issued so far
+#ifdef B200_PROFILE
+            long long tp_wait = 0, tp_issue = 0;
+#endif
             bool ok = true;
             WorkItem w;
             auto issue = [&](bool is_q, uint32_t dst, uint32_t bar, int r0, int c0) {
@@ -710,24 +721,37 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
                 const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
-                                   DEV_TIMEOUT_EMPTY)) {
+                    PROF_T(tp0);
+                    if (!(DBG(64) ? mbar_wait_spin(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
+                                                   DEV_TIMEOUT_EMPTY)
+                                  : mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
+                                              DEV_TIMEOUT_EMPTY))) {
                         ok = false;
                         break;
                     }
+                    PROF_T(tp1);
                     const uint32_t local_bar = smem_u32(&ctrl->full[stage]);
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
+                    // timing experiments: 8 = Q only on even blocks, 16 = P only on even blocks (stale data otherwise)
+                    const bool starve = DBG(32) && (kb & 7);  // 32 = both only on every eighth block
+                    const bool ld_p = do_p && !(DBG(16) && (kb & 1)) && !starve, ld_q = do_q && !(DBG(8) && (kb & 1)) && !starve;
                     if (rank == 0)
-                        mbar_arrive_expect_tx(local_bar, CTAS * ((do_p ? Cfg::A_BYTES : 0) + (do_q ? Cfg::B_BYTES : 0)));
+                        mbar_arrive_expect_tx(local_bar, CTAS * ((ld_p ? Cfg::A_BYTES : 0) + (ld_q ? Cfg::B_BYTES : 0)));
                     const int c0 = kb * BK;
-                    if (do_p) issue(false, sP, bar, m0, c0);
-                    if (do_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
+                    if (ld_p) issue(false, sP, bar, m0, c0);
+                    if (ld_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
                     if (issued == 0 && do_p) PROF_MARK(1);
+#ifdef B200_PROFILE
+                    if (do_p) { const long long tp2 = clock64(); tp_wait += tp1 - tp0; tp_issue += tp2 - tp1; }
+#endif
                     ++issued;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
+#ifdef B200_PROFILE
+            if (do_p) { PROF_WRITE(13, tp_wait); PROF_WRITE(14, tp_issue); }
+#endif
             if (!ok && rank == 0 && do_p) {
                 // Abort path: let every copy counted on this CTA's barriers land before exit.
                 const uint32_t n_back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
@@ -761,6 +785,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             const uint64_t descQ0 = umma_smem_desc(smem_u32(tiles) + Cfg::A_BYTES, Q_LBO, 1024);
             const uint16_t pair_mask = static_cast<uint16_t>(3u << leader);
             (void)pair_mask;
+#ifdef B200_PROFILE
+            long long tw_full = 0, tw_issue = 0, tw_commit = 0;
+#endif
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
@@ -772,12 +799,16 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status,
-                                   DEV_TIMEOUT_FULL)) {
+                    PROF_T(tq0);
+                    if (!(DBG(64) ? mbar_wait_spin(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status,
+                                                   DEV_TIMEOUT_FULL)
+                                  : mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status,
+                                              DEV_TIMEOUT_FULL))) {
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
+                    if (!DBG(128) || kb == w.kb0) tc_fence_after();
+                    PROF_T(tq1);
                     if (i == 0 && kb == w.kb0) PROF_MARK(2);
                     // only the 14-bit start-address field of a descriptor changes from stage to stage and
                     // from one UMMA_K step to the next: add to the low word
@@ -787,11 +818,27 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                         const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
                         const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
                         if (DBG(4) && k > 0) continue;
+                        if (DBG(512) && k > 1) continue;
                         umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
                     }
+                    PROF_T(tq2);
                     // frees the stage (in both CTAs of a pair) when the MMAs retire
+                    if (DBG(256)) {  // timing experiment: one commit point for every two stages
+                        if (((kb - w.kb0) & 1) || kb == w.kb1 - 1) {
+                            const uint32_t prev = stage == 0 ? STAGES - 1 : stage - 1;
+                            if ((kb - w.kb0) & 1) {
+                                if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[prev]), pair_mask);
+                                else umma_commit(smem_u32(&ctrl->empty[prev]));
+                            }
+                            if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
+                            else umma_commit(smem_u32(&ctrl->empty[stage]));
+                        }
+                    } else
                     if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
                     else umma_commit(smem_u32(&ctrl->empty[stage]));
+#ifdef B200_PROFILE
+                    { const long long tq3 = clock64(); tw_full += tq1 - tq0; tw_issue += tq2 - tq1; tw_commit += tq3 - tq2; }
+#endif
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) {
@@ -801,6 +848,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             }
             PROF_MARK(3);
             PROF_MAX(22, clock64() - t_kernel);
+#ifdef B200_PROFILE
+            PROF_WRITE(10, tw_full); PROF_WRITE(11, tw_issue); PROF_WRITE(12, tw_commit);
+#endif
         }
     } else if (warp >= 4) {
         // ---------------------------------------------------------- epilogue
@@ -812,6 +862,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         WorkItem w;
         for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
             const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
+            if (DBG(1024) && lane == 0) {  // timing experiment: sleep between probes
+                for (int it = 0; it < 2000000 && !mbar_test_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase); ++it)
+                    __nanosleep(500);
+            }
             if (lane == 0)
                 ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __shfl_sync(0xffffffffu, ok, 0);

@@ -33,7 +33,8 @@ class LinearError(RuntimeError):
 class Plan(ctypes.Structure):
     _fields_ = [("bn", ctypes.c_int), ("cta_pair", ctypes.c_int), ("splits", ctypes.c_int),
                 ("m_fastest", ctypes.c_int), ("tiles", ctypes.c_int), ("waves_x100", ctypes.c_int),
-                ("dp_tiles", ctypes.c_int), ("sk_items", ctypes.c_int), ("cluster_split", ctypes.c_int)]
+                ("dp_tiles", ctypes.c_int), ("sk_items", ctypes.c_int), ("cluster_split", ctypes.c_int),
+                ("est_ns", ctypes.c_int)]
 
 
 def _load():
