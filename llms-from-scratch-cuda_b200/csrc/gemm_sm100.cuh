@@ -26,6 +26,7 @@
 // in a fixed order (so results do not depend on arrival order), applies beta and writes the
 // tile.  Nobody waits for anybody: only the last arriver does the reduction.
 #pragma once
+#include <cstddef>
 #include <cuda_bf16.h>
 #include "ptx.cuh"
 
@@ -242,7 +243,7 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
         }
         if constexpr (BETA1) {
             // the warp's previous store must have finished reading the staging buffer
-            if (lane == 0) {
+            if (elect_one()) {
                 tma_store_wait_read<0>();
                 mbar_arrive_expect_tx(old_bar, EPI_BUF_BYTES);
                 tma_load_2d(smem_u32(buf), tmD, old_bar, col0, row0);  // rows/cols beyond the matrix read as 0
@@ -272,14 +273,13 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
             tmem_ld_wait();
         }
         if constexpr (BETA1) {
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            bool ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) return false;
             old_phase ^= 1;
         } else {
             // the warp's previous store must have finished reading the staging buffer
-            if (lane == 0) tma_store_wait_read<0>();
+            if (elect_one()) tma_store_wait_read<0>();
             __syncwarp();
         }
 #pragma unroll
@@ -305,7 +305,7 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && row0 < p.Mo && !DBG(2)) {
+        if (row0 < p.Mo && elect_one()) {
             tma_store_2d(tmD, smem_u32(buf), col0, row0);
             tma_store_commit();
         }
@@ -319,7 +319,7 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
 template <bool BETA1>
 __device__ __forceinline__ void block32_begin(const CUtensorMap* tmD32, uint8_t* buf, uint32_t old_bar, int col0,
                                               int row0, int lane) {
-    if (lane == 0) {
+    if (elect_one()) {
         tma_store_wait_read<0>();  // the previous store of this warp has finished reading the buffer
         if constexpr (BETA1) {
             mbar_arrive_expect_tx(old_bar, 32 * 64);
@@ -332,9 +332,8 @@ __device__ __forceinline__ bool block32_finish(const GemmParams& p, const CUtens
                                                const float (&acc)[32], uint32_t old_bar, uint32_t& old_phase,
                                                int col0, int row0, int lane, volatile int* abort_flag) {
     if constexpr (BETA1) {
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        bool ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) return false;
         old_phase ^= 1;
     } else {
@@ -362,7 +361,7 @@ __device__ __forceinline__ bool block32_finish(const GemmParams& p, const CUtens
     }
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0 && row0 < p.Mo) {
+    if (row0 < p.Mo && elect_one()) {
         tma_store_2d(tmD32, smem_u32(buf), col0, row0);
         tma_store_commit();
     }
@@ -398,9 +397,8 @@ __device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, Gemm
         for (int d = 0; d < S; ++d)
             if (d != krank) mbar_arrive_cluster(smem_u32(&ctrl->ml_done), static_cast<uint32_t>(d * CTAS + rank));
     }
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait<true>(smem_u32(&ctrl->ml_done), 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    bool ok = mbar_wait<true>(smem_u32(&ctrl->ml_done), 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
+    ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
 
     PROF_T(tc1);
@@ -427,8 +425,8 @@ __device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, Gemm
 
     PROF_T(tc2);
     // receive, then sum my own column groups in member order
-    if (lane == 0) ok = mbar_wait<true>(recv_bar, 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = mbar_wait<true>(recv_bar, 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
+    ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
     PROF_T(tc3);
     // The output goes out in 32 x 32 blocks through the warp's staging buffer (64-byte swizzle) and
@@ -534,9 +532,8 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
         ctrl->sk_last = seen >= S;
         mbar_arrive(smem_u32(&ctrl->sk_decided));
     }
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait(smem_u32(&ctrl->sk_decided), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER);
-    ok = __shfl_sync(0xffffffffu, ok, 0) && ctrl->sk_last;
+    bool ok = mbar_wait(smem_u32(&ctrl->sk_decided), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER);
+    ok = __all_sync(0xffffffffu, ok) && ctrl->sk_last;
     if (!ok) return false;
     __threadfence();
     PROF_T(tc2);
@@ -631,7 +628,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         atomicMax((unsigned long long*)&p.prof[21], g_kernel);
     }
 #endif
-    const int warp = threadIdx.x >> 5;
+    // read through a shuffle so that the compiler treats the warp index (and everything derived from
+    // it: the role, the TMEM lane quarter, the staging buffer) as uniform across the warp
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
     const uint32_t ctarank = cluster_ctarank();          // 0 when launched without a cluster
     const uint32_t rank = ctarank % CTAS;                // position in the CTA pair
@@ -641,23 +640,23 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     const int slot = blockIdx.x / cluster_ctas, nslots = gridDim.x / cluster_ctas;
     const bool clustered = PAIR || p.ksplit > 1;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->full[s]), p.one_producer ? 1 : 2);  // one arrival (+ byte count) per producer thread
-            mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    if (warp == 1) {
+        // the barriers are consecutive 8-byte words at the start of the control block: one lane each
+        constexpr int N_BARS = 16 + 4 + 3 + EPI_WARPS + 2;
+        static_assert(offsetof(GemmCtrl, cs_recv) == (N_BARS - 1) * 8, "barrier list and control block disagree");
+        for (int b = lane; b < N_BARS; b += 32) {
+            uint32_t count = 1;  // empty[], tmem_full[], sk_decided, old_bar[], cs_recv
+            if (b < 8) count = p.one_producer ? 1 : 2;  // full[]: one arrival (+ byte count) per producer warp
+            else if (b >= 16 && b < 18) count = 1;
+            else if (b >= 18 && b < 20) count = EPI_WARPS * CTAS;         // tmem_empty[]
+            else if (b == 20 || b == 22) count = EPI_WARPS;                // sk_written, sk_read
+            else if (b == N_BARS - 2) count = p.ksplit > 1 ? p.ksplit - 1 : 1;  // ml_done
+            mbar_init(smem_u32(&ctrl->full[0]) + 8u * b, count);
         }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
-            mbar_init(smem_u32(&ctrl->tmem_empty[a]), EPI_WARPS * CTAS);
+        if (lane == 0) {
+            ctrl->abort_flag = 0;
+            ctrl->sk_last = 0;
         }
-        mbar_init(smem_u32(&ctrl->sk_written), EPI_WARPS);
-        mbar_init(smem_u32(&ctrl->sk_decided), 1);
-        mbar_init(smem_u32(&ctrl->sk_read), EPI_WARPS);
-        for (int w8 = 0; w8 < EPI_WARPS; ++w8) mbar_init(smem_u32(&ctrl->old_bar[w8]), 1);
-        mbar_init(smem_u32(&ctrl->ml_done), p.ksplit > 1 ? p.ksplit - 1 : 1);
-        mbar_init(smem_u32(&ctrl->cs_recv), 1);
-        ctrl->abort_flag = 0;
-        ctrl->sk_last = 0;
         fence_mbar_init();
     }
     if (warp == 0 && lane == 0) {
@@ -681,21 +680,23 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // Programmatic dependent launch: everything above overlapped the tail of the previous kernel
     // in the stream; its results (and its reads of our output buffers) are complete only after
     // this wait.  The next kernel may start its own set-up as soon as our CTAs make room.
-    if (!p.late_wait) griddep_wait();
+    // Only the warps that touch global memory wait, each as late as it can: the producers just before
+    // their first copy (after the first work item's coordinates are known), the epilogue warps on entry
+    // (they have nothing to do until the first accumulator is complete).
     griddep_launch_dependents();
-    if (threadIdx.x == 0) PROF_MARK(0);
 
+    // The three issuing roles below run with all 32 lanes of their warp converged: every lane waits on the
+    // barriers and does the (warp-uniform) address arithmetic, and one elected lane issues the copies, the
+    // MMAs and the commits.  Their operands then sit in uniform registers; the same loops run by a single
+    // lane inside a divergent branch cost several hundred cycles per 64-deep block just to issue.
     if (warp == 0 || warp == 3) {
         // ---------------------------------------------- TMA producers: warp 0 feeds P, warp 3 feeds Q
         // (with p.one_producer, warp 0 feeds both and warp 3 idles)
         const bool one = p.one_producer != 0;
-        if (lane == 0 && !(one && warp == 3)) {
+        if (!(one && warp == 3)) {
             const bool do_p = warp == 0, do_q = one || warp == 3;
             uint32_t stage = 0, phase = 0;
             uint32_t issued = 0;  // number of stage fills issued so far
-#ifdef B200_PROFILE
-            long long tp_wait = 0, tp_issue = 0;
-#endif
             bool ok = true;
             WorkItem w;
             auto issue = [&](bool is_q, uint32_t dst, uint32_t bar, int r0, int c0) {
@@ -716,43 +717,50 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     }
                 }
             };
+            // The state of the next stage's barrier is probed one iteration ahead, so that the probe's
+            // latency overlaps the issue of the current stage's copies.
+            bool ready = mbar_test_wait(smem_u32(&ctrl->empty[0]), 1);
+            bool waited = false;
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
                 const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    PROF_T(tp0);
-                    if (!(DBG(64) ? mbar_wait_spin(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
-                                                   DEV_TIMEOUT_EMPTY)
-                                  : mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
-                                              DEV_TIMEOUT_EMPTY))) {
-                        ok = false;
-                        break;
+                    if (!__all_sync(0xffffffffu, ready)) {
+                        ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
+                                       DEV_TIMEOUT_EMPTY);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
                     }
-                    PROF_T(tp1);
+                    const uint32_t next_stage = stage + 1 == STAGES ? 0 : stage + 1;
+                    const uint32_t next_phase = next_stage == 0 ? phase ^ 1 : phase;
+                    ready = mbar_test_wait(smem_u32(&ctrl->empty[next_stage]), next_phase ^ 1);
                     const uint32_t local_bar = smem_u32(&ctrl->full[stage]);
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
-                    // timing experiments: 8 = Q only on even blocks, 16 = P only on even blocks (stale data otherwise)
-                    const bool starve = DBG(32) && (kb & 7);  // 32 = both only on every eighth block
-                    const bool ld_p = do_p && !(DBG(16) && (kb & 1)) && !starve, ld_q = do_q && !(DBG(8) && (kb & 1)) && !starve;
-                    if (rank == 0)
-                        mbar_arrive_expect_tx(local_bar, CTAS * ((ld_p ? Cfg::A_BYTES : 0) + (ld_q ? Cfg::B_BYTES : 0)));
+                    const bool starve = DBG(32) && (kb & 7);  // timing experiment: copies only on every eighth block
+                    const bool ld_p = do_p && !starve, ld_q = do_q && !starve;
                     const int c0 = kb * BK;
-                    if (ld_p) issue(false, sP, bar, m0, c0);
-                    if (ld_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
-                    if (issued == 0 && do_p) PROF_MARK(1);
-#ifdef B200_PROFILE
-                    if (do_p) { const long long tp2 = clock64(); tp_wait += tp1 - tp0; tp_issue += tp2 - tp1; }
-#endif
+                    if (!waited) {
+                        if (!p.late_wait) griddep_wait();
+                        waited = true;
+                        if (lane == 0 && do_p) PROF_MARK(0);
+                    }
+                    if (elect_one()) {
+                        if (rank == 0)
+                            mbar_arrive_expect_tx(local_bar,
+                                                  CTAS * ((ld_p ? Cfg::A_BYTES : 0) + (ld_q ? Cfg::B_BYTES : 0)));
+                        if (ld_p) issue(false, sP, bar, m0, c0);
+                        if (ld_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
+                        if (issued == 0 && do_p) PROF_MARK(1);
+                    }
+                    __syncwarp();
                     ++issued;
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    stage = next_stage;
+                    phase = next_phase;
                 }
             }
-#ifdef B200_PROFILE
-            if (do_p) { PROF_WRITE(13, tp_wait); PROF_WRITE(14, tp_issue); }
-#endif
-            if (!ok && rank == 0 && do_p) {
+            if (!ok && rank == 0 && do_p && lane == 0) {
                 // Abort path: let every copy counted on this CTA's barriers land before exit.
                 const uint32_t n_back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
                 uint32_t s2 = stage, ph = phase;
@@ -770,8 +778,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             }
         }
     } else if (warp == 1) {
-        // -------------------------------------------------------- MMA issuer
-        if (lane == 0 && rank == 0) {
+        // -------------------------------------------------------- MMA issuer (the even CTA of a pair)
+        if (rank == 0) {
             constexpr uint32_t idesc = umma_idesc(1, BM * CTAS, BN, P_MN ? 1 : 0, Q_MN ? 1 : 0);
             // K-major tile: rows of 128 B, 8-row groups 1024 B apart; +32 B per UMMA_K step.
             // MN-major tile: 64-wide column panels of BK rows x 128 B (LBO = panel pitch),
@@ -785,75 +793,74 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             const uint64_t descQ0 = umma_smem_desc(smem_u32(tiles) + Cfg::A_BYTES, Q_LBO, 1024);
             const uint16_t pair_mask = static_cast<uint16_t>(3u << leader);
             (void)pair_mask;
+            // as in the producers: the next stage's barrier is probed while this stage's MMAs are issued
+            bool ready = mbar_test_wait(smem_u32(&ctrl->full[0]), 0);
 #ifdef B200_PROFILE
-            long long tw_full = 0, tw_issue = 0, tw_commit = 0;
+            long long tw[5] = {0, 0, 0, 0, 0}, tq_prev = clock64();
 #endif
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
-                if (!mbar_wait<PAIR>(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
-                                     DEV_TIMEOUT_TMEM_E)) {
-                    ok = false;
-                    break;
-                }
+                ok = mbar_wait<PAIR>(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
+                                     DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     PROF_T(tq0);
-                    if (!(DBG(64) ? mbar_wait_spin(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status,
-                                                   DEV_TIMEOUT_FULL)
-                                  : mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status,
-                                              DEV_TIMEOUT_FULL))) {
-                        ok = false;
-                        break;
+                    if (!__all_sync(0xffffffffu, ready)) {
+                        ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
                     }
-                    if (!DBG(128) || kb == w.kb0) tc_fence_after();
+                    tc_fence_after();
+                    const uint32_t next_stage = stage + 1 == STAGES ? 0 : stage + 1;
+                    const uint32_t next_phase = next_stage == 0 ? phase ^ 1 : phase;
                     PROF_T(tq1);
-                    if (i == 0 && kb == w.kb0) PROF_MARK(2);
+                    ready = mbar_test_wait(smem_u32(&ctrl->full[next_stage]), next_phase);
+                    PROF_T(tq2);
                     // only the 14-bit start-address field of a descriptor changes from stage to stage and
                     // from one UMMA_K step to the next: add to the low word
                     const uint32_t st_off = (stage * Cfg::STAGE_BYTES) >> 4;
+                    if (elect_one()) {
+                        if (i == 0 && kb == w.kb0) PROF_MARK(2);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
-                        const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
-                        if (DBG(4) && k > 0) continue;
-                        if (DBG(512) && k > 1) continue;
-                        umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
-                    }
-                    PROF_T(tq2);
-                    // frees the stage (in both CTAs of a pair) when the MMAs retire
-                    if (DBG(256)) {  // timing experiment: one commit point for every two stages
-                        if (((kb - w.kb0) & 1) || kb == w.kb1 - 1) {
-                            const uint32_t prev = stage == 0 ? STAGES - 1 : stage - 1;
-                            if ((kb - w.kb0) & 1) {
-                                if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[prev]), pair_mask);
-                                else umma_commit(smem_u32(&ctrl->empty[prev]));
-                            }
-                            if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
-                            else umma_commit(smem_u32(&ctrl->empty[stage]));
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
+                            const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
+                            if (DBG(4) && k > 0) continue;  // timing experiment: a quarter of the MMAs
+                            umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
                         }
-                    } else
-                    if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
-                    else umma_commit(smem_u32(&ctrl->empty[stage]));
+                        PROF_T(tq3);
+                        // frees the stage (in both CTAs of a pair) when the MMAs retire
+                        if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
+                        else umma_commit(smem_u32(&ctrl->empty[stage]));
 #ifdef B200_PROFILE
-                    { const long long tq3 = clock64(); tw_full += tq1 - tq0; tw_issue += tq2 - tq1; tw_commit += tq3 - tq2; }
+                        { const long long tq4 = clock64(); tw[0] += tq1 - tq0; tw[1] += tq2 - tq1; tw[2] += tq3 - tq2; tw[3] += tq4 - tq3; tw[4] += tq0 - tq_prev; tq_prev = tq4; }
 #endif
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                }
-                if (ok) {
-                    if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->tmem_full[acc]), pair_mask);
-                    else umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+                        // the accumulator is complete when the last block's MMAs retire
+                        if (kb == w.kb1 - 1) {
+                            if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->tmem_full[acc]), pair_mask);
+                            else umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+                        }
+                    }
+                    __syncwarp();
+                    stage = next_stage;
+                    phase = next_phase;
                 }
             }
-            PROF_MARK(3);
-            PROF_MAX(22, clock64() - t_kernel);
 #ifdef B200_PROFILE
-            PROF_WRITE(10, tw_full); PROF_WRITE(11, tw_issue); PROF_WRITE(12, tw_commit);
+            if (elect_one()) for (int j = 0; j < 5; ++j) PROF_WRITE(24 + j, tw[j]);
 #endif
+            if (lane == 0) {
+                PROF_MARK(3);
+                PROF_MAX(22, clock64() - t_kernel);
+            }
         }
     } else if (warp >= 4) {
         // ---------------------------------------------------------- epilogue
+        if (!p.late_wait) griddep_wait();
         const int q = warp & 3;            // TMEM lane quarter
         const int hsel = (warp - 4) >> 2;  // which half of the column chunks
         uint32_t sk_phase = 0, old_phase = 0;
@@ -866,9 +873,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 for (int it = 0; it < 2000000 && !mbar_test_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase); ++it)
                     __nanosleep(500);
             }
-            if (lane == 0)
-                ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             if (warp == 4 && lane == 0) PROF_MARK(4);  // last item's accumulator ready
@@ -878,7 +884,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             auto release_acc = [&]() {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) {
+                if (elect_one()) {
                     if constexpr (PAIR) mbar_arrive_cluster(smem_u32(&ctrl->tmem_empty[acc]), leader);
                     else mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
                 }
@@ -930,9 +936,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     }
                     mbar_arrive(smem_u32(&ctrl->sk_decided));
                 }
-                if (lane == 0)
-                    ok = mbar_wait(smem_u32(&ctrl->sk_decided), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+                ok = mbar_wait(smem_u32(&ctrl->sk_decided), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 sk_phase ^= 1;
                 PROF_T(ts3);
@@ -955,7 +960,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         }
         // every TMA store of this warp must have read its staging buffer and landed before exit
         if (warp == 4 && lane == 0) PROF_MARK(5);
-        if (lane == 0) tma_store_wait_all<0>();
+        if (elect_one()) tma_store_wait_all<0>();
         if (warp == 4 && lane == 0) PROF_MARK(6);
     }
 
