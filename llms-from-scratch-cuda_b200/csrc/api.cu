@@ -67,6 +67,7 @@ struct b200_linear_ctx {
     int no_peer_split = 0;
     int one_producer = 0;
     int overlap_backward = 1;
+    int partition_backward = 1;  // 0: dgrad and wgrad both plan for the whole GPU (wgrad still fills dgrad's tail)
     int fp32_simt = 0;  // 1: fp32 products on the CUDA cores only (exact fp32 FMA arithmetic)
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
@@ -229,29 +230,55 @@ Decomp decompose(int Mo, int No, int Kc, int bn, int ctas, int slots, int force_
     return d;
 }
 
-// Main-loop cost of one BK = 64 block of one work item, in nanoseconds: measured averages on a
-// B200 (graph replay, SM clock ~1.75 GHz).  Every configuration is bound by the L2 -> SM feed
-// (about 60 B/clk/SM without multicast), which is why 256-wide CTA-pair tiles, with the most
-// reuse per byte fetched, are the cheapest per FLOP.
-double per_block_ns(int bn, int ctas) {
-    if (ctas == 2) return bn == 256 ? 335.0 : 300.0;
-    return bn == 256 ? 400.0 : bn == 192 ? 335.0 : bn == 128 ? 255.0 : 200.0;
+// Main-loop cost of one BK = 64 block of one work item, in nanoseconds, measured on a B200 (graph replay,
+// SM clock ~1.85 GHz), the same for the three operand layouts.  `lo`: a few CTAs alone on the GPU -- the
+// issue loop's floor of ~480 cycles per block, or the tensor pipe for the 256-wide pair tile.  `hi`: all
+// 148 SMs busy, where the shared L2 -> SM feed adds to it.  In between, by the busy fraction of the SMs.
+double per_block_ns(int bn, int ctas, double busy) {
+    double lo, hi;
+    if (ctas == 2) {
+        lo = bn == 256 ? 275.0 : 256.0;
+        hi = bn == 256 ? 386.0 : 256.0;
+    } else {
+        lo = bn == 256 ? 275.0 : 256.0;
+        hi = bn == 256 ? 480.0 : bn == 192 ? 430.0 : bn == 128 ? 320.0 : 260.0;  // slowest GPUs seen, not the average
+    }
+    if (busy > 1.0) busy = 1.0;
+    return lo + (hi - lo) * busy;
+}
+
+// Cost outside the main loops: launch gap, set-up, first copies' latency, tear-down (a CTA pair also
+// waits for its cluster to be scheduled, the longer the fuller the GPU, and synchronises it twice), and
+// the last, exposed epilogue.
+double fixed_ns(int bn, int ctas, double busy) {
+    if (busy > 1.0) busy = 1.0;
+    return 2560.0 + (ctas == 2 ? 1840.0 * busy : 0.0) + 600.0 + 4.0 * bn;
 }
 
 // Estimated duration in nanoseconds of the persistent schedule described by `d`.
 double plan_cost_ns(const Decomp& d, int bn, int ctas, int slots) {
-    const double per_kb = per_block_ns(bn, ctas);
+    const long long items = static_cast<long long>(d.dp_tiles) + d.sk_items;
+    const double busy = static_cast<double>(items < slots ? items : slots) / slots;
+    const double per_kb = per_block_ns(bn, ctas, busy);
     const int dp_rounds = (d.dp_tiles + slots - 1) / slots;
     const int sk_rounds = (d.sk_items + slots - 1) / slots;
     double t = (static_cast<double>(dp_rounds) * d.kb_total + static_cast<double>(sk_rounds) * d.kb_per_sk) * per_kb;
     t += 300.0 * (dp_rounds + sk_rounds);  // pipeline refill at item boundaries
-    t += 600.0 + 4.0 * bn;                 // the last epilogue is exposed
+    t += fixed_ns(bn, ctas, busy);
     if (d.sk_items > 0) {
         // partial sums through L2: peers exchanging slices (all resident) or a last arriver adding whole tiles
         const bool peer = d.sk_items <= slots && d.sk_splits <= bn / 32;
-        t += peer ? 5000.0 : 6000.0 + 1500.0 * d.sk_splits;
+        t += peer ? 5000.0 + 750.0 * d.sk_splits : 6000.0 + 1500.0 * d.sk_splits;
     }
     return t;
+}
+
+// Same for a cluster split: every tile shared by `ks` CTAs (or pairs) that add up through distributed
+// shared memory; the exchange costs about a microsecond per member.
+double cluster_split_cost_ns(int tiles, int kb_total, int ks, int bn, int ctas, int sm_count) {
+    const int per = ceil_div_i(kb_total, ks);
+    const double busy = static_cast<double>(tiles) * ks * ctas / sm_count;
+    return per * per_block_ns(bn, ctas, busy) + 300.0 + fixed_ns(bn, ctas, busy) + 1500.0 + 1000.0 * ks;
 }
 
 // Clusters of `size` CTAs (one CTA per SM) that can be resident at once, measured on a 148-SM B200
@@ -309,7 +336,7 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
             if (d.tiles > max_resident_clusters(ks * ctas, sm_count)) continue;
             const int per = ceil_div_i(kb_total, ks);
             if (ceil_div_i(kb_total, per) != ks) continue;
-            const double cc = per * per_block_ns(bn, ctas) + 300.0 + 600.0 + 4.0 * bn + 3500.0;
+            const double cc = cluster_split_cost_ns(d.tiles, kb_total, ks, bn, ctas, sm_count);
             if (cc < best) {
                 best = cc;
                 plan->bn = bn;
@@ -322,7 +349,6 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
                 plan->est_ns = static_cast<int>(cc);
                 plan->waves_x100 = static_cast<int>(100LL * d.tiles * ks / slots);
             }
-            break;  // the largest admissible cluster is the candidate
         }
     }
     plan->m_fastest = Mo <= No ? 1 : 0;
@@ -771,6 +797,7 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     if (const char* e = getenv("B200_LINEAR_PEER_SPLIT")) ctx->no_peer_split = atoi(e) == 0;
     if (const char* e = getenv("B200_LINEAR_ONE_PRODUCER")) ctx->one_producer = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_OVERLAP_BACKWARD")) ctx->overlap_backward = atoi(e) != 0;
+    if (const char* e = getenv("B200_LINEAR_PARTITION_BACKWARD")) ctx->partition_backward = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_FP32_SIMT")) ctx->fp32_simt = atoi(e) != 0;
     if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
@@ -931,7 +958,7 @@ extern "C" int b200_linear_backward_bf16(b200_linear_ctx* ctx, void* dA, void* d
     // after the other on the whole GPU is estimated to be faster.  The second kernel starts as soon as
     // the first one's CTAs are all resident and waits for the first only before it exits.
     int sm_dgrad = 0, sm_wgrad = 0;
-    if (dA && dB && M > 0 && N > 0 && K > 0 && ctx->use_pdl && ctx->overlap_backward && ctx->force_bn <= 0 &&
+    if (dA && dB && M > 0 && N > 0 && K > 0 && ctx->use_pdl && ctx->overlap_backward && ctx->partition_backward && ctx->force_bn <= 0 &&
         ctx->sm_count >= 16)
         split_sms_for_backward(ctx, M, N, K, &sm_dgrad, &sm_wgrad);
     if (dA) {

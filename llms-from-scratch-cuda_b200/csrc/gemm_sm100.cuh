@@ -680,10 +680,14 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // Programmatic dependent launch: everything above overlapped the tail of the previous kernel
     // in the stream; its results (and its reads of our output buffers) are complete only after
     // this wait.  The next kernel may start its own set-up as soon as our CTAs make room.
-    // Only the warps that touch global memory wait, each as late as it can: the producers just before
-    // their first copy (after the first work item's coordinates are known), the epilogue warps on entry
-    // (they have nothing to do until the first accumulator is complete).
+    // Programmatic dependent launch: everything above overlapped the tail of the previous kernel in the
+    // stream; its results (and its reads of our output buffers) are complete only after this wait.
+    // The next kernel is released only after the wait: if that kernel is one that runs beside this one
+    // (late_wait), it starts reading at once and relies on everything older than this kernel being
+    // complete and visible.
+    if (!p.late_wait) griddep_wait();
     griddep_launch_dependents();
+    if (threadIdx.x == 0) PROF_MARK(0);
 
     // The three issuing roles below run with all 32 lanes of their warp converged: every lane waits on the
     // barriers and does the (warp-uniform) address arithmetic, and one elected lane issues the copies, the
@@ -720,7 +724,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             // The state of the next stage's barrier is probed one iteration ahead, so that the probe's
             // latency overlaps the issue of the current stage's copies.
             bool ready = mbar_test_wait(smem_u32(&ctrl->empty[0]), 1);
-            bool waited = false;
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
@@ -739,13 +742,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
                     const bool starve = DBG(32) && (kb & 7);  // timing experiment: copies only on every eighth block
-                    const bool ld_p = do_p && !starve, ld_q = do_q && !starve;
+                    const bool ld_p = do_p && !starve, ld_q = do_q && !starve && !(DBG(8) && (kb & 1));  // 8: Q on even blocks only
                     const int c0 = kb * BK;
-                    if (!waited) {
-                        if (!p.late_wait) griddep_wait();
-                        waited = true;
-                        if (lane == 0 && do_p) PROF_MARK(0);
-                    }
                     if (elect_one()) {
                         if (rank == 0)
                             mbar_arrive_expect_tx(local_bar,
@@ -860,7 +858,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         }
     } else if (warp >= 4) {
         // ---------------------------------------------------------- epilogue
-        if (!p.late_wait) griddep_wait();
         const int q = warp & 3;            // TMEM lane quarter
         const int hsel = (warp - 4) >> 2;  // which half of the column chunks
         uint32_t sk_phase = 0, old_phase = 0;

@@ -71,7 +71,8 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
     uint8_t* tiles = smem + Cfg::CTRL_BYTES;
     uint8_t* epi_bufs = tiles + STAGES * Cfg::STAGE_BYTES;
     volatile int* abort_flag = &ctrl->abort_flag;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index is read through a shuffle so that the compiler knows it is uniform across the warp
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int slot = blockIdx.x, nslots = gridDim.x;
 
     if (threadIdx.x == 0) {
@@ -103,10 +104,11 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
     const uint32_t tmem_base = ctrl->tmem_base;
     griddep_wait();
     griddep_launch_dependents();
+    // The issuing roles run with their warp converged and one elected lane issuing (uniform operands).
 
     if (warp == 0 || warp == 3) {
         // ------------------------------------------------------------ TMA producers (P: warp 0, Q: warp 3)
-        if (lane == 0) {
+        {
             const bool is_q = warp == 3;
             const CUtensorMap* tm = is_q ? &tmQ : &tmP;
             const bool mn = is_q ? Q_MN : P_MN;
@@ -120,21 +122,24 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
                 const int r0 = is_q ? w.n_blk * BN : w.m_blk * BM;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY)) {
-                        ok = false;
-                        break;
-                    }
+                    ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                     const uint32_t bar = smem_u32(&ctrl->full[stage]);
                     const uint32_t dst = smem_u32(tiles + stage * Cfg::STAGE_BYTES) + my_off;
-                    mbar_arrive_expect_tx(bar, my_bytes);
                     const int c0 = kb * T32_BK;
-                    if (!mn) {
-                        tma_load_2d(dst, tm, bar, c0, r0);                 // [rows][Kc]: box 32 x rows
-                    } else if (as3d) {
-                        tma_load_3d(dst, tm, bar, 0, c0, r0 >> 5);         // [Kc][rows]: all 32-wide panels
-                    } else {
-                        for (int j = 0; j < panels; ++j) tma_load_2d(dst + j * (32 * 128), tm, bar, r0 + 32 * j, c0);
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(bar, my_bytes);
+                        if (!mn) {
+                            tma_load_2d(dst, tm, bar, c0, r0);                 // [rows][Kc]: box 32 x rows
+                        } else if (as3d) {
+                            tma_load_3d(dst, tm, bar, 0, c0, r0 >> 5);         // [Kc][rows]: all 32-wide panels
+                        } else {
+                            for (int j = 0; j < panels; ++j)
+                                tma_load_2d(dst + j * (32 * 128), tm, bar, r0 + 32 * j, c0);
+                        }
                     }
+                    __syncwarp();
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -147,8 +152,8 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
         WorkItem w;
         for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
             for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                if (lane == 0) ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+                ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const uint4* src = reinterpret_cast<const uint4*>(tiles + stage * Cfg::STAGE_BYTES);
                 uint4* dst = reinterpret_cast<uint4*>(tiles + stage * Cfg::STAGE_BYTES + Cfg::HI_BYTES);
@@ -164,13 +169,13 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
                 }
                 fence_proxy_async_smem();  // generic writes -> visible to the tensor core's reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctrl->conv[stage]));
+                if (elect_one()) mbar_arrive(smem_u32(&ctrl->conv[stage]));
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        {
             constexpr uint32_t idesc = umma_idesc(2, BM, BN, P_MN ? 1 : 0, Q_MN ? 1 : 0);
             // K-major: 128-byte swizzle, +32 B per UMMA_K (8 fp32).  MN-major: 32-wide panels of BK rows x
             // 128 B (LBO = panel pitch 4096 B), 4-row swizzle atoms 512 B apart (SBO), layout type 1;
@@ -188,40 +193,43 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
             for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
                 for (int kc = w.kb0; ok && kc < w.kb1; kc += T32_CHUNK, ++cc) {
                     const uint32_t acc = cc & 1, acc_phase = (cc >> 1) & 1;
-                    if (!mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E)) {
-                        ok = false;
-                        break;
-                    }
+                    ok = mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                     tc_fence_after();
                     const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
                     const int kend = min(kc + T32_CHUNK, w.kb1);
                     for (int kb = kc; kb < kend; ++kb) {
                         const uint32_t st_off = (stage * Cfg::STAGE_BYTES) >> 4;
-                        if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL)) {
-                            ok = false;
-                            break;
-                        }
+                        ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
                         tc_fence_after();
+                        if (elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < T32_BK / T32_UMMA_K; ++k)  // hi * hi, as soon as the stage has landed
-                            umma_tf32<1>(d_tmem, descP0 + (st_off + ((k * P_STEP) >> 4)),
-                                         descQ0 + (st_off + ((k * Q_STEP) >> 4)), idesc, (kb > kc || k > 0) ? 1u : 0u);
-                        if (!mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL)) {
-                            ok = false;
-                            break;
+                            for (int k = 0; k < T32_BK / T32_UMMA_K; ++k)  // hi * hi, as soon as the stage has landed
+                                umma_tf32<1>(d_tmem, descP0 + (st_off + ((k * P_STEP) >> 4)),
+                                             descQ0 + (st_off + ((k * Q_STEP) >> 4)), idesc, (kb > kc || k > 0) ? 1u : 0u);
                         }
+                        __syncwarp();
+                        ok = mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
                         tc_fence_after();
+                        if (elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < T32_BK / T32_UMMA_K; ++k) {
-                            const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
-                            const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
-                            umma_tf32<1>(d_tmem, dP + LO, dQ, idesc, 1u);  // lo * hi
-                            umma_tf32<1>(d_tmem, dP, dQ + LO, idesc, 1u);  // hi * lo
+                            for (int k = 0; k < T32_BK / T32_UMMA_K; ++k) {
+                                const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
+                                const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
+                                umma_tf32<1>(d_tmem, dP + LO, dQ, idesc, 1u);  // lo * hi
+                                umma_tf32<1>(d_tmem, dP, dQ + LO, idesc, 1u);  // hi * lo
+                            }
+                            umma_commit(smem_u32(&ctrl->empty[stage]));
+                            if (kb == kend - 1) umma_commit(smem_u32(&ctrl->tmem_full[acc]));
                         }
-                        umma_commit(smem_u32(&ctrl->empty[stage]));
+                        __syncwarp();
                         if (++stage == STAGES) { stage = 0; phase ^= 1; }
                     }
-                    if (ok) umma_commit(smem_u32(&ctrl->tmem_full[acc]));
                 }
             }
         }
@@ -241,8 +249,8 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
             for (int e = 0; e < HALF; ++e) sum[e] = 0.f;
             for (int kc = w.kb0; ok && kc < w.kb1; kc += T32_CHUNK, ++cc) {
                 const uint32_t acc = cc & 1, acc_phase = (cc >> 1) & 1;
-                if (lane == 0) ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+                ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + acc * Cfg::ACC_STRIDE + hsel * HALF + (static_cast<uint32_t>(q * 32) << 16);
@@ -256,7 +264,7 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+                if (elect_one()) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
             }
             if (!ok) break;
             const int row0 = w.m_blk * BM + q * 32;
@@ -264,7 +272,7 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
             for (int g = 0; g < HALF / 32; ++g) {
                 const int col0 = w.n_blk * BN + hsel * HALF + g * 32;
                 if (col0 >= p.No) break;
-                if (lane == 0) {
+                if (elect_one()) {
                     tma_store_wait_read<0>();
                     if constexpr (BETA1) {
                         mbar_arrive_expect_tx(old_bar, EPI_BUF_BYTES);
@@ -272,8 +280,8 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
                     }
                 }
                 if constexpr (BETA1) {
-                    if (lane == 0) ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    ok = mbar_wait(old_bar, old_phase, abort_flag, p.status, DEV_TIMEOUT_DRAIN);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     old_phase ^= 1;
                 } else {
@@ -292,13 +300,13 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0 && row0 < p.Mo) {
+                if (row0 < p.Mo && elect_one()) {
                     tma_store_2d(&tmD, smem_u32(buf), col0, row0);
                     tma_store_commit();
                 }
             }
         }
-        if (lane == 0) tma_store_wait_all<0>();
+        if (elect_one()) tma_store_wait_all<0>();
     }
 
     tc_fence_before();
