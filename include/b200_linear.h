@@ -104,6 +104,10 @@ int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_coun
  * (partials through the workspace), < 0 = share every tile among a cluster of |splits| CTAs (or
  * pairs) that sum through distributed shared memory (|splits| * (1 + cta_pair) <= 8, |splits| <= bn/32). */
 int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits);
+/* b200_linear_backward_bf16 runs its two products side by side, each on its own share of the SMs, when the
+ * cost model expects that to finish sooner than one after the other.  sm_dgrad > 0 fixes dgrad's share
+ * (wgrad gets the rest) for subsequent calls; 0 restores the model's choice. */
+int b200_linear_force_backward_split(b200_linear_ctx* ctx, int sm_dgrad);
 
 /* Weight gradient dB[K,N] = bf16_rn(bf16_rn(A[M,K]^T * dC[M,N]) + dB) that allocates nothing.
  * This entry point has no counterpart in the reference.  It exists for hosts in which this

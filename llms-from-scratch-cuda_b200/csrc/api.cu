@@ -68,6 +68,7 @@ struct b200_linear_ctx {
     int one_producer = 0;
     int overlap_backward = 1;
     int partition_backward = 1;  // 0: dgrad and wgrad both plan for the whole GPU (wgrad still fills dgrad's tail)
+    int force_sm_dgrad = 0;      // > 0: dgrad's share of the SMs in matmul_backward, whatever the cost model says
     int fp32_simt = 0;  // 1: fp32 products on the CUDA cores only (exact fp32 FMA arithmetic)
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
@@ -262,8 +263,11 @@ double plan_cost_ns(const Decomp& d, int bn, int ctas, int slots) {
     const double per_kb = per_block_ns(bn, ctas, busy);
     const int dp_rounds = (d.dp_tiles + slots - 1) / slots;
     const int sk_rounds = (d.sk_items + slots - 1) / slots;
-    double t = (static_cast<double>(dp_rounds) * d.kb_total + static_cast<double>(sk_rounds) * d.kb_per_sk) * per_kb;
-    t += 300.0 * (dp_rounds + sk_rounds);  // pipeline refill at item boundaries
+    // an item cannot go faster than its epilogue (short contractions): ~0.5 us + 8 ns per output column
+    const double epi = 500.0 + 8.0 * bn;
+    const double dp_item = d.kb_total * per_kb + 300.0;  // + pipeline refill at the item boundary
+    const double sk_item = d.kb_per_sk * per_kb + 300.0;
+    double t = dp_rounds * (dp_item > epi ? dp_item : epi) + sk_rounds * (sk_item > epi ? sk_item : epi);
     t += fixed_ns(bn, ctas, busy);
     if (d.sk_items > 0) {
         // partial sums through L2: peers exchanging slices (all resident) or a last arriver adding whole tiles
@@ -472,6 +476,11 @@ void split_sms_for_backward(b200_linear_ctx* ctx, int M, int N, int K, int* sm_d
     if ((N % 8) != 0 || (K % 8) != 0) return;
     const unsigned long long key = (static_cast<unsigned long long>(M) << 42) ^ (static_cast<unsigned long long>(N) << 21) ^
                                    static_cast<unsigned long long>(K);
+    if (ctx->force_sm_dgrad > 0 && ctx->force_sm_dgrad < ctx->sm_count - 1) {
+        *sm_dgrad = ctx->force_sm_dgrad;
+        *sm_wgrad = (ctx->sm_count - ctx->force_sm_dgrad) & ~1;
+        return;
+    }
     auto it = ctx->backward_split.find(key);
     if (it != ctx->backward_split.end()) {
         *sm_dgrad = it->second >> 16;
@@ -488,7 +497,10 @@ void split_sms_for_backward(b200_linear_ctx* ctx, int M, int N, int K, int* sm_d
         const int sw = (ctx->sm_count - sd) & ~1;
         b200_linear_plan_bf16(B200_GEMM_DGRAD_NT, 0, M, N, K, sd, &pd);
         b200_linear_plan_bf16(B200_GEMM_WGRAD_TN, 1, M, N, K, sw, &pw);
-        const double t = (pd.est_ns > pw.est_ns ? pd.est_ns : pw.est_ns) * 1.05;  // both feed from the same L2
+        // both feed from the same L2; among equal maxima (a weight gradient shared out to clusters needs a
+        // fixed number of SMs, whatever it is offered) the split that also shortens the other kernel wins
+        const double hi = pd.est_ns > pw.est_ns ? pd.est_ns : pw.est_ns, lo = pd.est_ns + pw.est_ns - hi;
+        const double t = hi * 1.05 + 0.1 * lo;
         if (t < best) {
             best = t;
             best_d = sd;
@@ -925,6 +937,12 @@ extern "C" int b200_linear_debug_timeline(b200_linear_ctx* ctx, long long* out, 
     return B200_OK;
 }
 #endif
+
+extern "C" int b200_linear_force_backward_split(b200_linear_ctx* ctx, int sm_dgrad) {
+    if (!ctx || sm_dgrad < 0 || sm_dgrad >= ctx->sm_count) return B200_E_BADARG;
+    ctx->force_sm_dgrad = sm_dgrad;
+    return B200_OK;
+}
 
 extern "C" int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair, int splits) {
     if (!ctx) return B200_E_BADARG;

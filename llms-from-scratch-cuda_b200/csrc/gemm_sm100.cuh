@@ -93,7 +93,10 @@ struct TileCfg {
     static constexpr int B_BYTES = B_ROWS * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int CTRL_BYTES = 1024;
-    static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;  // one staging buffer per epilogue warp
+    // staging buffers per epilogue warp: two, so that one TMA store can still be reading its buffer while the
+    // next chunk is converted into the other (one where a second would leave fewer than 4 pipeline stages)
+    static constexpr int EPI_BUFS = (BN == 256 && CTAS == 1) ? 1 : 2;
+    static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUFS * EPI_BUF_BYTES;
     static constexpr int STAGES_RAW = (SMEM_BUDGET - CTRL_BYTES - EPI_BYTES - 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + EPI_BYTES + 1024;  // +1024: manual alignment
@@ -227,15 +230,24 @@ __device__ __forceinline__ void add_partial32(uint32_t* acc, const float4 (&v)[8
 // in the workspace, added in the order 0..nsplits-1 (FROM_WS = true).
 // beta = 1: the old 32 x 64 block is fetched by TMA into the same staging buffer and updated in
 // place (each thread reads and rewrites only its own row), so global memory sees whole lines only.
-template <int BN, bool BETA1, bool FROM_WS>
-__device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const CUtensorMap* tmD, uint8_t* buf,
+template <int BN, bool BETA1, bool FROM_WS, int NBUF>
+__device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const CUtensorMap* tmD, uint8_t* bufs,
                                                     uint32_t taddr, const float* partials, size_t partial_stride,
                                                     int nsplits, int q, int hsel, int row0, int lane, int n0,
                                                     uint32_t old_bar, uint32_t& old_phase, volatile int* abort_flag) {
+    // With two buffers the chunks alternate between them and a chunk only waits for the store before the
+    // previous one; whatever this warp stored earlier (any path) has finished reading before the first chunk.
+    if constexpr (NBUF == 2) {
+        if (elect_one()) tma_store_wait_read<0>();
+        __syncwarp();
+    }
+    int sel = 0;
 #pragma unroll 1
     for (int c = hsel; c < BN / 64; c += 2) {
         const int col0 = n0 + c * 64;
         if (col0 >= p.No) break;  // whole chunk beyond the matrix (warp-uniform)
+        uint8_t* buf = bufs + sel * EPI_BUF_BYTES;
+        sel ^= NBUF - 1;
         uint32_t r[64];
         if constexpr (!FROM_WS) {
             tmem_ld_32x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
@@ -244,7 +256,7 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
         if constexpr (BETA1) {
             // the warp's previous store must have finished reading the staging buffer
             if (elect_one()) {
-                tma_store_wait_read<0>();
+                tma_store_wait_read<NBUF - 1>();
                 mbar_arrive_expect_tx(old_bar, EPI_BUF_BYTES);
                 tma_load_2d(smem_u32(buf), tmD, old_bar, col0, row0);  // rows/cols beyond the matrix read as 0
             }
@@ -278,8 +290,8 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
             if (!ok) return false;
             old_phase ^= 1;
         } else {
-            // the warp's previous store must have finished reading the staging buffer
-            if (elect_one()) tma_store_wait_read<0>();
+            // the warp's last store from this buffer must have finished reading it
+            if (elect_one()) tma_store_wait_read<NBUF - 1>();
             __syncwarp();
         }
 #pragma unroll
@@ -877,7 +889,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             if (warp == 4 && lane == 0) PROF_MARK(4);  // last item's accumulator ready
             const int row0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM + q * 32;
             const uint32_t taddr = tmem_base + acc * Cfg::ACC_STRIDE + (static_cast<uint32_t>(q * 32) << 16);
-            uint8_t* my_buf = epi_bufs + (warp - 4) * EPI_BUF_BYTES;
+            uint8_t* my_buf = epi_bufs + (warp - 4) * (Cfg::EPI_BUFS * EPI_BUF_BYTES);
             auto release_acc = [&]() {
                 tc_fence_before();
                 __syncwarp();
@@ -894,7 +906,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 if (!ok) break;
             } else if (w.sk_item < 0) {
                 if (!DBG(1))
-                    ok = epilogue_store_bf16<BN, BETA1, false>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
+                    ok = epilogue_store_bf16<BN, BETA1, false, Cfg::EPI_BUFS>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
                                                                w.n_blk * BN, old_bar, old_phase, abort_flag);
                 release_acc();
                 if (!ok) break;
@@ -943,7 +955,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     __threadfence();
                     const float* first = p.ws + (static_cast<size_t>(w.sk_tile) * p.sk_splits * CTAS + rank) *
                                                     Cfg::PARTIAL_FLOATS;
-                    ok = epilogue_store_bf16<BN, BETA1, true>(p, &tmD, my_buf, 0, first,
+                    ok = epilogue_store_bf16<BN, BETA1, true, Cfg::EPI_BUFS>(p, &tmD, my_buf, 0, first,
                                                               static_cast<size_t>(CTAS) * Cfg::PARTIAL_FLOATS, p.sk_splits,
                                                               q, hsel, row0, lane, w.n_blk * BN, old_bar, old_phase,
                                                               abort_flag);

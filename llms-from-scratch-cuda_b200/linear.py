@@ -61,6 +61,7 @@ def _load():
         getattr(lib, name).argtypes = [vp, ci, ci, vp, vp, vp, ci, ci, ci]
     lib.b200_linear_plan_bf16.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(Plan)]
     lib.b200_linear_force_plan.argtypes = [vp, ci, ci, ci]
+    lib.b200_linear_force_backward_split.argtypes = [vp, ci]
     return lib
 
 
@@ -128,6 +129,10 @@ class Handle:
 
     def force_plan(self, bn=-1, cta_pair=0, splits=0):
         self._check(lib.b200_linear_force_plan(self._h, bn, cta_pair, splits), "force_plan")
+
+    def force_backward_split(self, sm_dgrad=0):
+        """SMs given to dgrad when matmul_backward runs its two products side by side (0 = cost model)."""
+        self._check(lib.b200_linear_force_backward_split(self._h, sm_dgrad), "force_backward_split")
 
     def destroy(self):
         if self._h:
