@@ -697,6 +697,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // The next kernel is released only after the wait: if that kernel is one that runs beside this one
     // (late_wait), it starts reading at once and relies on everything older than this kernel being
     // complete and visible.
+    if (threadIdx.x == 0) PROF_MARK(9);
     if (!p.late_wait) griddep_wait();
     griddep_launch_dependents();
     if (threadIdx.x == 0) PROF_MARK(0);
