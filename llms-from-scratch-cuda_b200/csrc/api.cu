@@ -69,6 +69,7 @@ struct b200_linear_ctx {
     int overlap_backward = 1;
     int partition_backward = 1;  // 0: dgrad and wgrad both plan for the whole GPU (wgrad still fills dgrad's tail)
     int force_sm_dgrad = 0;      // > 0: dgrad's share of the SMs in matmul_backward, whatever the cost model says
+    int tile_group = 0;          // > 0: tiles of the fast dimension per group of the tile order (0 = plain raster)
     int fp32_simt = 0;  // 1: fp32 products on the CUDA cores only (exact fp32 FMA arithmetic)
     EncodeTiledFn encode = nullptr;
     std::unordered_map<TmKey, CUtensorMap, TmKeyHash> tm_cache;
@@ -570,6 +571,9 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
     gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
     gp.m_fastest = plan.m_fastest;
+    // Grouped tile order (B200_LINEAR_TILE_GROUP=n): measured no gain over the plain raster on any shape,
+    // up to 8192 x 32000 x 32000, with the runs interleaved; off unless asked for.
+    gp.group = ctx->tile_group > 0 ? ctx->tile_group : 0;
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
     gp.ksplit = ksplit;
     gp.late_wait = (overlap_prev && ctx->use_pdl && ctx->overlap_backward) ? 1 : 0;
@@ -756,6 +760,7 @@ int gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float
     gp.n_tiles = ceil_div_i(No, bn);
     gp.kb_total = ceil_div_i(Kc, T32_BK);
     gp.m_fastest = Mo <= No ? 1 : 0;
+    gp.group = 0;
     const long long tiles = 1LL * gp.m_tiles * gp.n_tiles;
     if (tiles > 0x7FFFFFFFLL) return B200_E_TOOBIG;
     gp.dp_tiles = static_cast<int>(tiles);
@@ -810,6 +815,7 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     if (const char* e = getenv("B200_LINEAR_ONE_PRODUCER")) ctx->one_producer = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_OVERLAP_BACKWARD")) ctx->overlap_backward = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_PARTITION_BACKWARD")) ctx->partition_backward = atoi(e) != 0;
+    if (const char* e = getenv("B200_LINEAR_TILE_GROUP")) ctx->tile_group = atoi(e);
     if (const char* e = getenv("B200_LINEAR_FP32_SIMT")) ctx->fp32_simt = atoi(e) != 0;
     if (cudaMalloc(&ctx->status_dev, sizeof(int)) != cudaSuccess ||
         cudaMemset(ctx->status_dev, 0, sizeof(int)) != cudaSuccess) {
@@ -1082,6 +1088,7 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
     gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
     gp.m_fastest = Mo <= No ? 1 : 0;
+    gp.group = 0;
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
     gp.ksplit = 1;
     gp.late_wait = 0;

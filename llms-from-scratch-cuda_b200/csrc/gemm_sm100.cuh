@@ -45,6 +45,7 @@ struct GemmParams {
     int m_tiles, n_tiles;    // ceil(Mo/(BM*CTAS)), ceil(No/BN)
     int kb_total;            // ceil(Kc/BK)
     int m_fastest;           // tile raster: 1 = consecutive tiles walk down the rows
+    int group;               // tiles of the fast dimension per group of the tile order (0 = no grouping)
     int dp_tiles;            // tiles [0, dp_tiles) are computed whole
     int sk_splits;           // tiles [dp_tiles, m_tiles*n_tiles) are cut into this many ranges
     int kb_per_sk;           // ceil(kb_total/sk_splits); every range owns >= 1 block
@@ -139,13 +140,26 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int slot, int nslo
         w.kb0 = 0;
         w.kb1 = p.kb_total;
     }
-    if (p.m_fastest) {
-        w.n_blk = tile / p.m_tiles;
-        w.m_blk = tile - w.n_blk * p.m_tiles;
+    // Tile order: the fast dimension is walked in groups of p.group tiles (0: the whole dimension), each
+    // group across the whole slow dimension before the next, so that the tiles running at one time form a
+    // block of the output (about as many distinct row tiles as column tiles) instead of a thin stripe:
+    // fewer distinct operand panels per wave, which is what L2 and HBM see.
+    const int fast_tiles = p.m_fastest ? p.m_tiles : p.n_tiles;
+    const int slow_tiles = p.m_fastest ? p.n_tiles : p.m_tiles;
+    int fast, slow;
+    if (p.group > 0 && p.group < fast_tiles) {
+        const int per_group = p.group * slow_tiles;
+        const int g = tile / per_group;
+        const int r = tile - g * per_group;
+        const int width = min(p.group, fast_tiles - g * p.group);  // the last group may be narrower
+        slow = r / width;
+        fast = g * p.group + (r - slow * width);
     } else {
-        w.m_blk = tile / p.n_tiles;
-        w.n_blk = tile - w.m_blk * p.n_tiles;
+        slow = tile / fast_tiles;
+        fast = tile - slow * fast_tiles;
     }
+    w.m_blk = p.m_fastest ? fast : slow;
+    w.n_blk = p.m_fastest ? slow : fast;
     return true;
 }
 
