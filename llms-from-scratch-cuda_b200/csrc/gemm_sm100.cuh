@@ -893,10 +893,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         WorkItem w;
         for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
             const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
-            if (DBG(1024) && lane == 0) {  // timing experiment: sleep between probes
-                for (int it = 0; it < 2000000 && !mbar_test_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase); ++it)
-                    __nanosleep(500);
-            }
             ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;

@@ -98,15 +98,6 @@ __device__ __forceinline__ bool elect_one() {
         : "=r"(pred));
     return pred != 0;
 }
-// Device-scope release increment / acquire load of a flag word in global memory.
-__device__ __forceinline__ void red_release_gpu_add(int* ptr, int v) {
-    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
-    return v;
-}
 // Non-blocking probe of a barrier phase.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -121,25 +112,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait that polls without suspending the thread.
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                               int code) {
-    if (mbar_test_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    uint32_t spins = 0;
-    while (true) {
-        if (mbar_test_wait(bar, parity)) return true;
-        if ((++spins & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-
 // Bounded wait. `abort_flag` lives in shared memory and is shared by all roles
 // of the CTA; `status` is the context's device status word.
 template <bool kCluster = false>

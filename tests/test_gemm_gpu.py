@@ -215,3 +215,30 @@ def test_reference_golden_fixture(pkg, handle, oracle):
                 if bf:
                     want = (want.astype(np.uint32) << 16).view(np.float32)
                 assert rel_err(got, want.astype(np.float64)) <= (8e-3 if bf else 1e-5), (sfx, i, name)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sm_dgrad", [0, 24, 48, 100, 140])
+def test_backward_side_by_side_on_sm_shares(pkg, handle, oracle, sm_dgrad):
+    """matmul_backward with dgrad and wgrad on complementary shares of the SMs (0 = the cost model's choice):
+    same results as the oracle for every share, dB accumulated over two calls."""
+    rng = np.random.default_rng(sm_dgrad)
+    dt = torch.bfloat16
+    try:
+        handle.force_backward_split(sm_dgrad)
+        for M, N, K in ((8192, 768, 768), (8192, 256, 768), (4096, 2048, 768), (1000, 768, 2048)):
+            A, B, dC = inputs(oracle, M, N, K, 3000 + N + sm_dgrad, True)
+            a, b, dc = dev(A, dt), dev(B, dt), dev(dC, dt)
+            da = torch.empty(M, K, device=DEV, dtype=dt)
+            db = torch.zeros(K, N, device=DEV, dtype=dt)
+            pkg.matmul_backward(handle, da, db, dc, a, b, M, N, K)
+            pkg.matmul_backward(handle, da, db, dc, a, b, M, N, K)
+            handle.sync()
+            for which, got, x, y, mult in ((1, da, dC, B, 1.0), (2, db, A, dC, 2.0)):
+                rows, cols = got.shape
+                r, cc = _sample_points(rng, rows, cols)
+                want = mult * oracle.gemm_f64_samples(which, x, y, M, N, K, r, cc)
+                g = got.float().cpu().numpy()[r, cc].astype(np.float64)
+                assert np.abs(g - want).max() / np.abs(want).max() <= 1e-2, (sm_dgrad, which, M, N, K)
+    finally:
+        handle.force_backward_split(0)

@@ -67,3 +67,25 @@ def test_plan_rejects_bad_arguments(pkg):
     for args in ((3, 0, 8, 8, 8, 148), (0, 0, 0, 8, 8, 148), (0, 0, 8, -1, 8, 148), (0, 0, 8, 8, 8, 0)):
         with pytest.raises(pkg.LinearError):
             pkg.plan_bf16(*args)
+
+
+def test_plan_for_a_share_of_the_sms(pkg):
+    """matmul_backward plans its two products for complementary shares of the GPU: every plan must fit its share."""
+    for sms in (8, 32, 48, 64, 84, 100, 116, 140):
+        for which in (1, 2):
+            for N, K in ((768, 768), (256, 768), (2048, 768), (768, 2048), (32000, 768)):
+                p = pkg.plan_bf16(which, which == 2, 8192, N, K, sms)
+                ctas = 2 if p.cta_pair else 1
+                assert p.est_ns > 0
+                if p.cluster_split > 1:
+                    assert p.tiles * p.cluster_split * ctas <= sms, (sms, which, N, K)
+                elif p.splits > 1:
+                    assert p.sk_items <= sms // ctas, (sms, which, N, K)
+
+
+def test_estimate_grows_when_sms_are_taken_away(pkg):
+    for which in (0, 1, 2):
+        for N, K in ((768, 768), (2048, 768), (32000, 768)):
+            full = pkg.plan_bf16(which, which == 2, 8192, N, K, 148).est_ns
+            third = pkg.plan_bf16(which, which == 2, 8192, N, K, 48).est_ns
+            assert third > full, (which, N, K, full, third)
