@@ -696,13 +696,24 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         tmem_relinquish<CTAS>();
     }
     tc_fence_before();
+    // The other CTAs' barriers must exist before anything signals them.  Every thread arrives at the cluster
+    // barrier as soon as its own part of the set-up is done (release), so the barrier's latency overlaps the
+    // slowest part (the TMEM allocation) instead of following it.
+    if (clustered) cluster_arrive_release();
     __syncthreads();
-    if (clustered) {  // the other CTAs' barriers must exist before anything signals them
-        cluster_arrive_release();
-        cluster_wait_acquire();
-    }
+    if (clustered) cluster_wait_acquire();
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
+    // the first work item does not depend on memory: know it before the dependency wait
+    WorkItem w_first;
+    const bool have_first = get_work(p, slot, nslots, 0, w_first);
+    auto next_work = [&](int i, WorkItem& w) {
+        if (i == 0) {
+            w = w_first;
+            return have_first;
+        }
+        return get_work(p, slot, nslots, i, w);
+    };
     // Programmatic dependent launch: everything above overlapped the tail of the previous kernel
     // in the stream; its results (and its reads of our output buffers) are complete only after
     // this wait.  The next kernel may start its own set-up as soon as our CTAs make room.
@@ -711,6 +722,34 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // The next kernel is released only after the wait: if that kernel is one that runs beside this one
     // (late_wait), it starts reading at once and relies on everything older than this kernel being
     // complete and visible.
+    // While the previous kernel in the stream finishes: ask L2 for the first stages of the first work item.
+    // L2 is the point of coherence for device memory, so a line fetched early is still current when the
+    // copies into shared memory read it after the wait; inside the step the operands come from HBM (the
+    // working set is far larger than L2) and this takes their first-touch latency off the critical path.
+    if ((warp == 0 || warp == 3) && have_first && !p.late_wait && !(p.one_producer && warp == 3)) {
+        if (elect_one()) {
+            WorkItem w = w_first;
+            narrow_to_krank(p, krank, w);
+            const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
+            const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
+            const int kb_end = min(w.kb1, w.kb0 + STAGES);
+            for (int is_q = (warp == 0 ? 0 : 1); is_q <= ((warp == 3 || p.one_producer) ? 1 : 0); ++is_q) {
+                const CUtensorMap* tm = is_q ? &tmQ : &tmP;
+                const bool mn = is_q ? Q_MN : P_MN;
+                const bool as3d = is_q ? (p.q_3d != 0) : (p.p_3d != 0);
+                const int panels = is_q ? Cfg::B_ROWS / 64 : BM / 64;
+                const int r0 = is_q ? n0 : m0;
+                for (int kb = w.kb0; kb < kb_end; ++kb) {
+                    const int c0 = kb * BK;
+                    if (!mn) tma_prefetch_l2_2d(tm, c0, r0);
+                    else if (as3d) tma_prefetch_l2_3d(tm, 0, c0, r0 >> 6);
+                    else
+                        for (int j = 0; j < panels; ++j) tma_prefetch_l2_2d(tm, r0 + 64 * j, c0);
+                }
+            }
+        }
+        __syncwarp();
+    }
     if (threadIdx.x == 0) PROF_MARK(9);
     if (!p.late_wait) griddep_wait();
     griddep_launch_dependents();
@@ -751,7 +790,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             // The state of the next stage's barrier is probed one iteration ahead, so that the probe's
             // latency overlaps the issue of the current stage's copies.
             bool ready = mbar_test_wait(smem_u32(&ctrl->empty[0]), 1);
-            for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+            for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
                 const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
@@ -823,7 +862,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
 #ifdef B200_PROFILE
             long long tw[5] = {0, 0, 0, 0, 0}, tq_prev = clock64();
 #endif
-            for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+            for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
                 ok = mbar_wait<PAIR>(smem_u32(&ctrl->tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
@@ -891,7 +930,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         const uint32_t old_bar = smem_u32(&ctrl->old_bar[warp - 4]);
         bool ok = true;
         WorkItem w;
-        for (int i = 0; ok && get_work(p, slot, nslots, i, w); ++i) {
+        for (int i = 0; ok && next_work(i, w); ++i) {
             const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
             ok = mbar_wait(smem_u32(&ctrl->tmem_full[acc]), acc_phase, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __all_sync(0xffffffffu, ok);
@@ -978,9 +1017,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 __syncwarp();
             }
         }
-        // every TMA store of this warp must have read its staging buffer and landed before exit
+        // every TMA store of this warp must have read its staging buffer before the CTA gives up its shared
+        // memory; the writes themselves are complete when the grid is
         if (warp == 4 && lane == 0) PROF_MARK(5);
-        if (elect_one()) tma_store_wait_all<0>();
+        if (elect_one()) tma_store_wait_read<0>();
         if (warp == 4 && lane == 0) PROF_MARK(6);
     }
 

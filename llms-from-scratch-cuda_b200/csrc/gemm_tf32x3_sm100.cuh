@@ -306,7 +306,7 @@ gemm_tf32x3_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant
                 }
             }
         }
-        if (elect_one()) tma_store_wait_all<0>();
+        if (elect_one()) tma_store_wait_read<0>();  // staging buffers read; the grid's end completes the writes
     }
 
     tc_fence_before();

@@ -135,6 +135,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
 }
+// Bring the box of a tiled copy into L2 only (no shared memory, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tm, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                     reinterpret_cast<uint64_t>(tm)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* tm, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                     reinterpret_cast<uint64_t>(tm)),
+                 "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 // 2-D tiled load global -> shared, completion counted in bytes on `bar`.
 // x is the innermost (contiguous) coordinate and must keep the copy 16-byte aligned.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
