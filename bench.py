@@ -589,6 +589,67 @@ def run_sweep(args):
     print(json.dumps({"skipped": skipped, "seconds": round(time.time() - t_start, 1)}))
 
 
+def run_ce_shard(args):
+    """The vocabulary-sharded cross-entropy kernels on one rank's shard of config 4 (16384 tokens, llama3
+    vocabulary 128256 over 8 ranks = 16032 columns): HBM-bound, timed alone with CUDA events against the
+    measured copy bandwidth.  The reference's own cross-entropy kernels (one thread per row) are timed on the
+    same shard when oracle/_ref has them (rows a multiple of 256: their forward has no bounds check)."""
+    import ctypes
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rows, cols = 16384, 16032
+    g = torch.Generator(device=dev).manual_seed(5)
+    logits = (3.0 * torch.randn(rows, cols, device=dev, generator=g)).to(torch.bfloat16)  # 525 MB > L2
+    targets = torch.randint(0, cols, (rows,), device=dev, generator=g, dtype=torch.int32)
+    out = torch.empty_like(logits)
+    peaks = measured_peaks()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    lm, sm, tg = pkg.ce_shard_stats(logits, targets, 0)
+    us_stats = timed(lambda: pkg.ce_shard_stats(logits, targets, 0))
+    us_bwd = timed(lambda: pkg.ce_shard_backward(logits, targets, 0, lm, sm, 1.0 / rows, out=out))
+    nbytes = logits.numel() * 2
+    line = {"metric": "vocabulary-sharded cross-entropy kernels, one rank's shard of config 4", "unit": "GB/s",
+            "config": {"workload": "logits [16384, 16032] bf16 (525 MB, larger than L2), int32 targets"},
+            "stats": {"us": round(us_stats, 1), "gbs": round(nbytes / us_stats / 1e3, 1),
+                      "frac_of_measured_hbm": round(nbytes / us_stats / 1e3 / peaks["hbm_gbs"], 3),
+                      "algorithmic_bytes": nbytes},
+            "backward": {"us": round(us_bwd, 1), "gbs": round(2 * nbytes / us_bwd / 1e3, 1),
+                         "frac_of_measured_hbm": round(2 * nbytes / us_bwd / 1e3 / peaks["hbm_gbs"], 3),
+                         "algorithmic_bytes": 2 * nbytes},
+            "peak": peaks["hbm_gbs"], "peak_source": peaks["source"]}
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_matmul.so")
+    if os.path.exists(path):
+        lib = ctypes.CDLL(path)
+        if hasattr(lib, "ref_crossentropy_forward_bf16"):
+            vp, ci = ctypes.c_void_p, ctypes.c_int
+            lib.ref_crossentropy_forward_bf16.argtypes = [vp, vp, vp, ci, ci, ci]
+            lib.ref_crossentropy_forward_bf16.restype = None
+            lib.ref_crossentropy_backward_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ctypes.c_float]
+            lib.ref_crossentropy_backward_bf16.restype = None
+            probs = logits.clone()
+            loss = torch.empty(rows, device=dev, dtype=torch.float32)
+            us_rf = timed(lambda: lib.ref_crossentropy_forward_bf16(loss.data_ptr(), probs.data_ptr(), targets.data_ptr(), 2, rows // 2, cols), reps=3)
+            us_rb = timed(lambda: lib.ref_crossentropy_backward_bf16(out.data_ptr(), probs.data_ptr(), targets.data_ptr(), 2, rows // 2, cols, 1.0), reps=3)
+            line["reference"] = {"forward_us": round(us_rf, 1), "backward_us": round(us_rb, 1),
+                                 "what": "cuda/crossentropy.cu bf16 overloads, unmodified, whole-row version on the same matrix"}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None, help="profile mode: <projection>:<fwd_nn|dgrad_nt|wgrad_tn>")
@@ -603,10 +664,13 @@ def main():
     ap.add_argument("--sweep-seconds", type=float, default=240.0)
     ap.add_argument("--sweep-gb", type=float, default=40.0)
     ap.add_argument("--sweep-f32-flop", type=float, default=3e12)
+    ap.add_argument("--ce-shard", action="store_true", help="time the vocabulary-sharded cross-entropy kernels")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.sweep:
+    if args.ce_shard:
+        run_ce_shard(args)
+    elif args.sweep:
         run_sweep(args)
     elif args.only:
         run_only(args)

@@ -127,6 +127,30 @@ int b200_linear_force_backward_split(b200_linear_ctx* ctx, int sm_dgrad);
 int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const void* dC, int M, int N, int K,
                                    void* cuda_stream);
 
+/* Cross-entropy when the LM head [K, V] is sharded by columns across GPUs (one process per GPU): the
+ * per-shard device kernels.  They replace crossentropy_forward / crossentropy_softmax_backward
+ * (cuda/crossentropy.cu:96-122,124-132; bf16 overloads declared cuda/kernels.cuh:402-403; called from
+ * llama2-mistral/src/model.cpp:613-614,634) in that mode, where no rank ever holds a whole row of logits.
+ * logits: [rows, ld] bf16, this rank's columns [0, cols) = global columns [col0, col0 + cols); targets:
+ * global token ids [rows].  The host does the two small exchanges in between (all-reduce MAX of the row maxima,
+ * all-reduce SUM of the re-based sums and target logits).  No context: asynchronous on `cuda_stream`
+ * (a cudaStream_t; NULL = legacy default stream).  Same loss and gradient as the reference up to its bf16
+ * rounding of the probabilities, which these kernels do not do (only dlogits is rounded, once).
+ *   stats:    row_max = max_v l, row_sum = sum_v exp(l - row_max), row_target = l[target] or 0 if not owned
+ *   rescale:  row_sum *= exp(local_max - global_max)
+ *   loss:     loss = log(global_sum) + global_max - target_logit                  (= -log softmax[target])
+ *   backward: dlogits = (exp(l - global_max) / global_sum - [column == target]) * scale   (in place allowed);
+ *             the reference's scale is loss_scale / BT (cuda/crossentropy.cu:155). */
+int b200_ce_shard_stats_bf16(const void* logits, int rows, int cols, long long ld, const int* targets, int col0,
+                             float* row_max, float* row_sum, float* row_target, void* cuda_stream);
+int b200_ce_shard_rescale(const float* local_max, const float* global_max, float* row_sum, int rows,
+                          void* cuda_stream);
+int b200_ce_shard_loss(float* loss, const float* global_max, const float* global_sum, const float* target_logit,
+                       int rows, void* cuda_stream);
+int b200_ce_shard_backward_bf16(void* dlogits, const void* logits, int rows, int cols, long long ld,
+                                const int* targets, int col0, const float* global_max, const float* global_sum,
+                                float scale, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

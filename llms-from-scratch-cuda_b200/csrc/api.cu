@@ -14,6 +14,7 @@
 #include "gemm_sm100.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tf32x3_sm100.cuh"
+#include "ce_shard.cuh"
 
 using namespace b200;
 
@@ -1148,4 +1149,60 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD, gp) != cudaSuccess) return B200_E_CUDA;
     return B200_OK;
+}
+
+// ---------------------------------------------------------------- vocabulary-sharded cross-entropy
+namespace {
+int ce_launch_status() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA; }
+int ce_sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return sms;
+}
+}  // namespace
+
+extern "C" int b200_ce_shard_stats_bf16(const void* logits, int rows, int cols, long long ld, const int* targets,
+                                        int col0, float* row_max, float* row_sum, float* row_target,
+                                        void* cuda_stream) {
+    if (!targets || !row_max || !row_sum || !row_target || rows <= 0 || cols < 0 || ld < cols || col0 < 0 ||
+        (cols > 0 && !logits))
+        return B200_E_BADARG;
+    const int sms = ce_sm_count();
+    if (sms <= 0) return B200_E_NODEVICE;
+    const int grid = rows < sms * 8 ? rows : sms * 8;  // 8 CTAs of 256 threads fill an SM
+    b200::ce_shard_stats_bf16<<<grid, b200::CE_THREADS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const __nv_bfloat16*>(logits), rows, cols, ld, targets, col0, row_max, row_sum, row_target);
+    return ce_launch_status();
+}
+
+extern "C" int b200_ce_shard_rescale(const float* local_max, const float* global_max, float* row_sum, int rows,
+                                     void* cuda_stream) {
+    if (!local_max || !global_max || !row_sum || rows <= 0) return B200_E_BADARG;
+    b200::ce_shard_rescale<<<(rows + 255) / 256, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        local_max, global_max, row_sum, rows);
+    return ce_launch_status();
+}
+
+extern "C" int b200_ce_shard_loss(float* loss, const float* global_max, const float* global_sum,
+                                  const float* target_logit, int rows, void* cuda_stream) {
+    if (!loss || !global_max || !global_sum || !target_logit || rows <= 0) return B200_E_BADARG;
+    b200::ce_shard_loss<<<(rows + 255) / 256, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        loss, global_max, global_sum, target_logit, rows);
+    return ce_launch_status();
+}
+
+extern "C" int b200_ce_shard_backward_bf16(void* dlogits, const void* logits, int rows, int cols, long long ld,
+                                           const int* targets, int col0, const float* global_max,
+                                           const float* global_sum, float scale, void* cuda_stream) {
+    if (!targets || !global_max || !global_sum || rows <= 0 || cols < 0 || ld < cols || col0 < 0 ||
+        (cols > 0 && (!logits || !dlogits)))
+        return B200_E_BADARG;
+    if (cols == 0) return B200_OK;
+    const int per_cta = 8 * b200::CE_THREADS;
+    dim3 grid((cols + per_cta - 1) / per_cta, rows < 4096 ? rows : 4096, 1);
+    b200::ce_shard_backward_bf16<<<grid, b200::CE_THREADS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<__nv_bfloat16*>(dlogits), static_cast<const __nv_bfloat16*>(logits), rows, cols, ld, targets, col0,
+        global_max, global_sum, scale);
+    return ce_launch_status();
 }

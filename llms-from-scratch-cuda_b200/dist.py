@@ -10,8 +10,9 @@ data-parallel driver around its `ModelBF16` needs for THIS path:
     needs the row maximum and the row sum-of-exponentials across ranks (two small all-reduces)
     and the target logit from the rank that owns it.
 
-Everything here is device-agnostic torch (CPU + gloo in the tests, CUDA + NCCL in the bench); the
-GEMMs themselves go through `linear.matmul_forward / matmul_backward`.
+The exchange logic is device-agnostic torch.distributed (gloo ranks on CPU in the tests, NCCL on GPUs); the
+GEMMs go through `linear.matmul_forward / matmul_backward` and the per-shard cross-entropy steps through
+this library's CUDA kernels (`linear.ce_shard_*`).
 """
 import torch
 import torch.distributed as dist
@@ -69,35 +70,54 @@ class GradBuckets:
         return self.flat
 
 
-def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None):
+class CudaShardOps:
+    """The four per-shard steps of the vocabulary-parallel cross-entropy as this library's CUDA kernels
+    (csrc/ce_shard.cuh).  CUDA tensors only: there is no host implementation in the package."""
+
+    @staticmethod
+    def stats(logits_local, targets, vocab_start):
+        from . import linear
+        return linear.ce_shard_stats(logits_local, targets, vocab_start)
+
+    @staticmethod
+    def rescale(local_max, global_max, row_sum):
+        from . import linear
+        return linear.ce_shard_rescale(local_max, global_max, row_sum)
+
+    @staticmethod
+    def loss(global_max, global_sum, target_logit):
+        from . import linear
+        return linear.ce_shard_loss(global_max, global_sum, target_logit)
+
+    @staticmethod
+    def backward(logits_local, targets, vocab_start, global_max, global_sum, scale):
+        from . import linear
+        return linear.ce_shard_backward(logits_local, targets, vocab_start, global_max, global_sum, scale)
+
+
+def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None, ops=CudaShardOps):
     """Cross-entropy over a vocabulary that is split across ranks.
 
-    logits_local [BT, V_r] are this rank's columns [vocab_start, vocab_start + V_r) of the LM-head
-    output; targets [BT] are global token ids.  Returns (loss_rows fp32 [BT], dlogits_local) with
+    logits_local [BT, V_r] (bf16) are this rank's columns [vocab_start, vocab_start + V_r) of the LM-head
+    output; targets [BT] (int32) are global token ids.  Returns (loss_rows fp32 [BT], dlogits_local) with
     dlogits = (softmax - onehot) / BT restricted to this rank's columns -- the same scaling as the
     reference's crossentropy_softmax_backward (cuda/crossentropy.cu:50-64,124-132).
-    Communication: all-reduce MAX of the row maxima, then one all-reduce SUM of [sum-exp, target logit]."""
-    bt, v_r = logits_local.shape
-    x = logits_local.float()
+    Communication: all-reduce MAX of the row maxima, then one all-reduce SUM of [sum-exp, target logit].
+    `ops` supplies the four per-shard steps: this library's CUDA kernels unless a test passes a host
+    restatement to exercise the exchange without a GPU."""
+    bt = logits_local.shape[0]
     multi = dist.is_initialized() and dist.get_world_size(group) > 1
-    row_max = x.max(dim=1).values if v_r > 0 else torch.full((bt,), -float("inf"), device=x.device)
+    local_max, row_sum, tgt = ops.stats(logits_local, targets, vocab_start)
+    global_max = local_max.clone()
     if multi:
-        dist.all_reduce(row_max, op=dist.ReduceOp.MAX, group=group)
-    e = torch.exp(x - row_max[:, None])
-    local = targets - vocab_start
-    mine = (local >= 0) & (local < v_r)
-    idx = local.clamp(0, max(v_r - 1, 0))
-    tgt = torch.where(mine, x.gather(1, idx[:, None]).squeeze(1) if v_r > 0 else torch.zeros_like(row_max),
-                      torch.zeros_like(row_max))
-    packed = torch.stack([e.sum(dim=1), tgt])
+        dist.all_reduce(global_max, op=dist.ReduceOp.MAX, group=group)
+    ops.rescale(local_max, global_max, row_sum)
+    packed = torch.stack([row_sum, tgt])
     if multi:
         dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
-    sum_exp, tgt_logit = packed[0], packed[1]
-    loss_rows = torch.log(sum_exp) + row_max - tgt_logit
-    d = e / sum_exp[:, None]
-    if v_r > 0:
-        d[mine, idx[mine]] -= 1.0
-    d = (d / bt).to(logits_local.dtype)
+    global_sum, tgt_logit = packed[0].contiguous(), packed[1].contiguous()
+    loss_rows = ops.loss(global_max, global_sum, tgt_logit)
+    d = ops.backward(logits_local, targets, vocab_start, global_max, global_sum, 1.0 / bt)
     return loss_rows, d
 
 

