@@ -600,7 +600,7 @@ def run_ce_shard(args):
     pkg = load_package()
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    rows, cols = 16384, 16032
+    rows, cols = args.ce_rows, 16032
     g = torch.Generator(device=dev).manual_seed(5)
     logits = (3.0 * torch.randn(rows, cols, device=dev, generator=g)).to(torch.bfloat16)  # 525 MB > L2
     targets = torch.randint(0, cols, (rows,), device=dev, generator=g, dtype=torch.int32)
@@ -624,7 +624,7 @@ def run_ce_shard(args):
     us_bwd = timed(lambda: pkg.ce_shard_backward(logits, targets, 0, lm, sm, 1.0 / rows, out=out))
     nbytes = logits.numel() * 2
     line = {"metric": "vocabulary-sharded cross-entropy kernels, one rank's shard of config 4", "unit": "GB/s",
-            "config": {"workload": "logits [16384, 16032] bf16 (525 MB, larger than L2), int32 targets"},
+            "config": {"workload": "logits [%d, 16032] bf16 (%d MB, larger than L2), int32 targets" % (rows, rows * cols * 2 // 1000000)},
             "stats": {"us": round(us_stats, 1), "gbs": round(nbytes / us_stats / 1e3, 1),
                       "frac_of_measured_hbm": round(nbytes / us_stats / 1e3 / peaks["hbm_gbs"], 3),
                       "algorithmic_bytes": nbytes},
@@ -665,6 +665,7 @@ def main():
     ap.add_argument("--sweep-gb", type=float, default=40.0)
     ap.add_argument("--sweep-f32-flop", type=float, default=3e12)
     ap.add_argument("--ce-shard", action="store_true", help="time the vocabulary-sharded cross-entropy kernels")
+    ap.add_argument("--ce-rows", type=int, default=16384, help="rows of the shard for --ce-shard (a multiple of 512)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -1170,7 +1170,8 @@ extern "C" int b200_ce_shard_stats_bf16(const void* logits, int rows, int cols, 
         return B200_E_BADARG;
     const int sms = ce_sm_count();
     if (sms <= 0) return B200_E_NODEVICE;
-    const int grid = rows < sms * 8 ? rows : sms * 8;  // 8 CTAs of 256 threads fill an SM
+    const int ctas = (rows + b200::CE_THREADS / 32 - 1) / (b200::CE_THREADS / 32);  // one warp per row
+    const int grid = ctas < sms * 8 ? ctas : sms * 8;  // 8 CTAs of 256 threads fill an SM
     b200::ce_shard_stats_bf16<<<grid, b200::CE_THREADS, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
         static_cast<const __nv_bfloat16*>(logits), rows, cols, ld, targets, col0, row_max, row_sum, row_target);
     return ce_launch_status();

@@ -44,74 +44,69 @@ __device__ __forceinline__ void ce_online_merge(float& m, float& s, float m2, fl
     }
 }
 
-// One CTA per row (grid-stride over rows).  logits: [rows, ld] bf16, columns [0, cols) belong to this shard and
-// are global columns [col0, col0 + cols).  Outputs per row: max, sum of exp(l - max), target logit (0 if the
-// target column lives on another rank).  cols == 0 gives (-inf, 0, 0).
+__device__ __forceinline__ void ce_add_vec8(float& m, float& s, const uint4& u) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        x[2 * j] = __uint_as_float(w[j] << 16);
+        x[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+    // the maximum of the eight first: one re-basing of the running sum at most (rare once the running
+    // maximum has settled), then eight exponentials without a branch
+    const float vm = fmaxf(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7])));
+    if (vm > m) {
+        s *= __expf(m - vm);  // exp(-inf) = 0 covers the first vector
+        m = vm;
+    }
+    float add = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add += __expf(x[j] - m);
+    s += add;
+}
+
+// One warp per row (grid-stride over rows), four 16-byte loads in flight per lane; the row is reduced with
+// shuffles only.  logits: [rows, ld] bf16, columns [0, cols) belong to this shard and are global columns
+// [col0, col0 + cols).  Outputs per row: max, sum of exp(l - max), target logit (0 if the target column
+// lives on another rank).  cols == 0 gives (-inf, 0, 0).
 __global__ void __launch_bounds__(CE_THREADS)
 ce_shard_stats_bf16(const __nv_bfloat16* __restrict__ logits, int rows, int cols, long long ld,
                     const int* __restrict__ targets, int col0, float* __restrict__ row_max,
                     float* __restrict__ row_sum, float* __restrict__ row_tgt) {
-    __shared__ float sm_m[CE_THREADS / 32], sm_s[CE_THREADS / 32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = CE_THREADS / 32;
+    for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
         const __nv_bfloat16* row = logits + static_cast<long long>(r) * ld;
         float m = -INFINITY, s = 0.f;
         // 16-byte loads where the row start allows it (ld and the base pointer multiples of 8 elements)
-        const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
         int v0 = 0;
-        if (vec) {
+        if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
             const int nvec = cols >> 3;
             const uint4* row4 = reinterpret_cast<const uint4*>(row);
-            for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
-                const uint4 u = __ldg(row4 + i);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-                float x[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    x[2 * j] = __uint_as_float(w[j] << 16);
-                    x[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
-                }
-                // the maximum of the eight first: one re-basing of the running sum at most (rare once the
-                // running maximum has settled), then eight exponentials without a branch
-                float vm = fmaxf(fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3])), fmaxf(fmaxf(x[4], x[5]), fmaxf(x[6], x[7])));
-                if (vm > m) {
-                    s *= __expf(m - vm);  // exp(-inf) = 0 covers the first vector
-                    m = vm;
-                }
-                float add = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) add += __expf(x[j] - m);
-                s += add;
+            int i = lane;
+            for (; i + 96 < nvec; i += 128) {
+                const uint4 u0 = __ldg(row4 + i), u1 = __ldg(row4 + i + 32), u2 = __ldg(row4 + i + 64),
+                            u3 = __ldg(row4 + i + 96);
+                ce_add_vec8(m, s, u0);
+                ce_add_vec8(m, s, u1);
+                ce_add_vec8(m, s, u2);
+                ce_add_vec8(m, s, u3);
             }
+            for (; i < nvec; i += 32) ce_add_vec8(m, s, __ldg(row4 + i));
             v0 = nvec << 3;
         }
-        for (int v = v0 + threadIdx.x; v < cols; v += CE_THREADS) ce_online_add(m, s, __bfloat162float(row[v]));
+        for (int v = v0 + lane; v < cols; v += 32) ce_online_add(m, s, __bfloat162float(row[v]));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
             ce_online_merge(m, s, m2, s2);
         }
         if (lane == 0) {
-            sm_m[warp] = m;
-            sm_s[warp] = s;
+            row_max[r] = m;
+            row_sum[r] = s;
+            const int t = targets[r] - col0;
+            row_tgt[r] = (t >= 0 && t < cols) ? __bfloat162float(row[t]) : 0.f;
         }
-        __syncthreads();
-        if (warp == 0) {
-            m = lane < CE_THREADS / 32 ? sm_m[lane] : -INFINITY;
-            s = lane < CE_THREADS / 32 ? sm_s[lane] : 0.f;
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) {
-                const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
-                ce_online_merge(m, s, m2, s2);
-            }
-            if (lane == 0) {
-                row_max[r] = m;
-                row_sum[r] = s;
-                const int t = targets[r] - col0;
-                row_tgt[r] = (t >= 0 && t < cols) ? __bfloat162float(row[t]) : 0.f;
-            }
-        }
-        __syncthreads();
     }
 }
 
@@ -132,33 +127,52 @@ __global__ void ce_shard_loss(float* __restrict__ loss, const float* __restrict_
     if (r < rows) loss[r] = logf(global_sum[r]) + global_max[r] - target_logit[r];
 }
 
+__device__ __forceinline__ uint4 ce_bwd_vec8(const uint4& u, float m, float inv, int t, int c0, float scale) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float a = __expf(__uint_as_float(w[j] << 16) - m) * inv;
+        float b = __expf(__uint_as_float(w[j] & 0xFFFF0000u) - m) * inv;
+        if (c0 + 2 * j == t) a -= 1.0f;
+        if (c0 + 2 * j + 1 == t) b -= 1.0f;
+        __nv_bfloat162 p = __floats2bfloat162_rn(a * scale, b * scale);
+        o[j] = *reinterpret_cast<uint32_t*>(&p);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // dlogits[r, v] = (exp(l - m_r) / s_r - [col0 + v == target_r]) * scale, bf16; may run in place.
-// grid = (column chunks of 8 * CE_THREADS, rows (grid-stride)).
+// grid = (column chunks of 8 * CE_THREADS, rows (grid-stride)); a thread owns 8 columns and walks down the rows,
+// two rows per step so that two 16-byte loads are in flight.
 __global__ void __launch_bounds__(CE_THREADS)
 ce_shard_backward_bf16(__nv_bfloat16* dlogits, const __nv_bfloat16* logits, int rows, int cols, long long ld,
                        const int* __restrict__ targets, int col0, const float* __restrict__ global_max,
                        const float* __restrict__ global_sum, float scale) {
     const int c0 = (blockIdx.x * CE_THREADS + threadIdx.x) * 8;
     if (c0 >= cols) return;
-    for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    const bool vec = c0 + 8 <= cols && (ld & 7) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0;
+    const int step = gridDim.y;
+    int r = blockIdx.y;
+    if (vec) {
+        for (; r + step < rows; r += 2 * step) {
+            const int r1 = r + step;
+            const uint4 u0 = *reinterpret_cast<const uint4*>(logits + static_cast<long long>(r) * ld + c0);
+            const uint4 u1 = *reinterpret_cast<const uint4*>(logits + static_cast<long long>(r1) * ld + c0);
+            const float m0 = global_max[r], i0 = 1.0f / global_sum[r], m1 = global_max[r1], i1 = 1.0f / global_sum[r1];
+            const int t0 = targets[r] - col0, t1 = targets[r1] - col0;
+            *reinterpret_cast<uint4*>(dlogits + static_cast<long long>(r) * ld + c0) = ce_bwd_vec8(u0, m0, i0, t0, c0, scale);
+            *reinterpret_cast<uint4*>(dlogits + static_cast<long long>(r1) * ld + c0) = ce_bwd_vec8(u1, m1, i1, t1, c0, scale);
+        }
+    }
+    for (; r < rows; r += step) {
         const float m = global_max[r], inv = 1.0f / global_sum[r];
         const int t = targets[r] - col0;
         const __nv_bfloat16* src = logits + static_cast<long long>(r) * ld + c0;
         __nv_bfloat16* dst = dlogits + static_cast<long long>(r) * ld + c0;
-        if (c0 + 8 <= cols && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
-            const uint4 u = *reinterpret_cast<const uint4*>(src);
-            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float a = __expf(__uint_as_float(w[j] << 16) - m) * inv;
-                float b = __expf(__uint_as_float(w[j] & 0xFFFF0000u) - m) * inv;
-                if (c0 + 2 * j == t) a -= 1.0f;
-                if (c0 + 2 * j + 1 == t) b -= 1.0f;
-                __nv_bfloat162 p = __floats2bfloat162_rn(a * scale, b * scale);
-                o[j] = *reinterpret_cast<uint32_t*>(&p);
-            }
-            *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+        if (vec) {
+            *reinterpret_cast<uint4*>(dst) = ce_bwd_vec8(*reinterpret_cast<const uint4*>(src), m, inv, t, c0, scale);
         } else {
             for (int j = 0; j < 8 && c0 + j < cols; ++j) {
                 float a = __expf(__bfloat162float(src[j]) - m) * inv;
