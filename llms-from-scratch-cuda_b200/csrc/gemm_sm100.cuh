@@ -790,6 +790,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             // The state of the next stage's barrier is probed one iteration ahead, so that the probe's
             // latency overlaps the issue of the current stage's copies.
             bool ready = mbar_test_wait(smem_u32(&ctrl->empty[0]), 1);
+            const bool issuer = elect_one();  // one lane, the same for the whole loop
             for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
@@ -810,7 +811,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     const bool starve = DBG(32) && (kb & 7);  // timing experiment: copies only on every eighth block
                     const bool ld_p = do_p && !starve, ld_q = do_q && !starve && !(DBG(8) && (kb & 1));  // 8: Q on even blocks only
                     const int c0 = kb * BK;
-                    if (elect_one()) {
+                    if (issuer) {
                         if (rank == 0)
                             mbar_arrive_expect_tx(local_bar,
                                                   CTAS * ((ld_p ? Cfg::A_BYTES : 0) + (ld_q ? Cfg::B_BYTES : 0)));
@@ -818,7 +819,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                         if (ld_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
                         if (issued == 0 && do_p) PROF_MARK(1);
                     }
-                    __syncwarp();
                     ++issued;
                     stage = next_stage;
                     phase = next_phase;
@@ -859,6 +859,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             (void)pair_mask;
             // as in the producers: the next stage's barrier is probed while this stage's MMAs are issued
             bool ready = mbar_test_wait(smem_u32(&ctrl->full[0]), 0);
+            const bool issuer = elect_one();  // one lane, the same for the whole loop (tcgen05.commit tracks the
+                                              // MMAs of the thread that executes it)
 #ifdef B200_PROFILE
             long long tw[5] = {0, 0, 0, 0, 0}, tq_prev = clock64();
 #endif
@@ -887,7 +889,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     // only the 14-bit start-address field of a descriptor changes from stage to stage and
                     // from one UMMA_K step to the next: add to the low word
                     const uint32_t st_off = (stage * Cfg::STAGE_BYTES) >> 4;
-                    if (elect_one()) {
+                    if (issuer) {
                         if (i == 0 && kb == w.kb0) PROF_MARK(2);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -909,7 +911,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                             else umma_commit(smem_u32(&ctrl->tmem_full[acc]));
                         }
                     }
-                    __syncwarp();
                     stage = next_stage;
                     phase = next_phase;
                 }
