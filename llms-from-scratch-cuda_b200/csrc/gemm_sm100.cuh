@@ -21,10 +21,12 @@
 // Work schedule ("slot" = a CTA, or a CTA pair): the first `dp_tiles` output tiles are
 // computed whole, round-robin over the slots.  The remaining tiles — the ragged last
 // wave, or every tile when the output alone cannot fill the GPU — are each cut into
-// `sk_splits` ranges of the contraction; every range is one work item that leaves an fp32
-// partial tile in the workspace, and the CTA whose partial arrives last adds all of them up
-// in a fixed order (so results do not depend on arrival order), applies beta and writes the
-// tile.  Nobody waits for anybody: only the last arriver does the reduction.
+// `sk_splits` ranges of the contraction, one work item each, and summed in a fixed order (member
+// order, not arrival order, so results are the same from run to run) in one of three ways:
+// peer split (the ranges of a tile all run at once: they exchange fp32 slices through the
+// workspace and each reduces and writes its own columns), last arriver (whole partial tiles
+// parked in the workspace, the last to arrive adds them up), or cluster split (p.ksplit: the
+// ranges are one thread-block cluster and exchange through distributed shared memory).
 #pragma once
 #include <cstddef>
 #include <cuda_bf16.h>
@@ -57,7 +59,7 @@ struct GemmParams {
     int ksplit;              // > 1: a cluster of CTAS*ksplit CTAs shares each tile, every member takes one
                              // range of the contraction and the sum is formed through distributed smem
     int p_3d, q_3d;          // MN-major operand described by a 3-D map: one copy per stage
-    int one_producer;        // 1: a single thread issues the copies of both operands
+    int one_producer;        // 1: one warp issues the copies of both operands
     void* out;               // bf16 [Mo,No]
     float* ws;               // split partials: sk_items * CTAS blocks of BM x BN fp32
     int* sk_counters;        // one arrival counter per (split tile, CTA of the pair); zero between launches
