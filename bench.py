@@ -281,8 +281,10 @@ def run_ours(args):
             l0 = h.launches - launches_in_graph
             us = e0.elapsed_time(e1) / reps * 1e3
             fl = 2.0 * TOKENS * b["N"] * b["K"]
+            # algorithmic bytes: both operands and the output once (the beta = 1 output twice), 2 bytes each
+            nbytes = 2.0 * (TOKENS * b["K"] + b["K"] * b["N"] + TOKENS * b["N"]) + (2.0 * b["K"] * b["N"] if kind == "wgrad_tn" else 0.0)
             rec = {"proj": b["name"], "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1),
-                   "launches_per_call": (h.launches - l0) // reps}
+                   "hbm_gbs": round(nbytes / us / 1e3, 1), "launches_per_call": (h.launches - l0) // reps}
             per.append(rec)
             if dominant is None or us > dominant["us"]:
                 dominant = dict(rec, flop=fl)
@@ -300,6 +302,7 @@ def run_ours(args):
                 "unit": "TFLOP/s", "frac": round(dominant["flop"] / dominant["us"] / 1e6 / peaks["bf16_tflops"], 4),
                 "peak_source": peaks["source"] + " (burst: kernel timed alone)",
                 "share_of_step": round(dominant["us"] / total_us, 3), "traffic": ncu_traffic(dominant),
+                "hbm_peak_gbs": peaks["hbm_gbs"],  # secondary bound: compare per_gemm[].hbm_gbs for the thin k/v shapes
                 "step_frac_of_sustained": round(value / world / peaks["bf16_tflops_sustained"], 4)}
 
     cpu = cpu_baseline_port()
