@@ -103,6 +103,36 @@ def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False
     return ref_bin, our_bin
 
 
+def build_train_dp(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False):
+    """oracle/_ref/train_dp_b200_<model>: the data-parallel driver of the package
+    (llms-from-scratch-cuda_b200/csrc/train_dp.cpp) linked with the reference's unmodified model.cpp,
+    dataloader.cpp and kernel objects (the ones build_train compiles, without main.cpp and matmul.cu),
+    libb200_linear.so, the cuBLAS stand-in and NCCL.  None when the checkout, nvcc or nccl.h is absent."""
+    out_dir = os.path.join(HERE, "_ref")
+    tag = model.replace("-", "_")
+    out = os.path.join(out_dir, "train_dp_b200_" + tag)
+    cuda_dir = os.path.join(reference, "cuda")
+    src_dir = os.path.join(reference, model, "src")
+    pkg = os.path.join(os.path.dirname(HERE), "llms-from-scratch-cuda_b200")
+    driver = os.path.join(pkg, "csrc", "train_dp.cpp")
+    if not os.path.isdir(src_dir) or shutil.which("nvcc") is None or not os.path.exists("/usr/include/nccl.h"):
+        return out if os.path.exists(out) else None
+    ref_bin, our_bin = build_train(reference, model, force)
+    if our_bin is None:
+        return None
+    obj_dir = os.path.join(out_dir, "obj_" + tag)
+    objs = [os.path.join(obj_dir, f + ".o") for f in KERNEL_SOURCES + ["model.cpp", "dataloader.cpp"]]
+    ours = [os.path.join(pkg, "libb200_linear.so"), os.path.join(pkg, "libb200_cublas_shim.so")]
+    if not force and _newer(out, objs + ours + [driver]):
+        return out
+    drv_obj = os.path.join(obj_dir, "train_dp.cpp.o")
+    subprocess.run(["nvcc", "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-I", cuda_dir, "-I", src_dir,
+                    "-x", "cu", "-c", driver, "-o", drv_obj], check=True)
+    subprocess.run(["nvcc", "-o", out, drv_obj] + objs + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim", "-lnccl",
+                   "-Xlinker", "-rpath=$ORIGIN/../../llms-from-scratch-cuda_b200"], check=True)
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=DEFAULT_REFERENCE)
@@ -111,3 +141,4 @@ if __name__ == "__main__":
     print(build_oracle(a.force))
     print(build_reference(a.reference, a.force))
     print(build_train(a.reference, "llama2-mistral", a.force))
+    print(build_train_dp(a.reference, "llama2-mistral", a.force))

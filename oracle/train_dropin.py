@@ -72,6 +72,37 @@ def throughput(steps=2):
     return res
 
 
+TOKS_RE = re.compile(r"step\s+(\d+) \| loss [0-9.naif-]+ \|.*\| (\d+) tok/s")
+
+
+def dp_binary(model="llama2_mistral"):
+    p = os.path.join(REF, "train_dp_b200_" + model)
+    return p if os.path.exists(p) else None
+
+
+def data_parallel(ranks_list=(1, 2), steps=3, batch=16, accum=4, lr="3e-4", warmup="20"):
+    """The package's data-parallel driver (csrc/train_dp.cpp around the reference's ModelBF16) on the same token
+    stream at every rank count: losses per step and the wall-clock tokens/s it prints for steps 2..S."""
+    b = dp_binary()
+    if not b:
+        raise FileNotFoundError("oracle/_ref/train_dp_b200_* not built")
+    res = {}
+    with tempfile.TemporaryDirectory() as d:
+        data = os.path.join(d, "data.bin")
+        write_tokens(data, batch * 512 * accum * steps + 1)
+        for r in ranks_list:
+            out = run(b, data, ["--ranks", str(r), "--steps", str(steps), "--batch", str(batch), "--accum", str(accum),
+                                "--lr", lr, "--warmup", warmup], d)
+            toks = [int(m.group(2)) for m in TOKS_RE.finditer(out["tail"])]
+            out["tokens_per_s"] = toks[-1] if toks else None
+            res[r] = out
+    return res
+
+
 if __name__ == "__main__":
     mode = sys.argv[1] if len(sys.argv) > 1 else "overfit"
-    print(json.dumps(overfit() if mode == "overfit" else throughput(int(sys.argv[2]) if len(sys.argv) > 2 else 2)))
+    if mode == "dp":
+        print(json.dumps(data_parallel(tuple(int(x) for x in sys.argv[2].split(",")) if len(sys.argv) > 2 else (1, 2),
+                                       *(int(x) for x in sys.argv[3:6]))))
+    else:
+        print(json.dumps(overfit() if mode == "overfit" else throughput(int(sys.argv[2]) if len(sys.argv) > 2 else 2)))
