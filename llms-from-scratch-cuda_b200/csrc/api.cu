@@ -754,7 +754,10 @@ int gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float
     if (which == B200_GEMM_FWD_NN) { Mo = M; No = N; Kc = K; p_mn = false; q_mn = true; }
     else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
     else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
-    const int bn = No > 64 ? 128 : 64;
+    // 128-wide tiles unless they would leave more than half of the SMs without a tile (this kernel does not split
+    // the contraction): 64-wide tiles then put twice as many SMs to work.
+    const long long tiles128 = 1LL * ceil_div_i(Mo, BM) * ceil_div_i(No, 128);
+    const int bn = (No > 64 && tiles128 * 2 > ctx->sm_count) ? 128 : 64;
     GemmParams gp = {};
     gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
     gp.m_tiles = ceil_div_i(Mo, BM);
