@@ -48,6 +48,11 @@ int b200_linear_set_stream(b200_linear_ctx* ctx, void* cuda_stream);
 /* Synchronise the context's stream and return B200_E_DEVICE_WAIT if any kernel since the last
  * call recorded a timed-out wait (the raw device code is stored in *device_code if non-null). */
 int b200_linear_sync(b200_linear_ctx* ctx, int* device_code);
+/* Self-test of the error path above, with no counterpart in the reference: launches one warp that waits
+ * (at most limit_cycles SM clocks, at most about a second) on a barrier that nothing completes.  The wait
+ * gives up, the kernel records its code and returns; the next b200_linear_sync reports
+ * B200_E_DEVICE_WAIT and clears it, and the context stays usable.  Nothing faults or hangs. */
+int b200_linear_selftest_wait_timeout(b200_linear_ctx* ctx, long long limit_cycles);
 /* Number of kernels this library has launched on this context so far. */
 long long b200_linear_launch_count(const b200_linear_ctx* ctx);
 int b200_linear_last_cuda_error(const b200_linear_ctx* ctx);
@@ -78,6 +83,14 @@ int b200_linear_gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out,
                           const void* y, int M, int N, int K);
 int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x,
                          const float* y, int M, int N, int K);
+/* The bf16 product on operands that are column ranges of wider row-major matrices: ld_out, ld_x, ld_y are
+ * the row pitches in elements (0 = dense).  This is how one rank multiplies by its vocabulary shard of the
+ * LM head w_out[K, V] (llama2-mistral/src/model.cpp:612,635) where it lies: y = w_out + col0, ld_y = V,
+ * N = the shard's width; likewise out = dw_out + col0 for the weight gradient.  Pitches must be multiples
+ * of 8 elements, pointers 16-byte aligned and N, K multiples of 8 (B200_E_BADARG otherwise: the CUDA-core
+ * kernel behind the dense entry points takes dense operands only). */
+int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int beta1, void* out, long long ld_out,
+                             const void* x, long long ld_x, const void* y, long long ld_y, int M, int N, int K);
 
 /* Tuning / introspection.  A plan is what the dispatcher would launch for a bf16 product:
  * tile width BN (output columns per tile; 0 = CUDA-core kernel), cta_pair (1 = 256-row tiles
@@ -116,16 +129,22 @@ int b200_linear_force_backward_split(b200_linear_ctx* ctx, int sm_dgrad);
  * stall of cudaMalloc/cudaFree when a context's workspace would have to grow.  It needs no
  * context: its split-K scratch is a fixed array of about 8 MiB inside the library image, resident on
  * every GPU that loads the library until the process exits.
- *   - Limit: ceil(K/128) * ceil(N/128) <= 128 output tiles (e.g. 768x2048 or 2048x4096); larger
- *     outputs return B200_E_TOOBIG.  N and K must be multiples of 8 and the pointers 16-byte
+ *   - Limit: ceil(K/128) * ceil(N/128) <= 128 output tiles (e.g. 768x2048 or 1024x2048; the 2048x4096
+ *     of a fused gate/up gradient and the LM head do not fit); larger outputs return B200_E_TOOBIG.  N and K must be multiples of 8 and the pointers 16-byte
  *     aligned (B200_E_BADARG otherwise; there is no slower fallback behind this call).
  *   - The first call on each device looks up the array's device address and configures the
- *     kernel; make that first call outside any stream capture.
+ *     kernel (under a lock, so threads may race for it); make that first call outside any stream capture.
  *   - All calls on a device share the one array: two calls whose kernels can run at the same time
  *     (different streams) race.  Calls on one stream are safe; each clears the counters it needs.
- *   - Asynchronous on `cuda_stream` (a cudaStream_t; NULL = legacy default stream). */
+ *   - Asynchronous on `cuda_stream` (a cudaStream_t; NULL = legacy default stream).
+ *   - Its kernels' waits are bounded like all others; one that runs out leaves a code in a status word
+ *     inside the same array, which stays set until b200_linear_noalloc_status reads it. */
 int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const void* dC, int M, int N, int K,
                                    void* cuda_stream);
+/* Waits for `cuda_stream`, then returns B200_E_DEVICE_WAIT (raw code in *device_code, may be NULL) if a
+ * kernel of b200_linear_wgrad_bf16_noalloc gave up on a wait on the current device since the last call,
+ * and clears the word; B200_OK otherwise.  Allocates nothing either.  No counterpart in the reference. */
+int b200_linear_noalloc_status(int* device_code, void* cuda_stream);
 
 /* Cross-entropy when the LM head [K, V] is sharded by columns across GPUs (one process per GPU): the
  * per-shard device kernels.  They replace crossentropy_forward / crossentropy_softmax_backward

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <unordered_map>
 
 #include "../../include/b200_linear.h"
@@ -29,9 +30,10 @@ struct TmKey {
     const void* ptr;
     uint64_t inner, outer;
     uint32_t box_inner, box_outer;
+    uint64_t ld;  // row pitch in elements
     bool operator==(const TmKey& o) const {
         return ptr == o.ptr && inner == o.inner && outer == o.outer && box_inner == o.box_inner &&
-               box_outer == o.box_outer;
+               box_outer == o.box_outer && ld == o.ld;
     }
 };
 struct TmKeyHash {
@@ -40,6 +42,7 @@ struct TmKeyHash {
         h ^= (k.inner + 0x7F4A7C15u) * 0xBF58476D1CE4E5B9ull;
         h ^= (k.outer + 0x1CE4E5B9u) * 0x94D049BB133111EBull;
         h ^= (static_cast<uint64_t>(k.box_inner) << 32 | k.box_outer) * 0xD6E8FEB86659FD93ull;
+        h ^= (k.ld + 0x6659FD93u) * 0xC2B2AE3D27D4EB4Full;
         return static_cast<size_t>(h ^ (h >> 29));
     }
 };
@@ -59,14 +62,11 @@ struct b200_linear_ctx {
     int* status_dev = nullptr;
     int* sk_counters = nullptr;     // arrival counters of split tiles (zero between launches)
     int sk_counters_len = 0;
-    long long* prof_dev = nullptr;  // role cycle counters (profiling builds only; else unused)
-    int dbg = 0;                    // timing-experiment switches (profiling builds only)
     long long launches = 0;
     int last_cuda = 0;
     int force_bn = -1, force_pair = 0, force_splits = 0;
     int use_pdl = 1;
     int no_peer_split = 0;
-    int one_producer = 0;
     int overlap_backward = 1;
     int partition_backward = 1;  // 0: dgrad and wgrad both plan for the whole GPU (wgrad still fills dgrad's tail)
     int force_sm_dgrad = 0;      // > 0: dgrad's share of the SMs in matmul_backward, whatever the cost model says
@@ -89,18 +89,19 @@ int cuda_fail(b200_linear_ctx* ctx, cudaError_t e) {
         if (e__ != cudaSuccess) return cuda_fail((ctx), e__); \
     } while (0)
 
-// bf16 2-D tensor map over a row-major [outer][inner] matrix; 128-byte swizzle for 64-element-wide
-// boxes, 64-byte swizzle for 32-element-wide ones.
+// bf16 2-D tensor map over a row-major [outer][inner] matrix whose rows are `ld` elements apart (0 = dense:
+// ld = inner); 128-byte swizzle for 64-element-wide boxes, 64-byte swizzle for 32-element-wide ones.
 int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
-                   uint32_t box_outer, CUtensorMap* out) {
-    TmKey key{ptr, inner, outer, box_inner, box_outer};
+                   uint32_t box_outer, CUtensorMap* out, uint64_t ld = 0) {
+    if (ld == 0) ld = inner;
+    TmKey key{ptr, inner, outer, box_inner, box_outer, ld};
     auto it = ctx->tm_cache.find(key);
     if (it != ctx->tm_cache.end()) {
         *out = it->second;
         return B200_OK;
     }
     cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner * 2};
+    cuuint64_t strides[1] = {ld * 2};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
@@ -119,7 +120,7 @@ int get_tensor_map(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64
 // fp32 2-D tensor map over a row-major [outer][inner] matrix, box {32 elements = 128 bytes, box_outer}.
 int get_tensor_map_f32(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_outer,
                        CUtensorMap* out, bool atom32 = false) {
-    TmKey key{ptr, inner, outer, (atom32 ? 0x48000u : 0x40000u) + 32u, box_outer};
+    TmKey key{ptr, inner, outer, (atom32 ? 0x48000u : 0x40000u) + 32u, box_outer, inner};
     auto it = ctx->tm_cache.find(key);
     if (it != ctx->tm_cache.end()) {
         *out = it->second;
@@ -144,7 +145,7 @@ int get_tensor_map_f32(b200_linear_ctx* ctx, const void* ptr, uint64_t inner, ui
 // fp32 MN-major operand [Kc][rows] (rows a multiple of 32) seen as {32 elements, Kc, rows/32 panels}.
 int get_panel_map_f32(b200_linear_ctx* ctx, const void* ptr, uint64_t rows, uint64_t kc, uint32_t panels,
                       CUtensorMap* out) {
-    TmKey key{ptr, rows, kc, 0x50000u + panels, T32_BK};
+    TmKey key{ptr, rows, kc, 0x50000u + panels, T32_BK, rows};
     auto it = ctx->tm_cache.find(key);
     if (it != ctx->tm_cache.end()) {
         *out = it->second;
@@ -180,6 +181,15 @@ int ensure_workspace(b200_linear_ctx* ctx, size_t bytes, int set = 0) {
 }
 
 inline int ceil_div_i(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
+
+constexpr int kMaxDevices = 64;
+
+// A context belongs to the device that was current when it was created; its kernels, scratch memory and
+// tensor maps are that device's.  Calls made with another device current are refused.
+bool on_context_device(const b200_linear_ctx* ctx) {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess && dev == ctx->device;
+}
 
 }  // namespace
 
@@ -367,15 +377,16 @@ namespace {
 // MN-major operand [Kc][rows] (rows a multiple of 64) seen as {64 elements, Kc, rows/64 panels}
 // so that one copy brings every 64-wide panel of a stage into its own 128B-swizzled block.
 int get_panel_map(b200_linear_ctx* ctx, const void* ptr, uint64_t rows, uint64_t kc, uint32_t panels,
-                  CUtensorMap* out) {
-    TmKey key{ptr, rows, kc, 0x30000u + panels, BK};
+                  CUtensorMap* out, uint64_t ld = 0) {
+    if (ld == 0) ld = rows;
+    TmKey key{ptr, rows, kc, 0x30000u + panels, BK, ld};
     auto it = ctx->tm_cache.find(key);
     if (it != ctx->tm_cache.end()) {
         *out = it->second;
         return B200_OK;
     }
     cuuint64_t dims[3] = {64, kc, rows / 64};
-    cuuint64_t strides[2] = {rows * 2, 128};
+    cuuint64_t strides[2] = {ld * 2, 128};
     cuuint32_t box[3] = {64, BK, panels};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = ctx->encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box,
@@ -414,11 +425,12 @@ int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& 
             CTAS * gp.ksplit > 8)
             return B200_E_BADARG;
     }
-    static bool configured = false;
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the function
+    static bool configured[kMaxDevices] = {};
     auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, BETA1, CTAS>;
-    if (!configured) {
+    if (!configured[ctx->device]) {
         CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        configured = true;
+        configured[ctx->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -521,10 +533,25 @@ void split_sms_for_backward(b200_linear_ctx* ctx, int M, int N, int K, int* sm_d
 // input gradient of the same matmul_backward).  The kernel then starts on whatever SMs that kernel
 // has already left and only waits for it before it finishes itself, so that completion order, and with it
 // every later kernel's view of memory, stays what the stream promises.
+// ld_out / ld_x / ld_y: row pitch in elements of the output and of the two inputs (0 = dense, the inner
+// extent), for operands that are column ranges of a wider matrix (a vocabulary shard of the LM head).
 int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x, const void* y, int M,
-              int N, int K, int overlap_prev = 0, int sm_limit = 0) {
+              int N, int K, int overlap_prev = 0, int sm_limit = 0, long long ld_out = 0, long long ld_x = 0,
+              long long ld_y = 0) {
     if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2)
         return B200_E_BADARG;
+    if (!on_context_device(ctx)) return B200_E_BADARG;
+    {   // inner extents of out, x, y for this product
+        const long long in_out = which == B200_GEMM_DGRAD_NT ? K : N;
+        const long long in_x = which == B200_GEMM_DGRAD_NT ? N : K;
+        const long long in_y = N;
+        if ((ld_out && ld_out < in_out) || (ld_x && ld_x < in_x) || (ld_y && ld_y < in_y)) return B200_E_BADARG;
+        if (ld_out == in_out) ld_out = 0;
+        if (ld_x == in_x) ld_x = 0;
+        if (ld_y == in_y) ld_y = 0;
+    }
+    const bool pitched = ld_out || ld_x || ld_y;
+    if (pitched && ((ld_out | ld_x | ld_y) % 8) != 0) return B200_E_BADARG;  // TMA needs 16-byte row pitches
     // sm_limit > 0: plan for, and occupy, only that many SMs (a concurrent kernel has the others)
     const int sm_count = (sm_limit > 0 && sm_limit < ctx->sm_count) ? sm_limit : ctx->sm_count;
     b200_linear_plan_t plan;
@@ -532,6 +559,7 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     if (rc) return rc;
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
                              reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    if ((plan.bn == 0 || !aligned16) && pitched) return B200_E_BADARG;  // the CUDA-core kernel takes dense operands only
     if (plan.bn == 0 || !aligned16)
         return launch_simt<__nv_bfloat16>(ctx, which, beta1, static_cast<__nv_bfloat16*>(out),
                                           static_cast<const __nv_bfloat16*>(x),
@@ -578,11 +606,8 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
     gp.ksplit = ksplit;
     gp.late_wait = (overlap_prev && ctx->use_pdl && ctx->overlap_backward) ? 1 : 0;
-    gp.one_producer = ctx->one_producer;
     gp.out = out;
     gp.status = ctx->status_dev;
-    gp.prof = ctx->prof_dev;
-    gp.dbg = ctx->dbg;
     gp.ws = nullptr;
     gp.sk_counters = nullptr;
     gp.sk_peer = 0;
@@ -614,20 +639,20 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     CUtensorMap tmP, tmQ, tmD;
     gp.p_3d = p_mn && (Mo % 64) == 0;
     gp.q_3d = q_mn && (No % 64) == 0;
-    if (gp.p_3d) rc = get_panel_map(ctx, P, Mo, Kc, BM / 64, &tmP);
-    else if (p_mn) rc = get_tensor_map(ctx, P, Mo, Kc, 64, BK, &tmP);
-    else rc = get_tensor_map(ctx, P, Kc, Mo, BK, BM, &tmP);
+    if (gp.p_3d) rc = get_panel_map(ctx, P, Mo, Kc, BM / 64, &tmP, ld_x);
+    else if (p_mn) rc = get_tensor_map(ctx, P, Mo, Kc, 64, BK, &tmP, ld_x);
+    else rc = get_tensor_map(ctx, P, Kc, Mo, BK, BM, &tmP, ld_x);
     if (rc) return rc;
-    if (gp.q_3d) rc = get_panel_map(ctx, Q, No, Kc, bn / ctas / 64, &tmQ);
-    else if (q_mn) rc = get_tensor_map(ctx, Q, No, Kc, 64, BK, &tmQ);
-    else rc = get_tensor_map(ctx, Q, Kc, No, BK, bn / ctas, &tmQ);
+    if (gp.q_3d) rc = get_panel_map(ctx, Q, No, Kc, bn / ctas / 64, &tmQ, ld_y);
+    else if (q_mn) rc = get_tensor_map(ctx, Q, No, Kc, 64, BK, &tmQ, ld_y);
+    else rc = get_tensor_map(ctx, Q, Kc, No, BK, bn / ctas, &tmQ, ld_y);
     if (rc) return rc;
     // Output map for the epilogue's TMA stores: [Mo][No] bf16, box = 64 columns x 32 rows.
-    rc = get_tensor_map(ctx, out, No, Mo, 64, 32, &tmD);
+    rc = get_tensor_map(ctx, out, No, Mo, 64, 32, &tmD, ld_out);
     if (rc) return rc;
     CUtensorMap tmD32 = tmD;  // 32-column blocks: the cluster-split and peer-split epilogues use it
     if (ksplit > 1 || gp.sk_peer) {
-        rc = get_tensor_map(ctx, out, No, Mo, 32, 32, &tmD32);
+        rc = get_tensor_map(ctx, out, No, Mo, 32, 32, &tmD32, ld_out);
         if (rc) return rc;
     }
 
@@ -709,11 +734,11 @@ template <int BN, bool P_MN, bool Q_MN, bool BETA1>
 int launch_tf32x3(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
                   const GemmParams& gp, int grid) {
     using Cfg = T32Cfg<BN>;
-    static bool configured = false;
+    static bool configured[kMaxDevices] = {};
     auto kern = gemm_tf32x3_sm100<BN, P_MN, Q_MN, BETA1>;
-    if (!configured) {
+    if (!configured[ctx->device]) {
         CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        configured = true;
+        configured[ctx->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -745,6 +770,7 @@ int launch_tf32x3_variants(b200_linear_ctx* ctx, int bn, int beta1, const CUtens
 int gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x, const float* y, int M, int N,
              int K) {
     if (!ctx || !out || !x || !y || M <= 0 || N <= 0 || K <= 0 || which < 0 || which > 2) return B200_E_BADARG;
+    if (!on_context_device(ctx)) return B200_E_BADARG;
     const bool aligned16 = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) |
                              reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     if (ctx->fp32_simt || !aligned16 || (N % 4) != 0 || (K % 4) != 0)
@@ -769,7 +795,6 @@ int gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float
     if (tiles > 0x7FFFFFFFLL) return B200_E_TOOBIG;
     gp.dp_tiles = static_cast<int>(tiles);
     gp.sk_splits = 1; gp.kb_per_sk = gp.kb_total; gp.sk_items = 0; gp.sk_peer = 0; gp.ksplit = 1; gp.late_wait = 0;
-    gp.one_producer = 0;
     gp.out = out;
     gp.status = ctx->status_dev;
     gp.p_3d = p_mn && (Mo % 32) == 0;
@@ -799,7 +824,7 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     if (!out) return B200_E_BADARG;
     *out = nullptr;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return B200_E_NODEVICE;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_E_NODEVICE;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return B200_E_NODEVICE;
     if (prop.major != 10) return B200_E_NODEVICE;  // tcgen05 / TMEM exist on sm_100 only
@@ -816,7 +841,6 @@ extern "C" int b200_linear_create(b200_linear_ctx** out) {
     ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
     if (const char* e = getenv("B200_LINEAR_PDL")) ctx->use_pdl = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_PEER_SPLIT")) ctx->no_peer_split = atoi(e) == 0;
-    if (const char* e = getenv("B200_LINEAR_ONE_PRODUCER")) ctx->one_producer = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_OVERLAP_BACKWARD")) ctx->overlap_backward = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_PARTITION_BACKWARD")) ctx->partition_backward = atoi(e) != 0;
     if (const char* e = getenv("B200_LINEAR_TILE_GROUP")) ctx->tile_group = atoi(e);
@@ -844,7 +868,6 @@ extern "C" int b200_linear_destroy(b200_linear_ctx* ctx) {
     if (ctx->sk_counters) cudaFree(ctx->sk_counters);
     if (ctx->ws2) cudaFree(ctx->ws2);
     if (ctx->sk_counters2) cudaFree(ctx->sk_counters2);
-    if (ctx->prof_dev) cudaFree(ctx->prof_dev);
     delete ctx;
     return B200_OK;
 }
@@ -870,6 +893,15 @@ extern "C" int b200_linear_sync(b200_linear_ctx* ctx, int* device_code) {
     return B200_OK;
 }
 
+extern "C" int b200_linear_selftest_wait_timeout(b200_linear_ctx* ctx, long long limit_cycles) {
+    if (!ctx || limit_cycles <= 0 || limit_cycles > WAIT_LIMIT_CYCLES) return B200_E_BADARG;
+    if (!on_context_device(ctx)) return B200_E_BADARG;
+    wait_timeout_probe<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, limit_cycles, DEV_TIMEOUT_FULL);
+    CU_TRY(ctx, cudaGetLastError());
+    ctx->launches++;
+    return B200_OK;
+}
+
 extern "C" long long b200_linear_launch_count(const b200_linear_ctx* ctx) { return ctx ? ctx->launches : -1; }
 extern "C" int b200_linear_last_cuda_error(const b200_linear_ctx* ctx) { return ctx ? ctx->last_cuda : -1; }
 
@@ -884,69 +916,6 @@ extern "C" const char* b200_linear_strerror(int code) {
         default: return "unknown error";
     }
 }
-
-#ifdef B200_PROFILE
-// Profiling builds only: how many clusters of `cluster` CTAs of the wgrad kernel can be resident.
-extern "C" int b200_linear_debug_max_clusters(int bn, int ctas, int cluster) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = -1;
-    cudaError_t e;
-    if (bn == 256 && ctas == 1) {
-        auto k = gemm_bf16_sm100<256, true, true, true, 1>;
-        cfg.dynamicSmemBytes = TileCfg<256, 1>::SMEM_BYTES;
-        cfg.gridDim = dim3(cluster * 64, 1, 1);
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.dynamicSmemBytes);
-        e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
-    } else if (bn == 256 && ctas == 2) {
-        auto k = gemm_bf16_sm100<256, true, true, true, 2>;
-        cfg.dynamicSmemBytes = TileCfg<256, 2>::SMEM_BYTES;
-        cfg.gridDim = dim3(cluster * 64, 1, 1);
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.dynamicSmemBytes);
-        e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
-    } else {
-        auto k = gemm_bf16_sm100<128, true, true, true, 1>;
-        cfg.dynamicSmemBytes = TileCfg<128, 1>::SMEM_BYTES;
-        cfg.gridDim = dim3(cluster * 64, 1, 1);
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, cfg.dynamicSmemBytes);
-        e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
-    }
-    return e == cudaSuccess ? n : -static_cast<int>(e);
-}
-extern "C" int b200_linear_debug_flags(b200_linear_ctx* ctx, int flags) {
-    if (!ctx) return B200_E_BADARG;
-    ctx->dbg = flags;
-    return B200_OK;
-}
-// Profiling builds only: copies the 16 role cycle counters of CTA 0 of the last tensor-core kernel.
-extern "C" int b200_linear_debug_prof(b200_linear_ctx* ctx, long long* out16) {
-    if (!ctx || !out16) return B200_E_BADARG;
-    if (!ctx->prof_dev) {
-        CU_TRY(ctx, cudaMalloc(&ctx->prof_dev, (64 + 16 * 512) * sizeof(long long)));
-        CU_TRY(ctx, cudaMemset(ctx->prof_dev, 0, (64 + 16 * 512) * sizeof(long long)));
-    }
-    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    CU_TRY(ctx, cudaMemcpy(out16, ctx->prof_dev, 32 * sizeof(long long), cudaMemcpyDeviceToHost));
-    CU_TRY(ctx, cudaMemset(ctx->prof_dev + 16, 0, 16 * sizeof(long long)));
-    CU_TRY(ctx, cudaMemset(ctx->prof_dev + 20, 0xFF, sizeof(long long)));
-    return B200_OK;
-}
-// per-CTA timeline of the last launches: 16 global-timer stamps for each of the first 512 CTAs
-extern "C" int b200_linear_debug_timeline(b200_linear_ctx* ctx, long long* out, int clear) {
-    if (!ctx || !out || !ctx->prof_dev) return B200_E_BADARG;
-    CU_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    CU_TRY(ctx, cudaMemcpy(out, ctx->prof_dev + 64, 16 * 512 * sizeof(long long), cudaMemcpyDeviceToHost));
-    if (clear) CU_TRY(ctx, cudaMemset(ctx->prof_dev + 64, 0, 16 * 512 * sizeof(long long)));
-    return B200_OK;
-}
-#endif
 
 extern "C" int b200_linear_force_backward_split(b200_linear_ctx* ctx, int sm_dgrad) {
     if (!ctx || sm_dgrad < 0 || sm_dgrad >= ctx->sm_count) return B200_E_BADARG;
@@ -968,6 +937,12 @@ extern "C" int b200_linear_force_plan(b200_linear_ctx* ctx, int bn, int cta_pair
 extern "C" int b200_linear_gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void* x,
                                      const void* y, int M, int N, int K) {
     return gemm_bf16(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K);
+}
+extern "C" int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int beta1, void* out, long long ld_out,
+                                        const void* x, long long ld_x, const void* y, long long ld_y, int M, int N,
+                                        int K) {
+    if (ld_out < 0 || ld_x < 0 || ld_y < 0) return B200_E_BADARG;
+    return gemm_bf16(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K, 0, 0, ld_out, ld_x, ld_y);
 }
 extern "C" int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x,
                                     const float* y, int M, int N, int K) {
@@ -1026,7 +1001,7 @@ constexpr int NA_COUNTERS = 256;
 struct NoAllocScratch {
     float partials[static_cast<size_t>(NA_MAX_ITEMS) * BM * NA_BN];  // 8 MiB
     int counters[NA_COUNTERS];
-    int status;
+    int status;  // sticky: only b200_linear_noalloc_status clears it
 };
 
 struct NoAllocDevice {
@@ -1035,7 +1010,8 @@ struct NoAllocDevice {
     int sm_count = 0;
     EncodeTiledFn encode = nullptr;
 };
-NoAllocDevice g_noalloc_dev[64];
+NoAllocDevice g_noalloc_dev[kMaxDevices];
+std::mutex g_noalloc_mutex;  // guards the once-per-device set-up below
 
 }  // namespace
 
@@ -1050,10 +1026,11 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
         ((reinterpret_cast<uintptr_t>(dB) | reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(dC)) & 15) != 0)
         return B200_E_BADARG;  // no CUDA-core fallback here: TMA needs 16-byte pitches and pointers
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_E_NODEVICE;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_E_NODEVICE;
     NoAllocDevice& nd = g_noalloc_dev[dev];
     using Cfg = TileCfg<NA_BN, 1>;
     auto kern = gemm_bf16_sm100<NA_BN, true, true, true, 1>;
+    std::unique_lock<std::mutex> setup_lock(g_noalloc_mutex);
     if (!nd.ready) {  // once per device, with that device current
         int major = 0, sms = 0;
         if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
@@ -1074,6 +1051,7 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
         nd.encode = reinterpret_cast<EncodeTiledFn>(fn);
         nd.ready = true;
     }
+    setup_lock.unlock();
     const int Mo = K, No = N, Kc = M;  // output rows/cols, contraction over the tokens
     const int tiles = ceil_div_i(Mo, BM) * ceil_div_i(No, NA_BN);
     if (tiles > NA_MAX_ITEMS || tiles > NA_COUNTERS) return B200_E_TOOBIG;
@@ -1097,15 +1075,12 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     gp.ksplit = 1;
     gp.late_wait = 0;
     gp.sk_peer = 0;
-    gp.one_producer = 0;
     gp.p_3d = (Mo % 64) == 0;
     gp.q_3d = (No % 64) == 0;
     gp.out = dB;
     gp.ws = nd.scratch->partials;
     gp.sk_counters = nd.scratch->counters;
     gp.status = &nd.scratch->status;
-    gp.prof = nullptr;
-    gp.dbg = 0;
 
     auto encode = [&](CUtensorMap* tm, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
                       const cuuint32_t* box) {
@@ -1135,8 +1110,9 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
         const cuuint32_t box[2] = {64, 32};
         if (!encode(&tmD, dB, 2, dims, strides, box)) return B200_E_CUDA;
     }
-    // The array keeps whatever the previous call left: the counters and the status word must start at zero.
-    if (cudaMemsetAsync(nd.scratch->counters, 0, sizeof(int) * (NA_COUNTERS + 1), stream) != cudaSuccess)
+    // The array keeps whatever the previous call left: the arrival counters must start at zero.  The status
+    // word is left alone, so that a wait that ran out in an earlier call stays visible until it is read.
+    if (cudaMemsetAsync(nd.scratch->counters, 0, sizeof(int) * NA_COUNTERS, stream) != cudaSuccess)
         return B200_E_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -1152,6 +1128,28 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     cfg.numAttrs = 1;
     if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD, gp) != cudaSuccess) return B200_E_CUDA;
     return B200_OK;
+}
+
+// Waits for `cuda_stream`, then reads (and clears) the status word that the kernels of
+// b200_linear_wgrad_bf16_noalloc write when one of their bounded waits runs out.  Allocates nothing: the
+// word lives in the fixed scratch array and is copied straight into *device_code.
+extern "C" int b200_linear_noalloc_status(int* device_code, void* cuda_stream) {
+    if (device_code) *device_code = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200_E_NODEVICE;
+    NoAllocScratch* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (g_noalloc_dev[dev].ready) scratch = g_noalloc_dev[dev].scratch;
+    }
+    if (cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream)) != cudaSuccess) return B200_E_CUDA;
+    if (!scratch) return B200_OK;  // the entry point has not run on this device yet: nothing to report
+    int code = 0;
+    if (cudaMemcpy(&code, &scratch->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return B200_E_CUDA;
+    if (device_code) *device_code = code;
+    if (code == 0) return B200_OK;
+    if (cudaMemset(&scratch->status, 0, sizeof(int)) != cudaSuccess) return B200_E_CUDA;
+    return B200_E_DEVICE_WAIT;
 }
 
 // ---------------------------------------------------------------- vocabulary-sharded cross-entropy

@@ -27,7 +27,10 @@ namespace b200 {
 
 constexpr int CE_THREADS = 256;
 
+// A logit of -inf (a masked column) contributes nothing; without the guards below a row or a lane's share
+// that is all -inf would compute exp(-inf - -inf) = exp(NaN).
 __device__ __forceinline__ void ce_online_add(float& m, float& s, float x) {
+    if (x == -INFINITY) return;
     if (x > m) {
         s = s * __expf(m - x) + 1.0f;  // exp(-inf) = 0 covers the first element
         m = x;
@@ -59,6 +62,7 @@ __device__ __forceinline__ void ce_add_vec8(float& m, float& s, const uint4& u) 
         s *= __expf(m - vm);  // exp(-inf) = 0 covers the first vector
         m = vm;
     }
+    if (m == -INFINITY) return;  // everything so far is masked: nothing to add
     float add = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) add += __expf(x[j] - m);

@@ -154,8 +154,10 @@ gemm_simt(const SimtParams p) {
                 reinterpret_cast<float*>(p.out)[static_cast<size_t>(split) * p.Mo * p.No + idx] = acc[i][j];
             } else {
                 T* o = reinterpret_cast<T*>(p.out);
-                const float old = p.beta1 ? to_f32<T>(o[idx]) : 0.f;
-                o[idx] = from_f32<T>(acc[i][j] + old);
+                // beta = 1 rounds like the tensor-core path and the reference's cuBLAS: the product is rounded
+                // to the storage type before the old value is added (a no-op for fp32)
+                o[idx] = p.beta1 ? from_f32<T>(to_f32<T>(from_f32<T>(acc[i][j])) + to_f32<T>(o[idx]))
+                                 : from_f32<T>(acc[i][j]);
             }
         }
     }
@@ -169,7 +171,7 @@ __global__ void splitk_reduce_generic(T* __restrict__ out, const float* __restri
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         float a = 0.f;
         for (int s = 0; s < splits; ++s) a += ws[s * n + i];
-        if (beta1) a += to_f32<T>(out[i]);
+        if (beta1) a = to_f32<T>(from_f32<T>(a)) + to_f32<T>(out[i]);  // product rounded first, as above
         out[i] = from_f32<T>(a);
     }
 }

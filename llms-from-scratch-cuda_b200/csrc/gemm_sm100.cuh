@@ -59,35 +59,11 @@ struct GemmParams {
     int ksplit;              // > 1: a cluster of CTAS*ksplit CTAs shares each tile, every member takes one
                              // range of the contraction and the sum is formed through distributed smem
     int p_3d, q_3d;          // MN-major operand described by a 3-D map: one copy per stage
-    int one_producer;        // 1: one warp issues the copies of both operands
     void* out;               // bf16 [Mo,No]
     float* ws;               // split partials: sk_items * CTAS blocks of BM x BN fp32
     int* sk_counters;        // one arrival counter per (split tile, CTA of the pair); zero between launches
     int* status;             // device status word (0 = ok)
-    long long* prof;         // cycle counters of CTA 0 (only read by builds with B200_PROFILE)
-    int dbg;                 // timing experiments (only read by builds with B200_PROFILE; results are wrong)
 };
-
-#ifdef B200_PROFILE
-#define PROF_WRITE(idx, val) do { if (p.prof && blockIdx.x == 0) p.prof[idx] = (val); } while (0)
-__device__ __forceinline__ unsigned long long prof_globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// per-CTA timeline in nanoseconds of the global timer: prof[64 + 16 * block + idx]
-#define PROF_MARK(idx) do { PROF_WRITE(idx, clock64() - t_kernel); \
-    if (p.prof && blockIdx.x < 512) p.prof[64 + 16 * blockIdx.x + (idx)] = (long long)prof_globaltimer(); } while (0)
-#define PROF_T(name) const long long name = clock64()
-#define PROF_MAX(idx, val) do { if (p.prof) atomicMax((unsigned long long*)&p.prof[idx], (unsigned long long)(val)); } while (0)
-#define DBG(bit) (p.dbg & (bit))
-#else
-#define PROF_WRITE(idx, val)
-#define PROF_MARK(idx)
-#define PROF_T(name)
-#define PROF_MAX(idx, val)
-#define DBG(bit) false
-#endif
 
 template <int BN, int CTAS>
 struct TileCfg {
@@ -419,7 +395,6 @@ __device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, Gemm
     const uint32_t recv_base = smem_u32(recv);
     const int trow = q * 32 + lane;               // row of the tile this thread owns
 
-    PROF_T(tc0);
     if (warp == 4 && lane == 0) {
         mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((S - 1) * (my_g1 - my_g0)) * 32u * BM * 4u);
         for (int d = 0; d < S; ++d)
@@ -429,7 +404,6 @@ __device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, Gemm
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
 
-    PROF_T(tc1);
     // send: my partial sums of every other member's column groups
     for (int dd = 1; dd < S; ++dd) {
         const int d = (krank + dd) % S;           // start with the next member: spreads the traffic
@@ -451,12 +425,10 @@ __device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, Gemm
         }
     }
 
-    PROF_T(tc2);
     // receive, then sum my own column groups in member order
     ok = mbar_wait<true>(recv_bar, 0, abort_flag, p.status, DEV_TIMEOUT_PEER);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
-    PROF_T(tc3);
     // The output goes out in 32 x 32 blocks through the warp's staging buffer (64-byte swizzle) and
     // a TMA store; with beta = 1 the old block comes in by TMA first and is updated in place.
 #pragma unroll 1
@@ -486,10 +458,6 @@ __device__ __forceinline__ bool epilogue_cluster_split(const GemmParams& p, Gemm
         }
         if (!block32_finish<BETA1>(p, tmD32, buf, acc, old_bar, old_phase, col0, row0, lane, abort_flag)) return false;
     }
-    PROF_T(tc4);
-    if (warp == 4 && lane == 0) {
-        PROF_MAX(16, tc1 - tc0); PROF_MAX(17, tc2 - tc1); PROF_MAX(18, tc3 - tc2); PROF_MAX(19, tc4 - tc3);
-    }
     return true;
 }
 
@@ -518,7 +486,6 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
     auto block_of = [&](int dest, int slot, int gi) {
         return region + static_cast<size_t>((dest * (S - 1) + slot) * maxg + gi) * BLOCK_FLOATS;
     };
-    PROF_T(tc0);
     for (int dd = 1; dd < S; ++dd) {
         const int d = (me + dd) % S;
         const int slot = me < d ? me : me - 1;
@@ -534,7 +501,6 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
                 *reinterpret_cast<uint4*>(dst + j * BM * 4) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         }
     }
-    PROF_T(tc1);
     // publish, then wait for the other members
     __threadfence();
     __syncwarp();
@@ -564,7 +530,6 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
     ok = __all_sync(0xffffffffu, ok) && ctrl->sk_last;
     if (!ok) return false;
     __threadfence();
-    PROF_T(tc2);
 #pragma unroll 1
     for (int g = my_g0 + hsel; g < my_g1; g += 2) {
         const int col0 = n0 + g * 32;
@@ -613,7 +578,6 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
         }
         if (!block32_finish<BETA1>(p, tmD32, buf, acc, old_bar, old_phase, col0, row0, lane, abort_flag)) return false;
     }
-    PROF_T(tc3);
     // everybody has read: the member that counts last puts the counter back to zero
     __syncwarp();
     if (lane == 0) mbar_arrive(smem_u32(&ctrl->sk_read));
@@ -622,7 +586,6 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
             const int prev = atomicAdd(counter, 1);
             if (prev == 2 * S - 1) atomicExch(counter, 0);
         }
-        PROF_MAX(16, tc1 - tc0); PROF_MAX(17, tc2 - tc1); PROF_MAX(18, tc3 - tc2);
     }
     return true;
 }
@@ -646,16 +609,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     uint8_t* epi_bufs = tiles + STAGES * Cfg::STAGE_BYTES;  // per epilogue warp: 2 staging buffers
     volatile int* abort_flag = &ctrl->abort_flag;
 
-#ifdef B200_PROFILE
-    const long long t_kernel = clock64();
-    if (threadIdx.x == 0) PROF_MARK(8);
-    unsigned long long g_kernel;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_kernel));
-    if (threadIdx.x == 0 && p.prof) {
-        atomicMin((unsigned long long*)&p.prof[20], g_kernel);
-        atomicMax((unsigned long long*)&p.prof[21], g_kernel);
-    }
-#endif
     // read through a shuffle so that the compiler treats the warp index (and everything derived from
     // it: the role, the TMEM lane quarter, the staging buffer) as uniform across the warp
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -674,7 +627,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         static_assert(offsetof(GemmCtrl, cs_recv) == (N_BARS - 1) * 8, "barrier list and control block disagree");
         for (int b = lane; b < N_BARS; b += 32) {
             uint32_t count = 1;  // empty[], tmem_full[], sk_decided, old_bar[], cs_recv
-            if (b < 8) count = p.one_producer ? 1 : 2;  // full[]: one arrival (+ byte count) per producer warp
+            if (b < 8) count = 2;  // full[]: one arrival (+ byte count) per producer warp
             else if (b >= 16 && b < 18) count = 1;
             else if (b >= 18 && b < 20) count = EPI_WARPS * CTAS;         // tmem_empty[]
             else if (b == 20 || b == 22) count = EPI_WARPS;                // sk_written, sk_read
@@ -728,14 +681,15 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // L2 is the point of coherence for device memory, so a line fetched early is still current when the
     // copies into shared memory read it after the wait; inside the step the operands come from HBM (the
     // working set is far larger than L2) and this takes their first-touch latency off the critical path.
-    if ((warp == 0 || warp == 3) && have_first && !p.late_wait && !(p.one_producer && warp == 3)) {
+    if ((warp == 0 || warp == 3) && have_first && !p.late_wait) {
         if (elect_one()) {
             WorkItem w = w_first;
             narrow_to_krank(p, krank, w);
             const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
             const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
             const int kb_end = min(w.kb1, w.kb0 + STAGES);
-            for (int is_q = (warp == 0 ? 0 : 1); is_q <= ((warp == 3 || p.one_producer) ? 1 : 0); ++is_q) {
+            {
+                const bool is_q = warp == 3;
                 const CUtensorMap* tm = is_q ? &tmQ : &tmP;
                 const bool mn = is_q ? Q_MN : P_MN;
                 const bool as3d = is_q ? (p.q_3d != 0) : (p.p_3d != 0);
@@ -752,10 +706,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         }
         __syncwarp();
     }
-    if (threadIdx.x == 0) PROF_MARK(9);
     if (!p.late_wait) griddep_wait();
     griddep_launch_dependents();
-    if (threadIdx.x == 0) PROF_MARK(0);
 
     // The three issuing roles below run with all 32 lanes of their warp converged: every lane waits on the
     // barriers and does the (warp-uniform) address arithmetic, and one elected lane issues the copies, the
@@ -763,10 +715,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // lane inside a divergent branch cost several hundred cycles per 64-deep block just to issue.
     if (warp == 0 || warp == 3) {
         // ---------------------------------------------- TMA producers: warp 0 feeds P, warp 3 feeds Q
-        // (with p.one_producer, warp 0 feeds both and warp 3 idles)
-        const bool one = p.one_producer != 0;
-        if (!(one && warp == 3)) {
-            const bool do_p = warp == 0, do_q = one || warp == 3;
+        {
+            const bool do_p = warp == 0, do_q = warp == 3;
             uint32_t stage = 0, phase = 0;
             uint32_t issued = 0;  // number of stage fills issued so far
             bool ok = true;
@@ -810,16 +760,12 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     const uint32_t local_bar = smem_u32(&ctrl->full[stage]);
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
-                    const bool starve = DBG(32) && (kb & 7);  // timing experiment: copies only on every eighth block
-                    const bool ld_p = do_p && !starve, ld_q = do_q && !starve && !(DBG(8) && (kb & 1));  // 8: Q on even blocks only
                     const int c0 = kb * BK;
                     if (issuer) {
                         if (rank == 0)
-                            mbar_arrive_expect_tx(local_bar,
-                                                  CTAS * ((ld_p ? Cfg::A_BYTES : 0) + (ld_q ? Cfg::B_BYTES : 0)));
-                        if (ld_p) issue(false, sP, bar, m0, c0);
-                        if (ld_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
-                        if (issued == 0 && do_p) PROF_MARK(1);
+                            mbar_arrive_expect_tx(local_bar, CTAS * (do_p ? Cfg::A_BYTES : Cfg::B_BYTES));
+                        if (do_p) issue(false, sP, bar, m0, c0);
+                        if (do_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
                     }
                     ++issued;
                     stage = next_stage;
@@ -863,9 +809,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             bool ready = mbar_test_wait(smem_u32(&ctrl->full[0]), 0);
             const bool issuer = elect_one();  // one lane, the same for the whole loop (tcgen05.commit tracks the
                                               // MMAs of the thread that executes it)
-#ifdef B200_PROFILE
-            long long tw[5] = {0, 0, 0, 0, 0}, tq_prev = clock64();
-#endif
             for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 const uint32_t acc = i & 1, acc_phase = (i >> 1) & 1;
@@ -876,7 +819,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::ACC_STRIDE;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    PROF_T(tq0);
                     if (!__all_sync(0xffffffffu, ready)) {
                         ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, p.status, DEV_TIMEOUT_FULL);
                         ok = __all_sync(0xffffffffu, ok);
@@ -885,28 +827,20 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     tc_fence_after();
                     const uint32_t next_stage = stage + 1 == STAGES ? 0 : stage + 1;
                     const uint32_t next_phase = next_stage == 0 ? phase ^ 1 : phase;
-                    PROF_T(tq1);
                     ready = mbar_test_wait(smem_u32(&ctrl->full[next_stage]), next_phase);
-                    PROF_T(tq2);
                     // only the 14-bit start-address field of a descriptor changes from stage to stage and
                     // from one UMMA_K step to the next: add to the low word
                     const uint32_t st_off = (stage * Cfg::STAGE_BYTES) >> 4;
                     if (issuer) {
-                        if (i == 0 && kb == w.kb0) PROF_MARK(2);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             const uint64_t dP = descP0 + (st_off + ((k * P_STEP) >> 4));
                             const uint64_t dQ = descQ0 + (st_off + ((k * Q_STEP) >> 4));
-                            if (DBG(4) && k > 0) continue;  // timing experiment: a quarter of the MMAs
                             umma_f16<CTAS>(d_tmem, dP, dQ, idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
                         }
-                        PROF_T(tq3);
                         // frees the stage (in both CTAs of a pair) when the MMAs retire
                         if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->empty[stage]), pair_mask);
                         else umma_commit(smem_u32(&ctrl->empty[stage]));
-#ifdef B200_PROFILE
-                        { const long long tq4 = clock64(); tw[0] += tq1 - tq0; tw[1] += tq2 - tq1; tw[2] += tq3 - tq2; tw[3] += tq4 - tq3; tw[4] += tq0 - tq_prev; tq_prev = tq4; }
-#endif
                         // the accumulator is complete when the last block's MMAs retire
                         if (kb == w.kb1 - 1) {
                             if constexpr (PAIR) umma_commit_2cta(smem_u32(&ctrl->tmem_full[acc]), pair_mask);
@@ -916,13 +850,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     stage = next_stage;
                     phase = next_phase;
                 }
-            }
-#ifdef B200_PROFILE
-            if (elect_one()) for (int j = 0; j < 5; ++j) PROF_WRITE(24 + j, tw[j]);
-#endif
-            if (lane == 0) {
-                PROF_MARK(3);
-                PROF_MAX(22, clock64() - t_kernel);
             }
         }
     } else if (warp >= 4) {
@@ -939,7 +866,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            if (warp == 4 && lane == 0) PROF_MARK(4);  // last item's accumulator ready
             const int row0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM + q * 32;
             const uint32_t taddr = tmem_base + acc * Cfg::ACC_STRIDE + (static_cast<uint32_t>(q * 32) << 16);
             uint8_t* my_buf = epi_bufs + (warp - 4) * (Cfg::EPI_BUFS * EPI_BUF_BYTES);
@@ -958,8 +884,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 release_acc();
                 if (!ok) break;
             } else if (w.sk_item < 0) {
-                if (!DBG(1))
-                    ok = epilogue_store_bf16<BN, BETA1, false, Cfg::EPI_BUFS>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
+                ok = epilogue_store_bf16<BN, BETA1, false, Cfg::EPI_BUFS>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
                                                                w.n_blk * BN, old_bar, old_phase, abort_flag);
                 release_acc();
                 if (!ok) break;
@@ -978,13 +903,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 // One range of a split tile: park the partial, count the arrival, and if every
                 // other range of this tile has already arrived, reduce them all and write the tile.
                 float* block = p.ws + (static_cast<size_t>(w.sk_item) * CTAS + rank) * Cfg::PARTIAL_FLOATS;
-                PROF_T(ts0);
                 epilogue_store_partial<BN>(block, taddr, q, hsel, lane);
                 release_acc();
-                PROF_T(ts1);
                 __threadfence();
                 __syncwarp();
-                PROF_T(ts2);
                 if (lane == 0) mbar_arrive(smem_u32(&ctrl->sk_written));
                 if (warp == 4 && lane == 0) {
                     if (mbar_wait(smem_u32(&ctrl->sk_written), sk_phase, abort_flag, p.status, DEV_TIMEOUT_PEER)) {
@@ -1002,8 +924,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 sk_phase ^= 1;
-                PROF_T(ts3);
-                if (warp == 4 && lane == 0) { PROF_MAX(16, ts1 - ts0); PROF_MAX(17, ts2 - ts1); PROF_MAX(18, ts3 - ts2); }
                 if (ctrl->sk_last) {
                     __threadfence();
                     const float* first = p.ws + (static_cast<size_t>(w.sk_tile) * p.sk_splits * CTAS + rank) *
@@ -1013,8 +933,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                                                               q, hsel, row0, lane, w.n_blk * BN, old_bar, old_phase,
                                                               abort_flag);
                     if (!ok) break;
-                    PROF_T(ts4);
-                    if (warp == 4 && lane == 0) PROF_MAX(19, ts4 - ts3);
                 }
                 // every warp must have read sk_last before the next split item overwrites it
                 __syncwarp();
@@ -1022,9 +940,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         }
         // every TMA store of this warp must have read its staging buffer before the CTA gives up its shared
         // memory; the writes themselves are complete when the grid is
-        if (warp == 4 && lane == 0) PROF_MARK(5);
         if (elect_one()) tma_store_wait_read<0>();
-        if (warp == 4 && lane == 0) PROF_MARK(6);
     }
 
     // ------------------------------------------------------------- teardown
@@ -1034,7 +950,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         cluster_arrive_release();
         cluster_wait_acquire();
     }
-    if (threadIdx.x == 0) PROF_MARK(7);
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc<CTAS>(tmem_base, Cfg::TMEM_COLS);
@@ -1042,15 +957,6 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // A kernel that ran beside its predecessor must not finish before it: whoever waits for this
     // kernel next is entitled to see the predecessor's results as well.
     if (p.late_wait && threadIdx.x == 0) griddep_wait();
-#ifdef B200_PROFILE
-    if (threadIdx.x == 0) {
-        unsigned long long g_end;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_end));
-        PROF_WRITE(9, clock64() - t_kernel);
-        PROF_WRITE(14, (long long)(g_end - g_kernel));
-        if (p.prof && blockIdx.x == 0) { p.prof[13] = p.prof[15]; p.prof[15] = (long long)g_kernel; p.prof[12] = (long long)g_end; }
-    }
-#endif
 }
 
 }  // namespace b200

@@ -29,6 +29,8 @@ namespace {
 constexpr int kMaxDevices = 64;
 b200_linear_ctx* g_ctx[kMaxDevices] = {};
 
+void poll_all_at_exit();
+
 b200_linear_ctx* device_ctx() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
@@ -36,6 +38,11 @@ b200_linear_ctx* device_ctx() {
         exit(EXIT_FAILURE);
     }
     if (!g_ctx[dev]) {
+        static bool registered = false;
+        if (!registered) {
+            registered = true;
+            atexit(poll_all_at_exit);
+        }
         int rc = b200_linear_create(&g_ctx[dev]);
         if (rc != B200_OK) {
             fprintf(stderr, "b200_linear error %s:%d: context creation failed: %s\n", __FILE__, __LINE__,
@@ -46,11 +53,45 @@ b200_linear_ctx* device_ctx() {
     return g_ctx[dev];
 }
 
-void check(int rc, b200_linear_ctx* ctx, const char* what, int line) {
-    if (rc == B200_OK) return;
+void fail(int rc, b200_linear_ctx* ctx, const char* what, int line) {
     fprintf(stderr, "b200_linear error %s:%d: %s: %s (cuda %d)\n", __FILE__, line, what, b200_linear_strerror(rc),
             b200_linear_last_cuda_error(ctx));
     exit(EXIT_FAILURE);
+}
+
+// A kernel whose bounded wait ran out has left its output partly written; the void signatures of the
+// reference have no way to say so.  Every kPollEvery-th call therefore reads the context's device status
+// word (a stream synchronisation and a 4-byte copy; the reference's callers synchronise the device several
+// times per layer themselves, with their cudaFree of temporaries) and ends the program the way the
+// reference ends on any CUDA error.  A process that exits normally is checked once more on the way out.
+constexpr long long kPollEvery = 1024;
+long long g_calls = 0;
+
+void poll_status(b200_linear_ctx* ctx, const char* what, int line) {
+    int code = 0;
+    const int rc = b200_linear_sync(ctx, &code);
+    if (rc == B200_OK) return;
+    fprintf(stderr, "b200_linear: device code %d\n", code);
+    fail(rc, ctx, what, line);
+}
+
+void poll_all_at_exit() {
+    int current = 0;
+    if (cudaGetDevice(&current) != cudaSuccess) return;
+    for (int dev = 0; dev < kMaxDevices; ++dev) {
+        if (!g_ctx[dev]) continue;
+        if (cudaSetDevice(dev) != cudaSuccess) continue;
+        int code = 0;
+        if (b200_linear_sync(g_ctx[dev], &code) == B200_E_DEVICE_WAIT)
+            fprintf(stderr, "b200_linear: a kernel on device %d gave up on a bounded wait (device code %d): "
+                            "results of this run are not to be trusted\n", dev, code);
+    }
+    cudaSetDevice(current);
+}
+
+void check(int rc, b200_linear_ctx* ctx, const char* what, int line) {
+    if (rc != B200_OK) fail(rc, ctx, what, line);
+    if (++g_calls % kPollEvery == 0) poll_status(ctx, what, line);
 }
 
 }  // namespace

@@ -116,19 +116,36 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // of the CTA; `status` is the context's device status word.
 template <bool kCluster = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag, int* status, int code) {
+                                          volatile int* abort_flag, int* status, int code,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES) {
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
         if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if ((++spins & 63u) == 0 && clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        if ((++spins & 63u) == 0 && clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             atomicCAS(status, 0, code);
             return false;
         }
     }
+}
+
+// One warp waits on a barrier phase that nothing will ever complete, with a short limit: the wait gives
+// up, records `code` in the status word and the kernel returns.  This is the whole life of a bounded wait
+// that runs out, made to happen on purpose so that the host side of it (status read-back, clean-up, the
+// next launches on the same context) can be tested without any kernel misbehaving.
+__global__ void wait_timeout_probe(int* status, long long limit_cycles, int code) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, code, limit_cycles);
 }
 
 // ---------------------------------------------------------------------- TMA

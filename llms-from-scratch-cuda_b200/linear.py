@@ -59,6 +59,9 @@ def _load():
         getattr(lib, name).argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci]
     for name in ("b200_linear_gemm_bf16", "b200_linear_gemm_f32"):
         getattr(lib, name).argtypes = [vp, ci, ci, vp, vp, vp, ci, ci, ci]
+    lib.b200_linear_gemm_bf16_ld.argtypes = [vp, ci, ci, vp, ctypes.c_longlong, vp, ctypes.c_longlong, vp,
+                                             ctypes.c_longlong, ci, ci, ci]
+    lib.b200_linear_selftest_wait_timeout.argtypes = [vp, ctypes.c_longlong]
     lib.b200_linear_plan_bf16.argtypes = [ci, ci, ci, ci, ci, ci, ctypes.POINTER(Plan)]
     lib.b200_linear_force_plan.argtypes = [vp, ci, ci, ci]
     lib.b200_linear_force_backward_split.argtypes = [vp, ci]
@@ -128,6 +131,11 @@ class Handle:
         if rc:
             raise LinearError(rc, "b200_linear_sync", f" ({strerror(rc)}; device code {code.value})")
 
+    def selftest_wait_timeout(self, limit_cycles=2_000_000):
+        """Launch the one-warp probe whose bounded wait runs out after `limit_cycles` SM clocks; the
+        next sync() then raises LinearError with code B200_E_DEVICE_WAIT and the handle stays usable."""
+        self._check(lib.b200_linear_selftest_wait_timeout(self._h, int(limit_cycles)), "selftest_wait_timeout")
+
     @property
     def launches(self):
         return int(lib.b200_linear_launch_count(self._h))
@@ -170,6 +178,24 @@ def gemm(handle, which, beta1, out, x, y, M, N, K, dtype=None):
     sfx = dtype or _suffix(out, x, y)
     fn = getattr(lib, "b200_linear_gemm_" + sfx)
     handle._check(fn(handle._h, which, int(bool(beta1)), _ptr(out), _ptr(x), _ptr(y), M, N, K), "gemm")
+
+
+def _ptr_ld(t):
+    """Device address and row pitch (elements) of a 2-D tensor whose rows are contiguous: a dense matrix
+    or a column range of a wider one."""
+    if isinstance(t, tuple):
+        return t
+    if not t.is_cuda or t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise LinearError(1, "argument", " (need a CUDA matrix with contiguous rows)")
+    return t.data_ptr(), t.stride(0)
+
+
+def gemm_ld(handle, which, beta1, out, x, y, M, N, K):
+    """bf16 product on operands with a row pitch: torch views such as W[:, c0:c1] (a vocabulary shard of
+    the LM head where it lies), or (address, pitch) pairs."""
+    (po, lo), (px, lx), (py, ly) = _ptr_ld(out), _ptr_ld(x), _ptr_ld(y)
+    handle._check(lib.b200_linear_gemm_bf16_ld(handle._h, which, int(bool(beta1)), po, lo, px, lx, py, ly, M, N, K),
+                  "gemm_ld")
 
 
 def plan_bf16(which, beta1, M, N, K, sm_count=148):
@@ -234,8 +260,8 @@ def ce_shard_backward(logits, targets, col0, global_max, global_sum, scale, out=
     """dlogits = (exp(l - max) / sum - onehot) * scale for this rank's columns; out=logits works in place."""
     import torch
     rows, cols, ld, stream = _ce_args(logits, targets)
-    if out is None:
-        out = torch.empty_like(logits)
+    if out is None:  # same shape and row pitch as the input, which may be a column range of a wider matrix
+        out = torch.empty_strided(logits.shape, logits.stride(), dtype=logits.dtype, device=logits.device)
     if out.shape != logits.shape or out.stride() != logits.stride() or out.dtype != logits.dtype:
         raise LinearError(1, "ce_shard_backward", "out must match logits")
     _ce_check(lib.b200_ce_shard_backward_bf16(out.data_ptr() if cols else None, logits.data_ptr() if cols else None, rows,

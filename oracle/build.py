@@ -15,7 +15,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = os.environ.get("LFS_CUDA_REFERENCE", "/root/reference")
+# Where the reference checkout lies: --reference, else $LFS_CUDA_REFERENCE, else a directory named
+# "reference" beside this repository.  Where none exists, only prebuilt files under oracle/_ref are used.
+DEFAULT_REFERENCE = os.environ.get("LFS_CUDA_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target, sources):

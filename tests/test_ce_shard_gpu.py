@@ -64,6 +64,37 @@ def test_ragged_and_empty_shards_combine(pkg, handle):
     assert (d.float() - d1.float()).abs().max() <= 2.0 ** -8 * d1.float().abs().max()
 
 
+def test_masked_columns_and_fully_masked_shard(pkg, handle):
+    """Logits of -inf (masked vocabulary entries): a shard whose columns are all masked, and rows in which
+    one lane's share of the columns is masked, must contribute zero -- not exp(-inf - -inf) = NaN."""
+    g = torch.Generator(device=DEV).manual_seed(19)
+    rows, vocab = 128, 4096
+    logits = (2.0 * torch.randn(rows, vocab, device=DEV, generator=g)).to(torch.bfloat16)
+    logits[:, 1024:2048] = float("-inf")          # the second of four shards is masked entirely
+    logits[3, :1024] = float("-inf")              # a row masked at the start (the running maximum is still -inf)
+    logits[4, ::2] = float("-inf")
+    targets = torch.randint(2048, vocab, (rows,), device=DEV, generator=g, dtype=torch.int32)
+    targets[4] = 2049                             # an unmasked column of the row with every second one masked
+    shards = [(0, 1024), (1024, 1024), (2048, 1024), (3072, 1024)]
+    loss, d = _single_rank(pkg, logits, targets, shards)
+    assert torch.isfinite(loss).all() and torch.isfinite(d.float()).all()
+    _check(loss, d, logits, targets)
+    assert (d[:, 1024:2048] == 0).all()
+
+
+def test_backward_default_output_follows_a_strided_view(pkg, handle):
+    g = torch.Generator(device=DEV).manual_seed(23)
+    rows, vocab, ld = 32, 512, 768
+    big = (2.0 * torch.randn(rows, ld, device=DEV, generator=g)).to(torch.bfloat16)
+    view = big[:, :vocab]
+    targets = torch.randint(0, vocab, (rows,), device=DEV, generator=g, dtype=torch.int32)
+    lm, sm, tg = pkg.ce_shard_stats(view, targets, 0)
+    loss = pkg.ce_shard_loss(lm, sm, tg)
+    d = pkg.ce_shard_backward(view, targets, 0, lm, sm, 1.0 / rows)   # no out=: allocated to match the view
+    torch.cuda.synchronize()
+    _check(loss, d, view.contiguous(), targets)
+
+
 def test_backward_in_place_and_strided(pkg, handle):
     g = torch.Generator(device=DEV).manual_seed(11)
     rows, vocab, ld = 64, 1536, 2048

@@ -207,3 +207,76 @@ def test_misaligned_pointers_take_the_cuda_core_path(pkg, handle):
     handle.sync()
     want = a.double() @ b.double()
     assert ((c.double() - want).abs().max() / want.abs().max()).item() <= 1e-2
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_column_ranges_of_wider_matrices(pkg, handle, which):
+    """Operands with a row pitch: the weight (and its gradient) as a column range of a wider matrix, which is
+    how a rank works on its vocabulary shard of the LM head in place.  Every plan variant the dispatcher may
+    pick for such a shard, plus the automatic one; columns outside the range must stay untouched."""
+    dt = torch.bfloat16
+    g = torch.Generator(device=DEV).manual_seed(321 + which)
+    M, K, V, c0, N = 1024, 768, 2304, 512, 1280
+    a = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    w_full = (0.05 * torch.randn(K, V, device=DEV, generator=g)).to(dt)
+    dc_full = torch.randn(M, V, device=DEV, generator=g).to(dt)      # logits-like buffer, also pitched
+    w, dc = w_full[:, c0:c0 + N], dc_full[:, c0:c0 + N]
+    try:
+        for plan in (None, (256, 1, 0), (128, 0, 2), (192, 0, 0), (128, 0, -2)):
+            if plan:
+                handle.force_plan(*plan)
+            for beta in (0, 1):
+                if which == 0:      # logits shard = a @ w, written into a column range of a [M, V] buffer
+                    out_full = torch.randn(M, V, device=DEV, generator=g).to(dt)
+                    keep = out_full.clone()
+                    out = out_full[:, c0:c0 + N]
+                    want = a.double() @ w.double() + (keep[:, c0:c0 + N].double() if beta else 0)
+                    pkg.gemm_ld(handle, 0, beta, out, a, w, M, N, K)
+                elif which == 1:    # d(input) = dlogits shard @ w^T, dense output
+                    out_full = torch.randn(M, K, device=DEV, generator=g).to(dt)
+                    keep = out_full.clone()
+                    out = out_full
+                    want = dc.double() @ w.double().T + (keep.double() if beta else 0)
+                    pkg.gemm_ld(handle, 1, beta, out, dc, w, M, N, K)
+                else:               # dW shard += a^T @ dlogits shard, written into a column range of dW [K, V]
+                    out_full = torch.randn(K, V, device=DEV, generator=g).to(dt)
+                    keep = out_full.clone()
+                    out = out_full[:, c0:c0 + N]
+                    want = a.double().T @ dc.double() + (keep[:, c0:c0 + N].double() if beta else 0)
+                    pkg.gemm_ld(handle, 2, beta, out, a, dc, M, N, K)
+                handle.sync()
+                err = ((out.double() - want).abs().max() / want.abs().max()).item()
+                assert err <= 1e-2, (which, plan, beta, err)
+                if which != 1:      # nothing outside the column range was written
+                    assert torch.equal(out_full[:, :c0], keep[:, :c0])
+                    assert torch.equal(out_full[:, c0 + N:], keep[:, c0 + N:])
+    finally:
+        handle.force_plan(-1, 0, 0)
+    # pitches the tensor maps cannot describe are refused, not silently mis-read
+    with pytest.raises(pkg.LinearError):
+        pkg.gemm_ld(handle, 0, 0, (a.data_ptr(), N), a, (w.data_ptr(), V + 4), M, N, K)
+    with pytest.raises(pkg.LinearError):
+        pkg.gemm_ld(handle, 0, 0, (a.data_ptr(), N - 8), a, w, M, N, K)
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_the_context_survives(pkg, handle, oracle):
+    """A device wait that gives up: the probe kernel waits about a millisecond on a barrier that nothing
+    completes, records its code and returns.  The next sync reports B200_E_DEVICE_WAIT (code 4) once, clears
+    it, and an ordinary product on the same context is correct afterwards.  Nothing faults or hangs."""
+    handle.sync()
+    handle.selftest_wait_timeout(2_000_000)
+    with pytest.raises(pkg.LinearError) as e:
+        handle.sync()
+    assert e.value.code == 4 and "102" in str(e.value)   # DEV_TIMEOUT_FULL is what the probe records
+    handle.sync()                                          # cleared: the second sync is clean
+    M, N, K = 512, 768, 2048
+    A = oracle.normal((M, K), 71, bf16=True)
+    dC = oracle.normal((M, N), 72, bf16=True)
+    a, dc = (torch.from_numpy(v).to(DEV, torch.bfloat16) for v in (A, dC))
+    db = torch.zeros(K, N, device=DEV, dtype=torch.bfloat16)
+    pkg.gemm(handle, 2, 1, db, a, dc, M, N, K)              # a split product: uses the counters sync() reset
+    handle.sync()
+    want = oracle.gemm_f64(2, A, dC, M, N, K)
+    assert np.abs(db.float().cpu().numpy() - want).max() / np.abs(want).max() <= 1e-2
+    with pytest.raises(pkg.LinearError):
+        handle.selftest_wait_timeout(0)
