@@ -116,6 +116,43 @@ def make_buffers(torch, dev, oracle_mod, host=False):
 
 
 PREHEAT_S = 1.0
+BLOCKS = 10  # the K-step block is timed this many times back to back; value = median block
+
+WORKLOAD = ("configs[1]: decoder-layer projections (Q,K,V,O,gate,up,down) + LM head 768->32000, "
+            "M=8192 tokens (B16xT512), fwd + dgrad + wgrad(beta=1), 24 GEMMs/step")
+
+
+def common_config(world):
+    """The same keys in both arms, so that the two lines describe one configuration."""
+    return {"workload": WORKLOAD,
+            "l2": "no flush: the step's working set (~1.7 GB, every GEMM its own buffers) exceeds the 126 MB L2",
+            "preheat": "%.1f s of untimed steps right before the timed region, in both arms (thermal / power-cap steady state)" % PREHEAT_S,
+            "timing": "%d blocks of --steps steps back to back, CUDA events around each block; value and ms_per_step "
+                      "are the median block (maximum over ranks per block), ms_per_step_min/max the spread" % BLOCKS,
+            "parallelism": "dp%d by tokens, dW all-reduce (NCCL) every %d micro-batches" % (world, ACCUM),
+            "flop_per_step": STEP_FLOP}
+
+
+def time_blocks(torch, step_fn, steps, after_step=None):
+    """BLOCKS blocks of `steps` steps, one CUDA event between blocks (no host synchronisation inside the region).
+    Returns the list of block durations in milliseconds."""
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(BLOCKS + 1)]
+    ev[0].record()
+    n = 0
+    for b in range(BLOCKS):
+        for _ in range(steps):
+            step_fn()
+            n += 1
+            if after_step is not None:
+                after_step(n)
+        ev[b + 1].record()
+    torch.cuda.synchronize()
+    return [ev[b].elapsed_time(ev[b + 1]) for b in range(BLOCKS)]
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2] if len(xs) % 2 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2])
 
 
 def preheat(torch, step_fn, seconds=PREHEAT_S):
@@ -217,24 +254,22 @@ def run_ours(args):
     launches0 = h.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.time()
-    e0.record()
-    for i in range(args.steps):
-        step_device()
-        if (i + 1) % ACCUM == 0:
+
+    def after_step(n):  # the dW exchange, once per ACCUM micro-batches (at least once per block)
+        if n % ACCUM == 0 or (args.steps < ACCUM and n % args.steps == 0):
             exchange()
-    if args.steps % ACCUM != 0:
-        exchange()  # the exchange is inside the timed region at least once
-    e1.record()
+
+    block_ms = time_blocks(torch, step_device, args.steps, after_step)
     barrier()
     t1 = time.time()
     h.sync()
-    ms = e0.elapsed_time(e1)
-    launches = h.launches - launches0
+    launches = (h.launches - launches0) // BLOCKS
     clocks = sampler.stop(t0, t1) if rank == 0 else None
     if world > 1:
-        t = torch.tensor([ms], device=dev)
+        t = torch.tensor(block_ms, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
+        block_ms = t.tolist()
+    ms = median(block_ms)
     value = world * args.steps * STEP_FLOP / (ms * 1e-3) / 1e12
 
     # ---- end to end: host buffers in, host buffers out, through the same calls
@@ -245,9 +280,16 @@ def run_ours(args):
         ms_e2e = t.item()
     e2e_value = world * e2e_steps * STEP_FLOP / (ms_e2e * 1e-3) / 1e12
 
+    # ---- the vocabulary-sharded LM head + cross-entropy of configs[3] on these ranks (a sub-record)
+    vocab_parallel = run_vocab_parallel(torch, dist, pkg, h, dev, world, rank) if args.vocab_parallel else None
+    # ---- a whole training step of the 125M model through the multi-GPU driver (a sub-record)
+    train_step = run_train_step(dist, world, rank, args) if args.train_step else None
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
+        if vocab_parallel is not None and not vocab_parallel.get("parity_ok", True):
+            sys.exit(3)
         return
 
     # ---- per-GEMM timing (rank 0): CUDA events on the launching stream, each GEMM alone
@@ -287,7 +329,7 @@ def run_ours(args):
                    "hbm_gbs": round(nbytes / us / 1e3, 1), "launches_per_call": (h.launches - l0) // reps}
             per.append(rec)
             if dominant is None or us > dominant["us"]:
-                dominant = dict(rec, flop=fl)
+                dominant = dict(rec, flop=fl, N=b["N"], K=b["K"])
     h.sync()
     h.set_stream(torch.cuda.current_stream())
     in_step = None
@@ -301,21 +343,22 @@ def run_ours(args):
                 "achieved": round(dominant["flop"] / dominant["us"] / 1e6, 1), "peak": peaks["bf16_tflops"],
                 "unit": "TFLOP/s", "frac": round(dominant["flop"] / dominant["us"] / 1e6 / peaks["bf16_tflops"], 4),
                 "peak_source": peaks["source"] + " (burst: kernel timed alone)",
-                "share_of_step": round(dominant["us"] / total_us, 3), "traffic": ncu_traffic(dominant),
+                "share_of_step": round(dominant["us"] / total_us, 3), "traffic": None,
+                "traffic_note": "DRAM bytes per launch come from an ncu capture, not from this run: see the kernel's summary "
+                                "under profiles/ (a capture at full size is too large to take under the profiler)",
+                "algorithmic_bytes": int(2.0 * (TOKENS * dominant["K"] + dominant["K"] * dominant["N"] + TOKENS * dominant["N"]) +
+                                         (2.0 * dominant["K"] * dominant["N"] if dominant["gemm"] == "wgrad_tn" else 0.0)),
                 "hbm_peak_gbs": peaks["hbm_gbs"],  # secondary bound: compare per_gemm[].hbm_gbs for the thin k/v shapes
                 "step_frac_of_sustained": round(value / world / peaks["bf16_tflops_sustained"], 4)}
 
     cpu = cpu_baseline_port()
     line = {"metric": "bf16 GEMM TFLOP/s, all linear-layer GEMMs of one 125M decoder layer + LM head, fwd+bwd",
             "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": round(ms / args.steps, 4), "ms_per_step_min": round(min(block_ms) / args.steps, 4),
+            "ms_per_step_max": round(max(block_ms) / args.steps, 4), "blocks": BLOCKS,
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[1]: decoder-layer projections (Q,K,V,O,gate,up,down) + LM head 768->32000, "
-                                   "M=8192 tokens (B16xT512), fwd + dgrad + wgrad(beta=1), 24 GEMMs/step",
-                       "l2": "no flush: the step's working set (~1.7 GB, every GEMM its own buffers) exceeds the 126 MB L2",
-                       "preheat": "%.1f s of untimed steps right before the timed region, in both arms (thermal / power-cap steady state)" % PREHEAT_S,
-                       "parallelism": "dp%d by tokens, dW all-reduce (NCCL) every %d micro-batches" % (world, ACCUM),
-                       "flop_per_step": STEP_FLOP},
+            "config": common_config(world),
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -323,21 +366,170 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per}
     if in_step:
         line["in_step_us"] = in_step
+    if vocab_parallel is not None:
+        line["vocab_parallel"] = vocab_parallel
+    if train_step is not None:
+        line["train_step"] = train_step
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if vocab_parallel is not None and not vocab_parallel.get("parity_ok", True):
+        sys.exit(3)
 
 
-def ncu_traffic(rec):
-    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, from the
-    committed ncu capture of its 2048-token case (profiles/gemm_bf16_sm100_lm_head_fwd_tokens2048.md:
-    132.1 MB for 183.0 MB of algorithmic bytes), scaled to the launch at hand by the algorithmic bytes
-    (traffic grows in proportion: every operand byte is read from DRAM once, the output written once)."""
-    if rec["proj"] != "lm_head" or rec["gemm"] != "fwd_nn":
-        return None
-    n, k = 32000, 768
-    algorithmic = 2.0 * (TOKENS * k + k * n + TOKENS * n)
-    return int(132.1e6 / 183.0e6 * algorithmic)
+def run_vocab_parallel(torch, dist, pkg, h, dev, world, rank):
+    """The LM head of BASELINE.json configs[3] (LLaMA-3 272M: 16384 tokens = B2 x T8192, vocabulary 128256, K = 768)
+    sharded by vocabulary over the ranks of this run, forward + cross-entropy + backward, as the multi-GPU driver
+    runs it (csrc/train_dp.cpp; replaces llama2-mistral/src/model.cpp:612-614,634-635 in that mode): every rank
+    multiplies by its own 256-column tiles of w_out where they lie (pitched operands), the row maxima and the sums
+    of exponentials cross the ranks in two small all-reduces, dlogits is formed in place, the weight gradient lands
+    in the rank's own columns of dw_out and the input gradient is summed over the ranks.  Total work is fixed
+    (strong scaling); every rank also runs the whole vocabulary alone once (n1_ms) for the efficiency figure.
+    A small case is checked against float64 first: parity_ok False makes the run exit non-zero."""
+    import importlib
+    dmod = importlib.import_module(pkg.__name__ + ".dist")
+    rows, V, K = 16384, 128256, 768
+    shards = dmod.vocab_shards(V, world)
+
+    def lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange):
+        n_rows = x.shape[0]
+        pkg.gemm_ld(h, pkg.FWD_NN, 0, logits, x, w[:, col0:col0 + cols], n_rows, cols, x.shape[1])
+        loss, d = dmod.vocab_parallel_cross_entropy(logits, targets, col0, in_place=True, exchange=exchange)
+        pkg.gemm_ld(h, pkg.DGRAD_NT, 0, dx, d, w[:, col0:col0 + cols], n_rows, cols, x.shape[1])
+        pkg.gemm_ld(h, pkg.WGRAD_TN, 1, dw[:, col0:col0 + cols], x, d, n_rows, cols, x.shape[1])
+        if exchange:
+            dmod.reduce_input_gradient(dx)
+        return loss
+
+    # ---- parity on a small case (every rank computes it; the float64 result on the host)
+    g = torch.Generator(device="cpu").manual_seed(99)
+    r_s, v_s, k_s = 512, 2048 + 256 * world, 256
+    xs = torch.randn(r_s, k_s, generator=g).to(torch.bfloat16)
+    ws = (0.05 * torch.randn(k_s, v_s, generator=g)).to(torch.bfloat16)
+    ts = torch.randint(0, v_s, (r_s,), generator=g, dtype=torch.int32)
+    s_col0, s_cols = dmod.vocab_shards(v_s, world)[rank]
+    x_d, w_d, t_d = xs.to(dev), ws.to(dev), ts.to(dev)
+    dw_d = torch.zeros(k_s, v_s, device=dev, dtype=torch.bfloat16)
+    lg_d = torch.empty(r_s, s_cols, device=dev, dtype=torch.bfloat16)
+    dx_d = torch.empty(r_s, k_s, device=dev, dtype=torch.bfloat16)
+    loss_s = lm_head(x_d, w_d, dw_d, t_d, lg_d, dx_d, s_col0, s_cols, True)
+    h.sync()
+    if world > 1:
+        dist.all_reduce(dw_d)  # every rank wrote its own columns only
+    l64 = (xs.double() @ ws.double()).to(torch.bfloat16).double()  # the logits as the GEMM stores them
+    loss64 = torch.logsumexp(l64, 1) - l64.gather(1, ts.long()[:, None]).squeeze(1)
+    d64 = torch.softmax(l64, 1)
+    d64[torch.arange(r_s), ts.long()] -= 1.0
+    d64 /= r_s
+    dx64, dw64 = d64 @ ws.double().T, xs.double().T @ d64
+    e_loss = (loss_s.double().cpu() - loss64).abs().max().item()
+    e_dx = ((dx_d.double().cpu() - dx64).abs().max() / dx64.abs().max()).item()
+    e_dw = ((dw_d.double().cpu() - dw64).abs().max() / dw64.abs().max()).item()
+    ok = torch.tensor([1 if (e_loss <= 5e-3 and e_dx <= 2e-2 and e_dw <= 2e-2) else 0], device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    parity = {"parity_ok": bool(ok.item()), "loss_abs_err": round(e_loss, 6), "dx_rel_err": round(e_dx, 5),
+              "dw_rel_err": round(e_dw, 5), "case": "rows %d, vocabulary %d, K %d vs float64" % (r_s, v_s, k_s),
+              "tolerance": "loss 5e-3 abs, dX and dW 2e-2 of their maximum (bf16 dlogits)"}
+    del x_d, w_d, dw_d, lg_d, dx_d
+
+    # ---- timing at configs[3] size
+    g = torch.Generator(device=dev).manual_seed(4321)
+    x = torch.randn(rows, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(K, V, device=dev, generator=g)).to(torch.bfloat16)
+    dw = torch.zeros(K, V, device=dev, dtype=torch.bfloat16)
+    targets = torch.randint(0, V, (rows,), device=dev, generator=g, dtype=torch.int32)
+    dx = torch.empty(rows, K, device=dev, dtype=torch.bfloat16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(col0, cols, exchange, reps=5):
+        logits = torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
+        for _ in range(2):
+            lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange)
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        del logits
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    col0, cols = shards[rank]
+    ms = timed(col0, cols, True)
+    n1_ms = ms if world == 1 else timed(0, V, False, reps=3)
+    h.sync()
+    flop = 3 * 2.0 * rows * V * K
+    rec = {"workload": "configs[3] LM head: 16384 tokens x 128256 vocabulary x 768, forward + cross-entropy + dgrad + wgrad(beta=1), "
+                       "vocabulary sharded in whole 256-column tiles over %d rank(s)" % world,
+           "ranks": world, "ms": round(ms, 3), "tflops": round(flop / ms / 1e9, 1), "n1_ms": round(n1_ms, 3),
+           "efficiency_vs_n1": round(n1_ms / (world * ms), 3), "scaling": "strong",
+           "columns_per_rank": [n for _, n in shards],
+           "exchange_bytes_per_rank": {"all_reduce_max_fp32": rows * 4, "all_reduce_sum_fp32": 2 * rows * 4,
+                                       "all_reduce_dx_bf16": rows * K * 2},
+           "logits_bytes_per_rank": rows * cols * 2}
+    rec.update(parity)
+    return rec
+
+
+def run_train_step(dist, world, rank, args):
+    """The metric's second half: tokens/s of a whole LLaMA-2/Mistral-125M training step (B=16, T=512, 16 micro-batches
+    = 131072 tokens per optimizer step, bf16, AdamW) on the ranks of this run, through the package's multi-GPU
+    driver csrc/train_dp.cpp (the reference's own model objects with this library's linear layers, one process per
+    GPU, NCCL gradient sum).  Rank 0 starts the driver, which forks its own ranks; the ranks of this benchmark hold
+    no kernels meanwhile (they wait on the host).  Present only where the binary was built."""
+    import tempfile
+    binary = os.path.join(ROOT, "oracle", "_ref", "train_dp_b200_llama2_mistral")
+    store = None
+    if world > 1:
+        from torch.distributed.distributed_c10d import _get_default_store
+        store = _get_default_store()
+    rec = None
+    if rank == 0:
+        if not os.path.exists(binary):
+            rec = {"unavailable": "driver binary not built (needs the reference checkout at build time)"}
+        else:
+            import re
+            import numpy as np
+            steps, batch, seq, accum = 2, 16, 512, 16
+            with tempfile.TemporaryDirectory() as d:
+                data = os.path.join(d, "tokens.bin")
+                np.random.default_rng(42).integers(0, 32000, batch * seq * accum * steps + 1, dtype=np.int32).tofile(data)
+                t0 = time.time()
+                try:
+                    out = subprocess.run([binary, data, "--ranks", str(world), "--steps", str(steps), "--batch", str(batch),
+                                          "--seq", str(seq), "--accum", str(accum), "--timers"], cwd=d, capture_output=True,
+                                         text=True, timeout=args.train_step_timeout)
+                    text, rc = out.stdout, out.returncode
+                except subprocess.TimeoutExpired:
+                    text, rc = "", -1
+                wall = time.time() - t0
+            toks = re.findall(r"\| (\d+) tok/s", text)
+            losses = [float(x) for x in re.findall(r"loss ([0-9.]+)", text)]
+            phases = re.search(r"phases, seconds per step.*?: (.*)", text)
+            if rc != 0 or not toks:
+                rec = {"unavailable": "driver run failed (rc %d)" % rc, "tail": text[-300:]}
+            else:
+                rec = {"metric": "LLaMA-125M train tok/s", "tokens_per_s": int(toks[-1]), "ranks": world,
+                       "tokens_per_step": batch * seq * accum, "steps": steps, "timed": "wall clock of step 2 (step 1 carries set-up)",
+                       "losses": losses, "phases_s_per_step": phases.group(1) if phases else None, "wall_s": round(wall, 1),
+                       "what": "csrc/train_dp.cpp around the reference's ModelBF16, linear layers from this library, "
+                               "micro-batches dealt to the ranks, one NCCL gradient sum per step"}
+        if store is not None:
+            store.set("b200_train_step_done", "1")
+    elif store is not None:
+        import datetime
+        store.wait(["b200_train_step_done"], datetime.timedelta(seconds=args.train_step_timeout + 60))
+    return rec
 
 
 def step_breakdown(torch, calls, steps=20):
@@ -437,13 +629,9 @@ def run_reference(args):
     preheat(torch, step)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.time()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
+    block_ms = time_blocks(torch, step, args.steps)
     t1 = time.time()
-    ms = e0.elapsed_time(e1)
+    ms = median(block_ms)
     value = args.steps * STEP_FLOP / (ms * 1e-3) / 1e12
     ms_e2e, e2e_steps, h2d, d2h = time_e2e(torch, bufs, step, args.steps, torch.cuda.synchronize)
     e2e_value = e2e_steps * STEP_FLOP / (ms_e2e * 1e-3) / 1e12
@@ -466,11 +654,10 @@ def run_reference(args):
         calls += [(b["name"] + ":bwd", (lambda b=b: lib.ref_matmul_backward_bf16(hd, b["dA"].data_ptr(), b["dB"].data_ptr(), b["dC"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"]))) for b in reversed(bufs)]
         base["in_step_us"] = step_breakdown(torch, calls)
     base.update({"value": round(value, 2), "dtype": "bf16", "ms_per_step": round(ms / args.steps, 4),
-                 "config": {"workload": "configs[1]: decoder-layer projections (Q,K,V,O,gate,up,down) + LM head 768->32000, "
-                                        "M=8192 tokens (B16xT512), fwd + dgrad + wgrad(beta=1), 24 GEMMs/step",
-                            "implementation": "reference cuda/matmul.cu unmodified (cuBLAS) on the same GPU; the reference has no CPU implementation of this path",
-                            "preheat": "%.1f s of untimed steps right before the timed region, in both arms (thermal / power-cap steady state)" % PREHEAT_S,
-                            "flop_per_step": STEP_FLOP},
+                 "ms_per_step_min": round(min(block_ms) / args.steps, 4), "ms_per_step_max": round(max(block_ms) / args.steps, 4),
+                 "blocks": BLOCKS,
+                 "implementation": "reference cuda/matmul.cu unmodified (cuBLAS) on the same GPU; the reference has no CPU implementation of this path",
+                 "config": common_config(1),
                  "clocks": sampler.stop(t0, t1),
                  "cpu_baseline": {"value": round(value, 2), "unit": "TFLOP/s", "cores": 0, "kind": "reference",
                                   "sample": "whole workload on the GPU (cuBLAS); not a CPU run"},
@@ -692,6 +879,11 @@ def main():
     ap.add_argument("--sweep-f32-flop", type=float, default=3e12)
     ap.add_argument("--ce-shard", action="store_true", help="time the vocabulary-sharded cross-entropy kernels")
     ap.add_argument("--ce-rows", type=int, default=16384, help="rows of the shard for --ce-shard (a multiple of 512)")
+    ap.add_argument("--no-vocab-parallel", dest="vocab_parallel", action="store_false",
+                    help="skip the vocabulary-sharded LM head + cross-entropy sub-record")
+    ap.add_argument("--train-step-timeout", type=float, default=600.0)
+    ap.add_argument("--no-train-step", dest="train_step", action="store_false",
+                    help="skip the whole-training-step sub-record (the multi-GPU driver, 2 optimizer steps)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

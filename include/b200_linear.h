@@ -42,6 +42,10 @@ enum {
  * workspace and the device status word.  One per process and GPU. */
 int b200_linear_create(b200_linear_ctx** out);
 int b200_linear_destroy(b200_linear_ctx* ctx);
+/* The context that the reference's C++ overloads exported by this library (matmul_forward and the other
+ * kernels.cuh signatures, which carry no context of ours) use on the current device: created on first use,
+ * on the legacy default stream, destroyed never.  NULL if it cannot be created. */
+b200_linear_ctx* b200_linear_default_ctx(void);
 /* cudaStream_t passed as void*; replaces cublasSetStream (never called by the reference,
  * which stays on the legacy default stream). */
 int b200_linear_set_stream(b200_linear_ctx* ctx, void* cuda_stream);

@@ -20,7 +20,7 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a",
 
 def _sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh"))) + [
-        os.path.join(HERE, "..", "include", "b200_linear.h")]
+        os.path.join(HERE, "..", "include", "b200_linear.h"), os.path.join(HERE, "..", "include", "b200_layers.h")]
 
 
 def _fresh(target, sources):
@@ -39,7 +39,7 @@ def build(force=False, verbose=False):
             return LIB
         raise RuntimeError("nvcc not found and libb200_linear.so is not prebuilt")
     extra = ["-Xptxas", "-v"] if verbose else []
-    units = [os.path.join(CSRC, f) for f in ("api.cu", "kernels_cuh_abi.cu") if os.path.exists(os.path.join(CSRC, f))]
+    units = [os.path.join(CSRC, f) for f in ("api.cu", "kernels_cuh_abi.cu", "layers_api.cu") if os.path.exists(os.path.join(CSRC, f))]
     subprocess.run(["nvcc"] + NVCC_FLAGS + extra + units + ["-o", LIB], check=True)
     shim = os.path.join(CSRC, "cublas_shim.cu")
     if os.path.exists(shim):

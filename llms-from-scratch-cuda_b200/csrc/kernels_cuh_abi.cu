@@ -89,6 +89,12 @@ void poll_all_at_exit() {
     cudaSetDevice(current);
 }
 
+}  // namespace
+
+extern "C" b200_linear_ctx* b200_linear_default_ctx(void) { return device_ctx(); }
+
+namespace {
+
 void check(int rc, b200_linear_ctx* ctx, const char* what, int line) {
     if (rc != B200_OK) fail(rc, ctx, what, line);
     if (++g_calls % kPollEvery == 0) poll_status(ctx, what, line);

@@ -1,0 +1,267 @@
+// Element-wise and row-wise kernels around the linear layers, for the callers of the GEMM path that this
+// library also replaces: rotary embedding (cuda/rope.cu of the reference), the SwiGLU gate
+// (cuda/swiglu.cu:12-47,132-155) and the whole-row softmax cross-entropy (cuda/crossentropy.cu:16-64,96-132).
+// All of them are HBM-bound streaming kernels: 16-byte accesses where the row pitch allows, grids sized from
+// the data, fp32 arithmetic, storage type T = float or __nv_bfloat16 with the reference's rounding points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "gemm_simt.cuh"
+
+namespace b200 {
+
+// ------------------------------------------------------------------------------------------------ RoPE
+// One thread per (token, head of q or k, rotation pair), as cuda/rope.cu:15-57 (forward) and :63-101
+// (backward: the inverse rotation), with a bounds check.  DIR = +1 forward, -1 backward.
+// The rotation frequencies theta^(-2i/head_dim) are formed on the host in double precision and handed over
+// rounded to fp32 (at most 64 pairs, i.e. head_dim <= 128): the angle t * freq then is one fp32 product on the device,
+// which a host restatement reproduces exactly.
+struct RopeFreq {
+    float f[64];
+};
+template <typename T, int DIR>
+__global__ void __launch_bounds__(256)
+rope_kernel(T* __restrict__ q, T* __restrict__ k, long long total, int Tlen, int n_head, int n_kv_head, int head_dim,
+            const RopeFreq freqs) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int total_heads = n_head + n_kv_head, half = head_dim / 2;
+    const int i = static_cast<int>(idx % half);
+    const int h = static_cast<int>((idx / half) % total_heads);
+    const long long bt = idx / (static_cast<long long>(half) * total_heads);
+    const int t = static_cast<int>(bt % Tlen);
+    float s, c;
+    sincosf(static_cast<float>(t) * freqs.f[i], &s, &c);
+    if (DIR < 0) s = -s;
+    T* target = h < n_head ? q : k;
+    const int heads = h < n_head ? n_head : n_kv_head, hh = h < n_head ? h : h - n_head;
+    T* p = target + bt * (static_cast<long long>(heads) * head_dim) + hh * head_dim + 2 * i;
+    const float x0 = to_f32<T>(p[0]), x1 = to_f32<T>(p[1]);
+    p[0] = from_f32<T>(x0 * c - x1 * s);
+    p[1] = from_f32<T>(x0 * s + x1 * c);
+}
+
+// ---------------------------------------------------------------------------------------------- SwiGLU
+__device__ __forceinline__ float sigmoid_f(float g) { return 1.0f / (1.0f + __expf(-g)); }
+
+// hidden = SiLU(gate) * up   (cuda/swiglu.cu:12-24, 132-140)
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_gate_kernel(T* __restrict__ hidden, const T* __restrict__ gate, const T* __restrict__ up, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = to_f32<T>(gate[i]);
+        hidden[i] = from_f32<T>(g * sigmoid_f(g) * to_f32<T>(up[i]));
+    }
+}
+// dup = dhidden * SiLU(gate);  dgate = dhidden * up * SiLU'(gate)   (cuda/swiglu.cu:27-47, 142-155)
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_gate_backward_kernel(T* __restrict__ dgate, T* __restrict__ dup, const T* __restrict__ dhidden,
+                            const T* __restrict__ gate, const T* __restrict__ up, long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = to_f32<T>(gate[i]), u = to_f32<T>(up[i]), dh = to_f32<T>(dhidden[i]);
+        const float sig = sigmoid_f(g);
+        dup[i] = from_f32<T>(dh * (g * sig));
+        dgate[i] = from_f32<T>(dh * u * (sig * (1.0f + g * (1.0f - sig))));
+    }
+}
+// Eight bf16 values per thread: 16-byte loads and stores (n a multiple of 8, pointers 16-byte aligned).
+__global__ void __launch_bounds__(256)
+swiglu_gate_kernel_bf16x8(uint4* __restrict__ hidden, const uint4* __restrict__ gate, const uint4* __restrict__ up,
+                          long long n8) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const uint4 gv = gate[i], uv = up[i];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xFFFF0000u);
+            const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xFFFF0000u);
+            __nv_bfloat162 r = __floats2bfloat162_rn(g0 * sigmoid_f(g0) * u0, g1 * sigmoid_f(g1) * u1);
+            o[j] = *reinterpret_cast<uint32_t*>(&r);
+        }
+        hidden[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+__global__ void __launch_bounds__(256)
+swiglu_gate_backward_kernel_bf16x8(uint4* __restrict__ dgate, uint4* __restrict__ dup, const uint4* __restrict__ dhidden,
+                                   const uint4* __restrict__ gate, const uint4* __restrict__ up, long long n8) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
+        const uint4 gv = gate[i], uv = up[i], dv = dhidden[i];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+        uint32_t og[4], ou[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float g[2] = {__uint_as_float(gw[j] << 16), __uint_as_float(gw[j] & 0xFFFF0000u)};
+            float u[2] = {__uint_as_float(uw[j] << 16), __uint_as_float(uw[j] & 0xFFFF0000u)};
+            float d[2] = {__uint_as_float(dw[j] << 16), __uint_as_float(dw[j] & 0xFFFF0000u)};
+            float rg[2], ru[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float sig = sigmoid_f(g[e]);
+                ru[e] = d[e] * (g[e] * sig);
+                rg[e] = d[e] * u[e] * (sig * (1.0f + g[e] * (1.0f - sig)));
+            }
+            __nv_bfloat162 a = __floats2bfloat162_rn(rg[0], rg[1]), b = __floats2bfloat162_rn(ru[0], ru[1]);
+            og[j] = *reinterpret_cast<uint32_t*>(&a);
+            ou[j] = *reinterpret_cast<uint32_t*>(&b);
+        }
+        dgate[i] = make_uint4(og[0], og[1], og[2], og[3]);
+        dup[i] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------- whole-row cross-entropy
+// One CTA per row (grid-stride over rows).  Same arithmetic and rounding points as the reference's
+// one-thread-per-row kernels (cuda/crossentropy.cu:16-46 fp32, :96-122 bf16): maximum; e = exp(l - max)
+// stored in place in the storage type while the sum adds the unrounded e; p = stored e / sum, stored in
+// place; loss = -log(stored p[target]).  Only the order of the fp32 additions differs (a tree instead of a
+// serial loop).  The row is read from HBM once and written once; the second and third passes hit L2.
+constexpr int CE_ROW_THREADS = 512;
+
+// fp32 storage: the accurate exponential; bf16 storage: the fast one (its error is far below a bf16 ulp)
+template <typename T> __device__ __forceinline__ float ce_exp(float x) { return sizeof(T) == 4 ? expf(x) : __expf(x); }
+
+__device__ __forceinline__ float ce_block_reduce(float v, float* sh, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float w = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, w) : v + w;
+    }
+    __syncthreads();  // sh may still be read from the previous reduction
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    v = threadIdx.x < (CE_ROW_THREADS / 32) ? sh[threadIdx.x] : (is_max ? -INFINITY : 0.f);
+    if (warp == 0) {
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            const float w = __shfl_xor_sync(0xffffffffu, v, o);
+            v = is_max ? fmaxf(v, w) : v + w;
+        }
+        if (lane == 0) sh[0] = v;
+    }
+    __syncthreads();
+    return sh[0];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CE_ROW_THREADS)
+ce_row_forward(float* __restrict__ losses, T* probs, const int* __restrict__ targets, int rows, long long V) {
+    __shared__ float sh[CE_ROW_THREADS / 32];
+    constexpr int VEC = 16 / sizeof(T);  // elements per 16-byte access
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        T* row = probs + static_cast<long long>(r) * V;
+        const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+        const long long nvec = vec ? V / VEC : 0;
+        uint4* row4 = reinterpret_cast<uint4*>(row);
+        auto unpack = [](const uint4& u, float (&x)[VEC]) {
+            if constexpr (sizeof(T) == 2) {
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    x[2 * j] = __uint_as_float(w[j] << 16);
+                    x[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+                }
+            } else {
+                x[0] = __uint_as_float(u.x); x[1] = __uint_as_float(u.y); x[2] = __uint_as_float(u.z); x[3] = __uint_as_float(u.w);
+            }
+        };
+        auto pack = [](const float (&x)[VEC]) {
+            if constexpr (sizeof(T) == 2) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    __nv_bfloat162 p = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+                    w[j] = *reinterpret_cast<uint32_t*>(&p);
+                }
+                return make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+                return make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3]));
+            }
+        };
+        // pass 1: maximum
+        float m = -INFINITY;
+        for (long long i = threadIdx.x; i < nvec; i += CE_ROW_THREADS) {
+            float x[VEC];
+            unpack(row4[i], x);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) m = fmaxf(m, x[j]);
+        }
+        for (long long v = nvec * VEC + threadIdx.x; v < V; v += CE_ROW_THREADS) m = fmaxf(m, to_f32<T>(row[v]));
+        m = ce_block_reduce(m, sh, true);
+        // pass 2: exponentials, stored in place in the storage type; the sum takes them unrounded
+        float s = 0.f;
+        for (long long i = threadIdx.x; i < nvec; i += CE_ROW_THREADS) {
+            float x[VEC];
+            unpack(row4[i], x);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+                x[j] = ce_exp<T>(x[j] - m);
+                s += x[j];
+            }
+            row4[i] = pack(x);
+        }
+        for (long long v = nvec * VEC + threadIdx.x; v < V; v += CE_ROW_THREADS) {
+            const float e = ce_exp<T>(to_f32<T>(row[v]) - m);
+            row[v] = from_f32<T>(e);
+            s += e;
+        }
+        s = ce_block_reduce(s, sh, false);  // its barriers also order pass 2's stores before pass 3's loads
+        // pass 3: normalise the stored values
+        for (long long i = threadIdx.x; i < nvec; i += CE_ROW_THREADS) {
+            float x[VEC];
+            unpack(row4[i], x);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) x[j] = x[j] / s;
+            row4[i] = pack(x);
+        }
+        for (long long v = nvec * VEC + threadIdx.x; v < V; v += CE_ROW_THREADS) row[v] = from_f32<T>(to_f32<T>(row[v]) / s);
+        __syncthreads();
+        if (threadIdx.x == 0) losses[r] = sizeof(T) == 4 ? -logf(to_f32<T>(row[targets[r]])) : -__logf(to_f32<T>(row[targets[r]]));
+    }
+}
+
+// dlogits = (probs - onehot) * scale   (cuda/crossentropy.cu:50-64, 124-132); may run in place.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ce_row_backward(T* dlogits, const T* probs, const int* __restrict__ targets, float scale, int rows, long long V) {
+    const long long n = static_cast<long long>(rows) * V;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long r = i / V;
+        const int v = static_cast<int>(i - r * V);
+        dlogits[i] = from_f32<T>((to_f32<T>(probs[i]) - (v == targets[r] ? 1.0f : 0.0f)) * scale);
+    }
+}
+// bf16, V a multiple of 8, 16-byte aligned: eight columns per thread.
+__global__ void __launch_bounds__(256)
+ce_row_backward_bf16x8(uint4* dlogits, const uint4* probs, const int* __restrict__ targets, float scale, int rows,
+                       long long V8) {
+    const long long n = static_cast<long long>(rows) * V8;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long r = i / V8;
+        const int c0 = static_cast<int>(i - r * V8) * 8;
+        const int t = targets[r] - c0;
+        const uint4 u = probs[i];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xFFFF0000u);
+            if (t == 2 * j) a -= 1.0f;
+            if (t == 2 * j + 1) b -= 1.0f;
+            __nv_bfloat162 p = __floats2bfloat162_rn(a * scale, b * scale);
+            o[j] = *reinterpret_cast<uint32_t*>(&p);
+        }
+        dlogits[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+}  // namespace b200

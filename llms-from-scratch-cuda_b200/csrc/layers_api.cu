@@ -1,0 +1,524 @@
+// The callers of the linear-layer path, as drop-ins: attention (with rotary embedding and the fused
+// softmax(QK^T)V core), the SwiGLU feed-forward block and the softmax cross-entropy.  Each function keeps the
+// signature -- and therefore the mangled name -- that the reference declares in cuda/kernels.cuh, so that
+// the reference's host code links against this library with its own cuda/attention.cu,
+// cuda/flash_attention.cu, cuda/swiglu.cu and cuda/crossentropy.cu left out of the build:
+//
+//   flash_attention_forward / _backward  kernels.cuh:316-341 (fp32), :420-437 (bf16); bodies empty upstream
+//                                        (flash_attention.cu:12-17, 51-57)
+//   attention_forward / _backward        kernels.cuh:156-206 (fp32), :371-388 (bf16); attention.cu:235-414, 582-700
+//   swiglu_forward / _backward           kernels.cuh:211-247 (fp32), :390-396 (bf16); swiglu.cu:49-130, 157-216
+//   crossentropy_forward / crossentropy_softmax_backward
+//                                        kernels.cuh:260-277 (fp32), :402-404 (bf16); crossentropy.cu:66-92, 134-151
+//
+// Differences from the reference, on purpose: no [B, n_head, T, T] matrix is ever formed (the `att` argument
+// of attention_forward keeps the row log-sum-exps and the attention context instead, which is what the
+// backward pass needs); temporaries come from a per-device scratch that grows on demand instead of one
+// cudaMalloc / cudaFree pair per temporary per call; d(input) of the three projections accumulates in the
+// GEMM's beta = 1 epilogue instead of through extra buffers and element-wise adds (same two bf16 roundings).
+// Everything runs on the legacy default stream, like the reference.  Head dimension 64.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+
+#include "../../include/b200_layers.h"
+#include "../../include/b200_linear.h"
+#include "attention_simt.cuh"
+#include "layers.cuh"
+
+struct cublasContext;
+typedef struct cublasContext* cublasHandle_t;
+
+using namespace b200;
+
+namespace {
+
+constexpr int kMaxDev = 64;
+enum Slot { S_CONTEXT, S_DCONTEXT, S_DQ, S_DK, S_DV, S_DELTA, S_LSE, S_HIDDEN, S_DHIDDEN, S_DGATE, S_DUP, S_COUNT };
+struct Scratch {
+    void* ptr[S_COUNT] = {};
+    size_t bytes[S_COUNT] = {};
+    bool attn_configured = false;
+};
+Scratch g_scratch[kMaxDev];
+
+// Per-device scratch buffer `slot` of at least `bytes` bytes (grown, never shrunk); nullptr on failure.
+void* scratch(int slot, size_t bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+    Scratch& s = g_scratch[dev];
+    if (bytes <= s.bytes[slot]) return s.ptr[slot];
+    if (s.ptr[slot]) cudaFree(s.ptr[slot]);
+    s.ptr[slot] = nullptr;
+    s.bytes[slot] = 0;
+    const size_t want = bytes + (bytes >> 3);
+    if (cudaMalloc(&s.ptr[slot], want) != cudaSuccess) return nullptr;
+    s.bytes[slot] = want;
+    return s.ptr[slot];
+}
+
+int configure_attention() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return B200_E_NODEVICE;
+    if (g_scratch[dev].attn_configured) return B200_OK;
+#define ATTN_SMEM(kern, bytes) \
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return B200_E_CUDA
+    ATTN_SMEM(attn_fwd_simt<float>, ATTN_FWD_SMEM);
+    ATTN_SMEM(attn_fwd_simt<__nv_bfloat16>, ATTN_FWD_SMEM);
+    ATTN_SMEM(attn_bwd_dq_simt<float>, ATTN_DQ_SMEM);
+    ATTN_SMEM(attn_bwd_dq_simt<__nv_bfloat16>, ATTN_DQ_SMEM);
+    ATTN_SMEM(attn_bwd_dkv_simt<float>, ATTN_DKV_SMEM);
+    ATTN_SMEM(attn_bwd_dkv_simt<__nv_bfloat16>, ATTN_DKV_SMEM);
+#undef ATTN_SMEM
+    g_scratch[dev].attn_configured = true;
+    return B200_OK;
+}
+
+int launch_ok() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA; }
+
+bool attn_args_ok(int B, int T, int n_head, int n_kv_head, int head_dim) {
+    return B > 0 && T > 0 && n_head > 0 && n_kv_head > 0 && n_head % n_kv_head == 0 && head_dim == AT_TILE &&
+           B <= 65535 && n_head <= 65535;
+}
+
+template <typename T>
+int flash_forward(T* context, float* lse, const T* q, const T* k, const T* v, int B, int Tlen, int n_head, int n_kv_head,
+                  int head_dim, cudaStream_t stream) {
+    if (!context || !lse || !q || !k || !v || !attn_args_ok(B, Tlen, n_head, n_kv_head, head_dim)) return B200_E_BADARG;
+    int rc = configure_attention();
+    if (rc) return rc;
+    const AttnParams p{B, Tlen, n_head, n_kv_head, 1.0f / sqrtf(static_cast<float>(head_dim))};
+    const dim3 grid((Tlen + AT_TILE - 1) / AT_TILE, n_head, B);
+    attn_fwd_simt<T><<<grid, AT_THREADS, ATTN_FWD_SMEM, stream>>>(context, lse, q, k, v, p);
+    return launch_ok();
+}
+
+// context == nullptr: the forward pass is run again into scratch to get it (the reference's flash API does
+// not hand the context to the backward pass).
+template <typename T>
+int flash_backward(T* dq, T* dk, T* dv, const T* dcontext, const T* q, const T* k, const T* v, const float* lse,
+                   const T* context, int B, int Tlen, int n_head, int n_kv_head, int head_dim, cudaStream_t stream) {
+    if (!dq || !dk || !dv || !dcontext || !q || !k || !v || !lse || !attn_args_ok(B, Tlen, n_head, n_kv_head, head_dim))
+        return B200_E_BADARG;
+    int rc = configure_attention();
+    if (rc) return rc;
+    const AttnParams p{B, Tlen, n_head, n_kv_head, 1.0f / sqrtf(static_cast<float>(head_dim))};
+    const size_t rows = static_cast<size_t>(B) * n_head * Tlen;
+    float* delta = static_cast<float*>(scratch(S_DELTA, rows * sizeof(float)));
+    if (!delta) return B200_E_CUDA;
+    if (!context) {
+        T* ctx_tmp = static_cast<T*>(scratch(S_CONTEXT, static_cast<size_t>(B) * Tlen * n_head * head_dim * sizeof(T)));
+        float* lse_tmp = static_cast<float*>(scratch(S_LSE, rows * sizeof(float)));
+        if (!ctx_tmp || !lse_tmp) return B200_E_CUDA;
+        rc = flash_forward<T>(ctx_tmp, lse_tmp, q, k, v, B, Tlen, n_head, n_kv_head, head_dim, stream);
+        if (rc) return rc;
+        context = ctx_tmp;
+    }
+    attn_delta<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(delta, dcontext, context, p);
+    const int tiles = (Tlen + AT_TILE - 1) / AT_TILE;
+    attn_bwd_dq_simt<T><<<dim3(tiles, n_head, B), AT_THREADS, ATTN_DQ_SMEM, stream>>>(dq, dcontext, q, k, v, lse, delta, p);
+    attn_bwd_dkv_simt<T><<<dim3(tiles, n_kv_head, B), AT_THREADS, ATTN_DKV_SMEM, stream>>>(dk, dv, dcontext, q, k, v, lse,
+                                                                                         delta, p);
+    return launch_ok();
+}
+
+template <typename T, int DIR>
+int rope(T* q, T* k, int B, int Tlen, int n_head, int n_kv_head, int head_dim, float theta, cudaStream_t stream) {
+    if (!q || !k || B <= 0 || Tlen <= 0 || head_dim <= 0 || (head_dim & 1) || head_dim > 128) return B200_E_BADARG;
+    const long long total = static_cast<long long>(B) * Tlen * (n_head + n_kv_head) * (head_dim / 2);
+    RopeFreq freqs;
+    for (int i = 0; i < head_dim / 2; ++i)  // cuda/rope.cu:29: 1 / theta^(2i / head_dim)
+        freqs.f[i] = static_cast<float>(1.0 / pow(static_cast<double>(theta), (2.0 * i) / head_dim));
+    rope_kernel<T, DIR><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(q, k, total, Tlen, n_head, n_kv_head,
+                                                                                       head_dim, freqs);
+    return launch_ok();
+}
+
+// GEMM dispatch by storage type.
+int gemm(b200_linear_ctx* ctx, int which, int beta1, __nv_bfloat16* out, const __nv_bfloat16* x, const __nv_bfloat16* y, int M,
+         int N, int K) {
+    return b200_linear_gemm_bf16(ctx, which, beta1, out, x, y, M, N, K);
+}
+int gemm(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x, const float* y, int M, int N, int K) {
+    return b200_linear_gemm_f32(ctx, which, beta1, out, x, y, M, N, K);
+}
+int backward(b200_linear_ctx* ctx, __nv_bfloat16* dA, __nv_bfloat16* dB, const __nv_bfloat16* dC, const __nv_bfloat16* A,
+             const __nv_bfloat16* Bm, int M, int N, int K) {
+    return b200_linear_backward_bf16(ctx, dA, dB, dC, A, Bm, M, N, K);
+}
+int backward(b200_linear_ctx* ctx, float* dA, float* dB, const float* dC, const float* A, const float* Bm, int M, int N, int K) {
+    return b200_linear_backward_f32(ctx, dA, dB, dC, A, Bm, M, N, K);
+}
+
+// What attention_forward leaves in the caller's `att` buffer ([B, n_head, T, T] elements of T in the reference):
+// the row log-sum-exps (fp32) followed, 256-byte aligned, by the attention context [B*T, C].  It fits whenever
+// T >= 68; for shorter sequences the backward pass recomputes both.
+template <typename T>
+struct AttStash {
+    float* lse;
+    T* context;
+    bool fits;
+    AttStash(void* att, int B, int Tlen, int C, int n_head) {
+        const size_t lse_bytes = ((static_cast<size_t>(B) * n_head * Tlen * sizeof(float) + 255) / 256) * 256;
+        const size_t ctx_bytes = static_cast<size_t>(B) * Tlen * C * sizeof(T);
+        fits = att != nullptr && lse_bytes + ctx_bytes <= static_cast<size_t>(B) * n_head * Tlen * Tlen * sizeof(T) &&
+               (reinterpret_cast<uintptr_t>(att) & 15) == 0;
+        lse = static_cast<float*>(att);
+        context = reinterpret_cast<T*>(static_cast<char*>(att) + lse_bytes);
+    }
+};
+
+#define TRY(expr)              \
+    do {                       \
+        int rc__ = (expr);     \
+        if (rc__) return rc__; \
+    } while (0)
+
+template <typename T>
+int attention_fwd(b200_linear_ctx* ctx, T* out, T* q, T* k, T* v, void* att, const T* inp, const T* wq, const T* wk,
+                  const T* wv, const T* wo, int B, int Tlen, int C, int n_head, int n_kv_head, float rope_theta) {
+    if (!ctx || !out || !q || !k || !v || !inp || !wq || !wk || !wv || !wo || n_head <= 0 || C % n_head != 0) return B200_E_BADARG;
+    const int hd = C / n_head, kv = n_kv_head * hd, BT = B * Tlen;
+    if (!attn_args_ok(B, Tlen, n_head, n_kv_head, hd)) return B200_E_BADARG;
+    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, q, inp, wq, BT, C, C));
+    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, k, inp, wk, BT, kv, C));
+    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, v, inp, wv, BT, kv, C));
+    TRY((rope<T, +1>(q, k, B, Tlen, n_head, n_kv_head, hd, rope_theta, nullptr)));
+    AttStash<T> st(att, B, Tlen, C, n_head);
+    T* context = st.context;
+    float* lse = st.lse;
+    if (!st.fits) {
+        context = static_cast<T*>(scratch(S_CONTEXT, static_cast<size_t>(BT) * C * sizeof(T)));
+        lse = static_cast<float*>(scratch(S_LSE, static_cast<size_t>(B) * n_head * Tlen * sizeof(float)));
+        if (!context || !lse) return B200_E_CUDA;
+    }
+    TRY(flash_forward<T>(context, lse, q, k, v, B, Tlen, n_head, n_kv_head, hd, nullptr));
+    return gemm(ctx, B200_GEMM_FWD_NN, 0, out, context, wo, BT, C, C);
+}
+
+template <typename T>
+int attention_bwd(b200_linear_ctx* ctx, T* dinp, T* dwq, T* dwk, T* dwv, T* dwo, const T* dout, const T* inp, const T* q,
+                  const T* k, const T* v, const void* att, const T* wq, const T* wk, const T* wv, const T* wo, int B,
+                  int Tlen, int C, int n_head, int n_kv_head, float rope_theta) {
+    if (!ctx || !dinp || !dwq || !dwk || !dwv || !dwo || !dout || !inp || !q || !k || !v || !wq || !wk || !wv || !wo ||
+        n_head <= 0 || C % n_head != 0)
+        return B200_E_BADARG;
+    const int hd = C / n_head, kv = n_kv_head * hd, BT = B * Tlen;
+    if (!attn_args_ok(B, Tlen, n_head, n_kv_head, hd)) return B200_E_BADARG;
+    AttStash<T> st(const_cast<void*>(att), B, Tlen, C, n_head);
+    const T* context = st.context;
+    const float* lse = st.lse;
+    if (!st.fits) {  // short sequences: nothing was kept, run the fused forward again
+        T* c2 = static_cast<T*>(scratch(S_CONTEXT, static_cast<size_t>(BT) * C * sizeof(T)));
+        float* l2 = static_cast<float*>(scratch(S_LSE, static_cast<size_t>(B) * n_head * Tlen * sizeof(float)));
+        if (!c2 || !l2) return B200_E_CUDA;
+        TRY(flash_forward<T>(c2, l2, q, k, v, B, Tlen, n_head, n_kv_head, hd, nullptr));
+        context = c2;
+        lse = l2;
+    }
+    T* dcontext = static_cast<T*>(scratch(S_DCONTEXT, static_cast<size_t>(BT) * C * sizeof(T)));
+    T* dq = static_cast<T*>(scratch(S_DQ, static_cast<size_t>(BT) * C * sizeof(T)));
+    T* dk = static_cast<T*>(scratch(S_DK, static_cast<size_t>(BT) * kv * sizeof(T)));
+    T* dv = static_cast<T*>(scratch(S_DV, static_cast<size_t>(BT) * kv * sizeof(T)));
+    if (!dcontext || !dq || !dk || !dv) return B200_E_CUDA;
+    TRY(backward(ctx, dcontext, dwo, dout, context, wo, BT, C, C));                       // attention.cu:640
+    TRY(flash_backward<T>(dq, dk, dv, dcontext, q, k, v, lse, context, B, Tlen, n_head, n_kv_head, hd, nullptr));
+    TRY((rope<T, -1>(dq, dk, B, Tlen, n_head, n_kv_head, hd, rope_theta, nullptr)));          // attention.cu:669
+    TRY(backward(ctx, dinp, dwq, dq, inp, wq, BT, C, C));                                 // attention.cu:671
+    // attention.cu:673-688: d(input) of the K and V projections added to that of the Q projection
+    TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dinp, dk, wk, BT, kv, C));
+    TRY(gemm(ctx, B200_GEMM_WGRAD_TN, 1, dwk, inp, dk, BT, kv, C));
+    TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dinp, dv, wv, BT, kv, C));
+    return gemm(ctx, B200_GEMM_WGRAD_TN, 1, dwv, inp, dv, BT, kv, C);
+}
+
+template <typename T>
+int swiglu_gate(T* hidden, const T* gate, const T* up, long long n) {
+    const bool vec = sizeof(T) == 2 && (n % 8) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
+    if (vec) {
+        const long long n8 = n / 8;
+        swiglu_gate_kernel_bf16x8<<<static_cast<unsigned>((n8 + 255) / 256 < 65535 * 16 ? (n8 + 255) / 256 : 65535 * 16), 256>>>(
+            reinterpret_cast<uint4*>(hidden), reinterpret_cast<const uint4*>(gate), reinterpret_cast<const uint4*>(up), n8);
+    } else {
+        swiglu_gate_kernel<T><<<static_cast<unsigned>((n + 255) / 256 < 65535 * 16 ? (n + 255) / 256 : 65535 * 16), 256>>>(hidden, gate, up, n);
+    }
+    return launch_ok();
+}
+
+template <typename T>
+int swiglu_fwd(b200_linear_ctx* ctx, T* out, T* gate, T* up, T* hidden, const T* inp, const T* w_gate, const T* w_up,
+               const T* w_down, int BT, int C, int ff) {
+    if (!ctx || !out || !gate || !up || !hidden || !inp || !w_gate || !w_up || !w_down || BT <= 0 || C <= 0 || ff <= 0)
+        return B200_E_BADARG;
+    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, gate, inp, w_gate, BT, ff, C));
+    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, up, inp, w_up, BT, ff, C));
+    TRY(swiglu_gate<T>(hidden, gate, up, static_cast<long long>(BT) * ff));
+    return gemm(ctx, B200_GEMM_FWD_NN, 0, out, hidden, w_down, BT, C, ff);
+}
+
+template <typename T>
+int swiglu_bwd(b200_linear_ctx* ctx, T* dinp, T* dw_gate, T* dw_up, T* dw_down, const T* dout, const T* inp, const T* gate,
+               const T* up, const T* w_gate, const T* w_up, const T* w_down, int BT, int C, int ff) {
+    if (!ctx || !dinp || !dw_gate || !dw_up || !dw_down || !dout || !inp || !gate || !up || !w_gate || !w_up || !w_down ||
+        BT <= 0 || C <= 0 || ff <= 0)
+        return B200_E_BADARG;
+    const long long n = static_cast<long long>(BT) * ff;
+    T* hidden = static_cast<T*>(scratch(S_HIDDEN, n * sizeof(T)));
+    T* dhidden = static_cast<T*>(scratch(S_DHIDDEN, n * sizeof(T)));
+    T* dgate = static_cast<T*>(scratch(S_DGATE, n * sizeof(T)));
+    T* dup = static_cast<T*>(scratch(S_DUP, n * sizeof(T)));
+    if (!hidden || !dhidden || !dgate || !dup) return B200_E_CUDA;
+    TRY(swiglu_gate<T>(hidden, gate, up, n));                                              // swiglu.cu:184
+    TRY(backward(ctx, dhidden, dw_down, dout, hidden, w_down, BT, C, ff));                 // swiglu.cu:192
+    const bool vec = sizeof(T) == 2 && (n % 8) == 0;
+    const unsigned blocks = static_cast<unsigned>(((vec ? n / 8 : n) + 255) / 256 < 65535 * 16 ? ((vec ? n / 8 : n) + 255) / 256 : 65535 * 16);
+    if (vec)
+        swiglu_gate_backward_kernel_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(dgate), reinterpret_cast<uint4*>(dup),
+                                                            reinterpret_cast<const uint4*>(dhidden),
+                                                            reinterpret_cast<const uint4*>(gate),
+                                                            reinterpret_cast<const uint4*>(up), n / 8);
+    else
+        swiglu_gate_backward_kernel<T><<<blocks, 256>>>(dgate, dup, dhidden, gate, up, n);
+    TRY(launch_ok());
+    TRY(backward(ctx, dinp, dw_gate, dgate, inp, w_gate, BT, ff, C));                      // swiglu.cu:197
+    // swiglu.cu:199-208: d(input) of the up projection added to that of the gate projection
+    TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dinp, dup, w_up, BT, ff, C));
+    return gemm(ctx, B200_GEMM_WGRAD_TN, 1, dw_up, inp, dup, BT, ff, C);
+}
+
+template <typename T>
+int ce_forward(float* losses, T* logits_probs, const int* targets, int B, int Tlen, int V) {
+    if (!losses || !logits_probs || !targets || B <= 0 || Tlen <= 0 || V <= 0) return B200_E_BADARG;
+    const int rows = B * Tlen;
+    ce_row_forward<T><<<rows, CE_ROW_THREADS>>>(losses, logits_probs, targets, rows, V);
+    return launch_ok();
+}
+
+template <typename T>
+int ce_backward(T* dlogits, const T* probs, const int* targets, int B, int Tlen, int V, float scale) {
+    if (!dlogits || !probs || !targets || B <= 0 || Tlen <= 0 || V <= 0) return B200_E_BADARG;
+    const int rows = B * Tlen;
+    const bool vec = sizeof(T) == 2 && (V % 8) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(dlogits) | reinterpret_cast<uintptr_t>(probs)) & 15) == 0;
+    const long long n = static_cast<long long>(rows) * (vec ? V / 8 : V);
+    const unsigned blocks = static_cast<unsigned>((n + 255) / 256 < 148LL * 64 ? (n + 255) / 256 : 148LL * 64);
+    if (vec)
+        ce_row_backward_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(dlogits), reinterpret_cast<const uint4*>(probs),
+                                                targets, scale, rows, V / 8);
+    else
+        ce_row_backward<T><<<blocks, 256>>>(dlogits, probs, targets, scale, rows, V);
+    return launch_ok();
+}
+
+// the reference's error convention for the void overloads (cuda/tensor.h:10-29)
+void check(int rc, const char* what) {
+    if (rc == B200_OK) return;
+    fprintf(stderr, "b200_layers error %s: %s (cuda: %s)\n", what, b200_linear_strerror(rc), cudaGetErrorString(cudaGetLastError()));
+    exit(EXIT_FAILURE);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ C entry points
+extern "C" {
+
+int b200_flash_attention_forward_bf16(void* context, float* lse, const void* q, const void* k, const void* v, int B, int T,
+                                      int n_head, int n_kv_head, int head_dim, void* cuda_stream) {
+    typedef __nv_bfloat16 bf;
+    return flash_forward<bf>(static_cast<bf*>(context), lse, static_cast<const bf*>(q), static_cast<const bf*>(k),
+                             static_cast<const bf*>(v), B, T, n_head, n_kv_head, head_dim, static_cast<cudaStream_t>(cuda_stream));
+}
+int b200_flash_attention_forward_f32(float* context, float* lse, const float* q, const float* k, const float* v, int B, int T,
+                                     int n_head, int n_kv_head, int head_dim, void* cuda_stream) {
+    return flash_forward<float>(context, lse, q, k, v, B, T, n_head, n_kv_head, head_dim, static_cast<cudaStream_t>(cuda_stream));
+}
+int b200_flash_attention_backward_bf16(void* dq, void* dk, void* dv, const void* dcontext, const void* q, const void* k,
+                                       const void* v, const float* lse, const void* context, int B, int T, int n_head,
+                                       int n_kv_head, int head_dim, void* cuda_stream) {
+    typedef __nv_bfloat16 bf;
+    return flash_backward<bf>(static_cast<bf*>(dq), static_cast<bf*>(dk), static_cast<bf*>(dv), static_cast<const bf*>(dcontext),
+                              static_cast<const bf*>(q), static_cast<const bf*>(k), static_cast<const bf*>(v), lse,
+                              static_cast<const bf*>(context), B, T, n_head, n_kv_head, head_dim,
+                              static_cast<cudaStream_t>(cuda_stream));
+}
+int b200_flash_attention_backward_f32(float* dq, float* dk, float* dv, const float* dcontext, const float* q, const float* k,
+                                      const float* v, const float* lse, const float* context, int B, int T, int n_head,
+                                      int n_kv_head, int head_dim, void* cuda_stream) {
+    return flash_backward<float>(dq, dk, dv, dcontext, q, k, v, lse, context, B, T, n_head, n_kv_head, head_dim,
+                                 static_cast<cudaStream_t>(cuda_stream));
+}
+int b200_rope_bf16(void* q, void* k, int B, int T, int n_head, int n_kv_head, int head_dim, float theta, int backward,
+                   void* cuda_stream) {
+    typedef __nv_bfloat16 bf;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    return backward ? rope<bf, -1>(static_cast<bf*>(q), static_cast<bf*>(k), B, T, n_head, n_kv_head, head_dim, theta, s)
+                    : rope<bf, +1>(static_cast<bf*>(q), static_cast<bf*>(k), B, T, n_head, n_kv_head, head_dim, theta, s);
+}
+
+int b200_attention_forward_bf16(b200_linear_ctx* ctx, void* out, void* q, void* k, void* v, void* att, const void* inp,
+                                const void* wq, const void* wk, const void* wv, const void* wo, int B, int T, int C, int n_head,
+                                int n_kv_head, float rope_theta) {
+    typedef __nv_bfloat16 bf;
+    return attention_fwd<bf>(ctx, static_cast<bf*>(out), static_cast<bf*>(q), static_cast<bf*>(k), static_cast<bf*>(v), att,
+                             static_cast<const bf*>(inp), static_cast<const bf*>(wq), static_cast<const bf*>(wk),
+                             static_cast<const bf*>(wv), static_cast<const bf*>(wo), B, T, C, n_head, n_kv_head, rope_theta);
+}
+int b200_attention_backward_bf16(b200_linear_ctx* ctx, void* dinp, void* dwq, void* dwk, void* dwv, void* dwo, const void* dout,
+                                 const void* inp, const void* q, const void* k, const void* v, const void* att, const void* wq,
+                                 const void* wk, const void* wv, const void* wo, int B, int T, int C, int n_head, int n_kv_head,
+                                 float rope_theta) {
+    typedef __nv_bfloat16 bf;
+    return attention_bwd<bf>(ctx, static_cast<bf*>(dinp), static_cast<bf*>(dwq), static_cast<bf*>(dwk), static_cast<bf*>(dwv),
+                             static_cast<bf*>(dwo), static_cast<const bf*>(dout), static_cast<const bf*>(inp),
+                             static_cast<const bf*>(q), static_cast<const bf*>(k), static_cast<const bf*>(v), att,
+                             static_cast<const bf*>(wq), static_cast<const bf*>(wk), static_cast<const bf*>(wv),
+                             static_cast<const bf*>(wo), B, T, C, n_head, n_kv_head, rope_theta);
+}
+int b200_attention_forward_f32(b200_linear_ctx* ctx, float* out, float* q, float* k, float* v, float* att, const float* inp,
+                               const float* wq, const float* wk, const float* wv, const float* wo, int B, int T, int C,
+                               int n_head, int n_kv_head, float rope_theta) {
+    return attention_fwd<float>(ctx, out, q, k, v, att, inp, wq, wk, wv, wo, B, T, C, n_head, n_kv_head, rope_theta);
+}
+int b200_attention_backward_f32(b200_linear_ctx* ctx, float* dinp, float* dwq, float* dwk, float* dwv, float* dwo,
+                                const float* dout, const float* inp, const float* q, const float* k, const float* v,
+                                const float* att, const float* wq, const float* wk, const float* wv, const float* wo, int B, int T,
+                                int C, int n_head, int n_kv_head, float rope_theta) {
+    return attention_bwd<float>(ctx, dinp, dwq, dwk, dwv, dwo, dout, inp, q, k, v, att, wq, wk, wv, wo, B, T, C, n_head,
+                                n_kv_head, rope_theta);
+}
+
+int b200_swiglu_forward_bf16(b200_linear_ctx* ctx, void* out, void* gate, void* up, void* hidden, const void* inp,
+                             const void* w_gate, const void* w_up, const void* w_down, int BT, int C, int ffn_hidden) {
+    typedef __nv_bfloat16 bf;
+    return swiglu_fwd<bf>(ctx, static_cast<bf*>(out), static_cast<bf*>(gate), static_cast<bf*>(up), static_cast<bf*>(hidden),
+                          static_cast<const bf*>(inp), static_cast<const bf*>(w_gate), static_cast<const bf*>(w_up),
+                          static_cast<const bf*>(w_down), BT, C, ffn_hidden);
+}
+int b200_swiglu_backward_bf16(b200_linear_ctx* ctx, void* dinp, void* dw_gate, void* dw_up, void* dw_down, const void* dout,
+                              const void* inp, const void* gate, const void* up, const void* w_gate, const void* w_up,
+                              const void* w_down, int BT, int C, int ffn_hidden) {
+    typedef __nv_bfloat16 bf;
+    return swiglu_bwd<bf>(ctx, static_cast<bf*>(dinp), static_cast<bf*>(dw_gate), static_cast<bf*>(dw_up), static_cast<bf*>(dw_down),
+                          static_cast<const bf*>(dout), static_cast<const bf*>(inp), static_cast<const bf*>(gate),
+                          static_cast<const bf*>(up), static_cast<const bf*>(w_gate), static_cast<const bf*>(w_up),
+                          static_cast<const bf*>(w_down), BT, C, ffn_hidden);
+}
+int b200_swiglu_forward_f32(b200_linear_ctx* ctx, float* out, float* gate, float* up, float* hidden, const float* inp,
+                            const float* w_gate, const float* w_up, const float* w_down, int BT, int C, int ffn_hidden) {
+    return swiglu_fwd<float>(ctx, out, gate, up, hidden, inp, w_gate, w_up, w_down, BT, C, ffn_hidden);
+}
+int b200_swiglu_backward_f32(b200_linear_ctx* ctx, float* dinp, float* dw_gate, float* dw_up, float* dw_down, const float* dout,
+                             const float* inp, const float* gate, const float* up, const float* w_gate, const float* w_up,
+                             const float* w_down, int BT, int C, int ffn_hidden) {
+    return swiglu_bwd<float>(ctx, dinp, dw_gate, dw_up, dw_down, dout, inp, gate, up, w_gate, w_up, w_down, BT, C, ffn_hidden);
+}
+
+int b200_crossentropy_forward_bf16(float* losses, void* logits_probs, const int* targets, int B, int T, int V) {
+    return ce_forward<__nv_bfloat16>(losses, static_cast<__nv_bfloat16*>(logits_probs), targets, B, T, V);
+}
+int b200_crossentropy_forward_f32(float* losses, float* logits_probs, const int* targets, int B, int T, int V) {
+    return ce_forward<float>(losses, logits_probs, targets, B, T, V);
+}
+int b200_crossentropy_backward_bf16(void* dlogits, const void* probs, const int* targets, int B, int T, int V, float loss_scale) {
+    if (B <= 0 || T <= 0) return B200_E_BADARG;
+    return ce_backward<__nv_bfloat16>(static_cast<__nv_bfloat16*>(dlogits), static_cast<const __nv_bfloat16*>(probs), targets, B, T,
+                                      V, loss_scale / static_cast<float>(B * T));
+}
+int b200_crossentropy_backward_f32(float* dlogits, const float* probs, const int* targets, int B, int T, int V) {
+    if (B <= 0 || T <= 0) return B200_E_BADARG;
+    return ce_backward<float>(dlogits, probs, targets, B, T, V, 1.0f / static_cast<float>(B * T));
+}
+
+}  // extern "C"
+
+// ------------------------------------------------- the reference's C++ overloads (exact mangled names)
+void flash_attention_forward(float* context, float* lse, const float* q, const float* k, const float* v, int B, int T, int n_head,
+                             int n_kv_head, int head_dim) {
+    check(b200_flash_attention_forward_f32(context, lse, q, k, v, B, T, n_head, n_kv_head, head_dim, nullptr), "flash_attention_forward(fp32)");
+}
+void flash_attention_forward(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                             const __nv_bfloat16* v, int B, int T, int n_head, int n_kv_head, int head_dim) {
+    check(b200_flash_attention_forward_bf16(context, lse, q, k, v, B, T, n_head, n_kv_head, head_dim, nullptr), "flash_attention_forward(bf16)");
+}
+void flash_attention_backward(float* dq, float* dk, float* dv, const float* dcontext, const float* q, const float* k,
+                              const float* v, const float* lse, int B, int T, int n_head, int n_kv_head, int head_dim) {
+    check(b200_flash_attention_backward_f32(dq, dk, dv, dcontext, q, k, v, lse, nullptr, B, T, n_head, n_kv_head, head_dim, nullptr),
+          "flash_attention_backward(fp32)");
+}
+void flash_attention_backward(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, const __nv_bfloat16* dcontext,
+                              const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, const float* lse, int B,
+                              int T, int n_head, int n_kv_head, int head_dim) {
+    check(b200_flash_attention_backward_bf16(dq, dk, dv, dcontext, q, k, v, lse, nullptr, B, T, n_head, n_kv_head, head_dim, nullptr),
+          "flash_attention_backward(bf16)");
+}
+
+void attention_forward(float* out, float* q, float* k, float* v, float* att_or_lse, const float* inp, const float* wq,
+                       const float* wk, const float* wv, const float* wo, int B, int T, int C, int n_head, int n_kv_head,
+                       float rope_theta, cublasHandle_t) {
+    check(b200_attention_forward_f32(b200_linear_default_ctx(), out, q, k, v, att_or_lse, inp, wq, wk, wv, wo, B, T, C, n_head,
+                                     n_kv_head, rope_theta), "attention_forward(fp32)");
+}
+void attention_backward(float* dinp, float* dwq, float* dwk, float* dwv, float* dwo, const float* dout, const float* inp,
+                        const float* q, const float* k, const float* v, const float* att_or_lse, const float* wq, const float* wk,
+                        const float* wv, const float* wo, int B, int T, int C, int n_head, int n_kv_head, float rope_theta,
+                        cublasHandle_t) {
+    check(b200_attention_backward_f32(b200_linear_default_ctx(), dinp, dwq, dwk, dwv, dwo, dout, inp, q, k, v, att_or_lse, wq, wk,
+                                      wv, wo, B, T, C, n_head, n_kv_head, rope_theta), "attention_backward(fp32)");
+}
+void attention_forward(__nv_bfloat16* out, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* v, __nv_bfloat16* att,
+                       const __nv_bfloat16* inp, const __nv_bfloat16* wq, const __nv_bfloat16* wk, const __nv_bfloat16* wv,
+                       const __nv_bfloat16* wo, int B, int T, int C, int n_head, int n_kv_head, float rope_theta, cublasHandle_t) {
+    check(b200_attention_forward_bf16(b200_linear_default_ctx(), out, q, k, v, att, inp, wq, wk, wv, wo, B, T, C, n_head, n_kv_head,
+                                      rope_theta), "attention_forward(bf16)");
+}
+void attention_backward(__nv_bfloat16* dinp, __nv_bfloat16* dwq, __nv_bfloat16* dwk, __nv_bfloat16* dwv, __nv_bfloat16* dwo,
+                        const __nv_bfloat16* dout, const __nv_bfloat16* inp, const __nv_bfloat16* q, const __nv_bfloat16* k,
+                        const __nv_bfloat16* v, const __nv_bfloat16* att, const __nv_bfloat16* wq, const __nv_bfloat16* wk,
+                        const __nv_bfloat16* wv, const __nv_bfloat16* wo, int B, int T, int C, int n_head, int n_kv_head,
+                        float rope_theta, cublasHandle_t) {
+    check(b200_attention_backward_bf16(b200_linear_default_ctx(), dinp, dwq, dwk, dwv, dwo, dout, inp, q, k, v, att, wq, wk, wv, wo,
+                                       B, T, C, n_head, n_kv_head, rope_theta), "attention_backward(bf16)");
+}
+
+void swiglu_forward(float* out, float* gate, float* up, float* hidden, const float* inp, const float* w_gate, const float* w_up,
+                    const float* w_down, int B_T, int C, int ffn_hidden, cublasHandle_t) {
+    check(b200_swiglu_forward_f32(b200_linear_default_ctx(), out, gate, up, hidden, inp, w_gate, w_up, w_down, B_T, C, ffn_hidden),
+          "swiglu_forward(fp32)");
+}
+void swiglu_backward(float* dinp, float* dw_gate, float* dw_up, float* dw_down, const float* dout, const float* inp,
+                     const float* gate, const float* up, const float* w_gate, const float* w_up, const float* w_down, int B_T,
+                     int C, int ffn_hidden, cublasHandle_t) {
+    check(b200_swiglu_backward_f32(b200_linear_default_ctx(), dinp, dw_gate, dw_up, dw_down, dout, inp, gate, up, w_gate, w_up,
+                                   w_down, B_T, C, ffn_hidden), "swiglu_backward(fp32)");
+}
+void swiglu_forward(__nv_bfloat16* out, __nv_bfloat16* gate, __nv_bfloat16* up, __nv_bfloat16* hidden, const __nv_bfloat16* inp,
+                    const __nv_bfloat16* w_gate, const __nv_bfloat16* w_up, const __nv_bfloat16* w_down, int B_T, int C,
+                    int ffn_hidden, cublasHandle_t) {
+    check(b200_swiglu_forward_bf16(b200_linear_default_ctx(), out, gate, up, hidden, inp, w_gate, w_up, w_down, B_T, C, ffn_hidden),
+          "swiglu_forward(bf16)");
+}
+void swiglu_backward(__nv_bfloat16* dinp, __nv_bfloat16* dw_gate, __nv_bfloat16* dw_up, __nv_bfloat16* dw_down,
+                     const __nv_bfloat16* dout, const __nv_bfloat16* inp, const __nv_bfloat16* gate, const __nv_bfloat16* up,
+                     const __nv_bfloat16* w_gate, const __nv_bfloat16* w_up, const __nv_bfloat16* w_down, int B_T, int C,
+                     int ffn_hidden, cublasHandle_t) {
+    check(b200_swiglu_backward_bf16(b200_linear_default_ctx(), dinp, dw_gate, dw_up, dw_down, dout, inp, gate, up, w_gate, w_up,
+                                    w_down, B_T, C, ffn_hidden), "swiglu_backward(bf16)");
+}
+
+void crossentropy_forward(float* losses, const float* logits, const int* targets, int B, int T, int V) {
+    check(b200_crossentropy_forward_f32(losses, const_cast<float*>(logits), targets, B, T, V), "crossentropy_forward(fp32)");
+}
+void crossentropy_softmax_backward(float* dlogits, const float* probs, const int* targets, int B, int T, int V) {
+    check(b200_crossentropy_backward_f32(dlogits, probs, targets, B, T, V), "crossentropy_softmax_backward(fp32)");
+}
+void crossentropy_forward(float* losses, const __nv_bfloat16* logits, const int* targets, int B, int T, int V) {
+    check(b200_crossentropy_forward_bf16(losses, const_cast<__nv_bfloat16*>(logits), targets, B, T, V), "crossentropy_forward(bf16)");
+}
+void crossentropy_softmax_backward(__nv_bfloat16* dlogits, const __nv_bfloat16* probs, const int* targets, int B, int T, int V,
+                                   float loss_scale) {
+    check(b200_crossentropy_backward_bf16(dlogits, probs, targets, B, T, V, loss_scale), "crossentropy_softmax_backward(bf16)");
+}

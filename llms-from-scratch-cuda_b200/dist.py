@@ -90,12 +90,13 @@ class CudaShardOps:
         return linear.ce_shard_loss(global_max, global_sum, target_logit)
 
     @staticmethod
-    def backward(logits_local, targets, vocab_start, global_max, global_sum, scale):
+    def backward(logits_local, targets, vocab_start, global_max, global_sum, scale, out=None):
         from . import linear
-        return linear.ce_shard_backward(logits_local, targets, vocab_start, global_max, global_sum, scale)
+        return linear.ce_shard_backward(logits_local, targets, vocab_start, global_max, global_sum, scale, out=out)
 
 
-def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None, ops=CudaShardOps):
+def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None, ops=CudaShardOps, in_place=False,
+                                 exchange=True):
     """Cross-entropy over a vocabulary that is split across ranks.
 
     logits_local [BT, V_r] (bf16) are this rank's columns [vocab_start, vocab_start + V_r) of the LM-head
@@ -104,9 +105,11 @@ def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None,
     reference's crossentropy_softmax_backward (cuda/crossentropy.cu:50-64,124-132).
     Communication: all-reduce MAX of the row maxima, then one all-reduce SUM of [sum-exp, target logit].
     `ops` supplies the four per-shard steps: this library's CUDA kernels unless a test passes a host
-    restatement to exercise the exchange without a GPU."""
+    restatement to exercise the exchange without a GPU.  in_place=True writes dlogits over the logits (the
+    CUDA kernels allow it; no second [BT, V_r] buffer).  exchange=False treats the local columns as the
+    whole vocabulary even inside a process group (a single-GPU baseline run on every rank)."""
     bt = logits_local.shape[0]
-    multi = dist.is_initialized() and dist.get_world_size(group) > 1
+    multi = exchange and dist.is_initialized() and dist.get_world_size(group) > 1
     local_max, row_sum, tgt = ops.stats(logits_local, targets, vocab_start)
     global_max = local_max.clone()
     if multi:
@@ -117,7 +120,10 @@ def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None,
         dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
     global_sum, tgt_logit = packed[0].contiguous(), packed[1].contiguous()
     loss_rows = ops.loss(global_max, global_sum, tgt_logit)
-    d = ops.backward(logits_local, targets, vocab_start, global_max, global_sum, 1.0 / bt)
+    if in_place:
+        d = ops.backward(logits_local, targets, vocab_start, global_max, global_sum, 1.0 / bt, out=logits_local)
+    else:
+        d = ops.backward(logits_local, targets, vocab_start, global_max, global_sum, 1.0 / bt)
     return loss_rows, d
 
 

@@ -1,8 +1,8 @@
 // TEST INFRASTRUCTURE — not part of the product.
 //
-// extern "C" doorway onto the reference's own, unmodified cuda/matmul.cu (cuBLAS) and
-// cuda/crossentropy.cu, so that Python tests and bench.py can call them through ctypes.
-// oracle/build.py compiles this file together with those two sources, taken from where the
+// extern "C" doorway onto the reference's own, unmodified cuda/matmul.cu (cuBLAS), cuda/crossentropy.cu,
+// cuda/attention.cu, cuda/swiglu.cu and cuda/rope.cu, so that Python tests and bench.py can call them through
+// ctypes.  oracle/build.py compiles this file together with those sources, taken from where the
 // reference checkout lies, into oracle/_ref/libref_matmul.so.  Nothing of the reference is copied into this
 // repository: its header is only included at build time.
 #include "kernels.cuh"  // the reference's cuda/kernels.cuh (via -I at build time)
@@ -52,6 +52,53 @@ void ref_crossentropy_forward_bf16(float* losses, const void* logits, const int*
 void ref_crossentropy_backward_bf16(void* dlogits, const void* probs, const int* targets, int B, int T, int V,
                                     float loss_scale) {
     crossentropy_softmax_backward((__nv_bfloat16*)dlogits, (const __nv_bfloat16*)probs, targets, B, T, V, loss_scale);
+}
+
+// cuda/attention.cu, cuda/swiglu.cu, cuda/rope.cu (with cuda/softmax.cu and cuda/residual.cu, which they call):
+// the reference's own layer code on the reference's own cuBLAS GEMMs, as the checker of the library's layer drop-ins.
+void ref_attention_forward_bf16(void* h, void* out, void* q, void* k, void* v, void* att, const void* inp, const void* wq,
+                                const void* wk, const void* wv, const void* wo, int B, int T, int C, int n_head, int n_kv_head,
+                                float rope_theta) {
+    typedef __nv_bfloat16 bf;
+    attention_forward((bf*)out, (bf*)q, (bf*)k, (bf*)v, (bf*)att, (const bf*)inp, (const bf*)wq, (const bf*)wk, (const bf*)wv,
+                      (const bf*)wo, B, T, C, n_head, n_kv_head, rope_theta, (cublasHandle_t)h);
+}
+void ref_attention_backward_bf16(void* h, void* dinp, void* dwq, void* dwk, void* dwv, void* dwo, const void* dout,
+                                 const void* inp, const void* q, const void* k, const void* v, const void* att, const void* wq,
+                                 const void* wk, const void* wv, const void* wo, int B, int T, int C, int n_head, int n_kv_head,
+                                 float rope_theta) {
+    typedef __nv_bfloat16 bf;
+    attention_backward((bf*)dinp, (bf*)dwq, (bf*)dwk, (bf*)dwv, (bf*)dwo, (const bf*)dout, (const bf*)inp, (const bf*)q,
+                       (const bf*)k, (const bf*)v, (const bf*)att, (const bf*)wq, (const bf*)wk, (const bf*)wv, (const bf*)wo, B, T,
+                       C, n_head, n_kv_head, rope_theta, (cublasHandle_t)h);
+}
+void ref_attention_forward_f32(void* h, float* out, float* q, float* k, float* v, float* att, const float* inp, const float* wq,
+                               const float* wk, const float* wv, const float* wo, int B, int T, int C, int n_head, int n_kv_head,
+                               float rope_theta) {
+    attention_forward(out, q, k, v, att, inp, wq, wk, wv, wo, B, T, C, n_head, n_kv_head, rope_theta, (cublasHandle_t)h);
+}
+void ref_attention_backward_f32(void* h, float* dinp, float* dwq, float* dwk, float* dwv, float* dwo, const float* dout,
+                                const float* inp, const float* q, const float* k, const float* v, const float* att,
+                                const float* wq, const float* wk, const float* wv, const float* wo, int B, int T, int C,
+                                int n_head, int n_kv_head, float rope_theta) {
+    attention_backward(dinp, dwq, dwk, dwv, dwo, dout, inp, q, k, v, att, wq, wk, wv, wo, B, T, C, n_head, n_kv_head, rope_theta,
+                       (cublasHandle_t)h);
+}
+void ref_swiglu_forward_bf16(void* h, void* out, void* gate, void* up, void* hidden, const void* inp, const void* w_gate,
+                             const void* w_up, const void* w_down, int BT, int C, int ff) {
+    typedef __nv_bfloat16 bf;
+    swiglu_forward((bf*)out, (bf*)gate, (bf*)up, (bf*)hidden, (const bf*)inp, (const bf*)w_gate, (const bf*)w_up, (const bf*)w_down,
+                   BT, C, ff, (cublasHandle_t)h);
+}
+void ref_swiglu_backward_bf16(void* h, void* dinp, void* dw_gate, void* dw_up, void* dw_down, const void* dout, const void* inp,
+                              const void* gate, const void* up, const void* w_gate, const void* w_up, const void* w_down, int BT,
+                              int C, int ff) {
+    typedef __nv_bfloat16 bf;
+    swiglu_backward((bf*)dinp, (bf*)dw_gate, (bf*)dw_up, (bf*)dw_down, (const bf*)dout, (const bf*)inp, (const bf*)gate,
+                    (const bf*)up, (const bf*)w_gate, (const bf*)w_up, (const bf*)w_down, BT, C, ff, (cublasHandle_t)h);
+}
+void ref_rope_forward_bf16(void* q, void* k, int B, int T, int n_head, int n_kv_head, int head_dim, float theta) {
+    rope_forward((__nv_bfloat16*)q, (__nv_bfloat16*)k, B, T, n_head, n_kv_head, head_dim, theta);
 }
 
 }  // extern "C"
