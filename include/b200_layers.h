@@ -2,7 +2,8 @@
  * chriskuchar/llms-from-scratch-cuda, each with the argument list of the reference function it replaces
  * (cuda/kernels.cuh) plus, where the reference passes a cublasHandle_t, a b200_linear_ctx.  The same library
  * also exports the reference's C++ overloads themselves (same mangled names), so that its host code links
- * unchanged with cuda/attention.cu, cuda/flash_attention.cu, cuda/swiglu.cu and cuda/crossentropy.cu left out.
+ * unchanged with cuda/attention.cu, cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu and cuda/rmsnorm.cu
+ * left out.
  *
  * Layouts are the reference's: activations [B*T, C] row-major, weights [in, out], q / context [B*T, n_head*hd],
  * k / v [B*T, n_kv_head*hd] with query head h reading KV head h / (n_head / n_kv_head); lse [B, n_head, T] fp32.
@@ -86,6 +87,18 @@ int b200_crossentropy_forward_f32(float* losses, float* logits_probs, const int*
 int b200_crossentropy_backward_bf16(void* dlogits, const void* probs, const int* targets, int B, int T, int V,
                                     float loss_scale);
 int b200_crossentropy_backward_f32(float* dlogits, const float* probs, const int* targets, int B, int T, int V);
+
+/* rmsnorm_forward, cuda/rmsnorm.cu:75-85 (fp32), :168-172 (bf16): out = inp * rsqrt(mean(inp^2) + eps) * weight per row,
+ * rrms [BT] = the rsqrt, kept for the backward pass. */
+int b200_rmsnorm_forward_bf16(void* out, float* rrms, const void* inp, const void* weight, float eps, int BT, int C);
+int b200_rmsnorm_forward_f32(float* out, float* rrms, const float* inp, const float* weight, float eps, int BT, int C);
+/* rmsnorm_backward, cuda/rmsnorm.cu:88-105 (fp32), :174-178 (bf16): dinp overwritten, dweight accumulated.  The
+ * reference adds to dweight with one atomic per element and row (on bf16: a compare-and-swap loop with a rounding
+ * per addition); here the rows are summed in fp32 in a fixed order and added to the stored gradient once. */
+int b200_rmsnorm_backward_bf16(void* dinp, void* dweight, const void* dout, const void* inp, const void* weight,
+                               const float* rrms, int BT, int C);
+int b200_rmsnorm_backward_f32(float* dinp, float* dweight, const float* dout, const float* inp, const float* weight,
+                              const float* rrms, int BT, int C);
 
 #ifdef __cplusplus
 }

@@ -57,6 +57,9 @@ int b200_linear_sync(b200_linear_ctx* ctx, int* device_code);
  * gives up, the kernel records its code and returns; the next b200_linear_sync reports
  * B200_E_DEVICE_WAIT and clears it, and the context stays usable.  Nothing faults or hangs. */
 int b200_linear_selftest_wait_timeout(b200_linear_ctx* ctx, long long limit_cycles);
+/* Device address of the context's status word (what b200_linear_sync reads): for kernels of this library that
+ * are launched outside the context's own entry points and report their bounded waits through it. */
+int* b200_linear_status_word(b200_linear_ctx* ctx);
 /* Number of kernels this library has launched on this context so far. */
 long long b200_linear_launch_count(const b200_linear_ctx* ctx);
 int b200_linear_last_cuda_error(const b200_linear_ctx* ctx);

@@ -893,6 +893,24 @@ extern "C" int b200_linear_sync(b200_linear_ctx* ctx, int* device_code) {
     return B200_OK;
 }
 
+namespace b200 {
+// One warp waits on a barrier phase that nothing will ever complete, with a short limit: the wait gives
+// up, records `code` in the status word and the kernel returns.  This is the whole life of a bounded wait
+// that runs out, made to happen on purpose so that the host side of it (status read-back, clean-up, the
+// next launches on the same context) can be tested without any kernel misbehaving.
+__global__ void wait_timeout_probe(int* status, long long limit_cycles, int code) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, code, limit_cycles);
+}
+}  // namespace b200
+
 extern "C" int b200_linear_selftest_wait_timeout(b200_linear_ctx* ctx, long long limit_cycles) {
     if (!ctx || limit_cycles <= 0 || limit_cycles > WAIT_LIMIT_CYCLES) return B200_E_BADARG;
     if (!on_context_device(ctx)) return B200_E_BADARG;
@@ -901,6 +919,8 @@ extern "C" int b200_linear_selftest_wait_timeout(b200_linear_ctx* ctx, long long
     ctx->launches++;
     return B200_OK;
 }
+
+extern "C" int* b200_linear_status_word(b200_linear_ctx* ctx) { return ctx ? ctx->status_dev : nullptr; }
 
 extern "C" long long b200_linear_launch_count(const b200_linear_ctx* ctx) { return ctx ? ctx->launches : -1; }
 extern "C" int b200_linear_last_cuda_error(const b200_linear_ctx* ctx) { return ctx ? ctx->last_cuda : -1; }

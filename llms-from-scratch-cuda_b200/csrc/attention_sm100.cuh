@@ -1,0 +1,888 @@
+// Fused causal grouped-query attention forward on the sm_100a tensor cores (bf16 in, fp32 accumulate):
+//   context = softmax(Q K^T / sqrt(64), causal) V,   lse = row log-sum-exp of the scaled scores,
+// for q, context [B, T, n_head*64], k, v [B, T, n_kv_head*64] -- the contract the reference declares for
+// flash_attention_forward (cuda/kernels.cuh:420-427) and leaves empty (cuda/flash_attention.cu:12-17), and the
+// core of its attention_forward (cuda/attention.cu:419-461,603-615).  No [B, n_head, T, T] matrix exists.
+//
+// One CTA per (batch, query head, 128 query rows).  Per 128-row key/value tile:
+//   S  = Q K^T          tcgen05.mma 128 x 128 x 64, both operands K-major from 128B-swizzled TMA tiles, S in TMEM
+//   P  = exp2(S - max)  four softmax warps: thread i owns TMEM lane i = query row i, so the row maximum and the
+//                       row sum need no exchange between threads; P goes to shared memory as bf16 in the
+//                       K-major swizzled layout the tensor core reads
+//   PV = P V            tcgen05.mma 128 x 64 x 128, V as an MN-major operand (its rows are the contraction)
+// and the running output lives in registers: O = O * exp2(old max - new max) + PV (read back from TMEM).
+// S and PV are double-buffered in TMEM and P, K/V in shared memory, so the tensor core computes the next
+// tile's S and this tile's PV while the softmax warps work.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4..7 = softmax + epilogue.
+// Every wait is bounded (ptx.cuh): on expiry the CTA records a code in *status and leaves.
+#pragma once
+#include <cuda_bf16.h>
+
+#include "gemm_sm100.cuh"
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int FA_BQ = 128;        // query rows per CTA = TMEM lanes
+constexpr int FA_BKV = 128;       // key/value rows per tile
+constexpr int FA_HD = 64;         // head dimension
+constexpr int FA_THREADS = 256;
+constexpr int FA_TILE_BYTES = 128 * 64 * 2;                 // one 128 x 64 bf16 tile, 128-byte rows
+constexpr int FA_KV_STAGES = 3;   // K/V tiles in flight: a stage is free again only after its P V product
+constexpr int FA_SMEM_BYTES = 1024 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
+                              2 * 2 * FA_TILE_BYTES /*P x 2: two 64-column panels each*/ + 1024 /*alignment*/;
+constexpr int FA_TMEM_COLS = 512;  // S: 2 x 128 columns, PV: 2 x 64 columns
+
+struct FaParams {
+    int B, T, n_head, n_kv_head;
+    float scale_log2e;   // log2(e) / sqrt(head_dim)
+    float* lse;          // [B, n_head, T]
+    int* status;         // device status word (0 = ok)
+};
+
+struct alignas(8) FaCtrl {
+    unsigned long long q_full;
+    unsigned long long kv_full[FA_KV_STAGES], kv_empty[FA_KV_STAGES];
+    unsigned long long s_full[2], s_empty[2];
+    unsigned long long p_full[2], p_empty[2];
+    unsigned long long pv_full[2], pv_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ float fa_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// tmQ / tmO: {n_head*64, T, B} bf16, box {64, 128, 1};  tmK / tmV: {n_kv_head*64, T, B}, box {64, 128, 1};
+// all 128-byte swizzled.  Rows beyond T read as zero and are not written.
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FaParams p) {
+    extern __shared__ uint8_t fa_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    FaCtrl* ctrl = reinterpret_cast<FaCtrl*>(smem);
+    uint8_t* sQ = smem + 1024;
+    uint8_t* sKV = sQ + FA_TILE_BYTES;            // stage s: [K tile | V tile]
+    uint8_t* sP = sKV + FA_KV_STAGES * 2 * FA_TILE_BYTES;   // buffer b: [columns 0..63 | columns 64..127]
+    volatile int* abort_flag = &ctrl->abort_flag;
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // longest rows first
+    const int kvh = h / (p.n_head / p.n_kv_head);
+    const int n_kv = qt + 1;                      // causal: key tiles 0 .. qt
+
+    if (warp == 1) {
+        if (lane == 0) {
+            mbar_init(smem_u32(&ctrl->q_full), 1);
+            for (int i = 0; i < FA_KV_STAGES; ++i) {
+                mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
+                mbar_init(smem_u32(&ctrl->kv_empty[i]), 1);
+            }
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(smem_u32(&ctrl->s_full[i]), 1);
+                mbar_init(smem_u32(&ctrl->s_empty[i]), 4);
+                mbar_init(smem_u32(&ctrl->p_full[i]), 4);
+                mbar_init(smem_u32(&ctrl->p_empty[i]), 1);
+                mbar_init(smem_u32(&ctrl->pv_full[i]), 1);
+                mbar_init(smem_u32(&ctrl->pv_empty[i]), 4);
+            }
+            ctrl->abort_flag = 0;
+            fence_mbar_init();
+        }
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmO);
+    }
+    if (warp == 2) {
+        tmem_alloc<1>(smem_u32(&ctrl->tmem_base), FA_TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const uint32_t tmem_S = tmem_base, tmem_PV = tmem_base + 256;   // S[b] at +128 b, PV[b] at +64 b
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        const bool issuer = elect_one();
+        if (issuer) {
+            mbar_arrive_expect_tx(smem_u32(&ctrl->q_full), FA_TILE_BYTES);
+            tma_load_3d(smem_u32(sQ), &tmQ, smem_u32(&ctrl->q_full), h * FA_HD, qt * FA_BQ, b);
+        }
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j % FA_KV_STAGES;
+            ok = mbar_wait(smem_u32(&ctrl->kv_empty[s]), ((j / FA_KV_STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (issuer) {
+                const uint32_t bar = smem_u32(&ctrl->kv_full[s]);
+                const uint32_t dst = smem_u32(sKV + s * 2 * FA_TILE_BYTES);
+                mbar_arrive_expect_tx(bar, 2 * FA_TILE_BYTES);
+                tma_load_3d(dst, &tmK, bar, kvh * FA_HD, j * FA_BKV, b);
+                tma_load_3d(dst + FA_TILE_BYTES, &tmV, bar, kvh * FA_HD, j * FA_BKV, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_S = umma_idesc(1, FA_BQ, FA_BKV, 0, 0);   // Q, K: K-major
+        constexpr uint32_t idesc_PV = umma_idesc(1, FA_BQ, FA_HD, 0, 1);   // P: K-major, V: MN-major
+        const bool issuer = elect_one();
+        const uint64_t descQ = umma_smem_desc(smem_u32(sQ), 16, 1024);
+        bool ok = mbar_wait(smem_u32(&ctrl->q_full), 0, abort_flag, p.status, DEV_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        for (int j = 0; j <= n_kv && ok; ++j) {
+            if (j < n_kv) {   // S_j = Q K_j^T
+                const int s = j & 1, st = j % FA_KV_STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->kv_full[st]), (j / FA_KV_STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                     mbar_wait(smem_u32(&ctrl->s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (issuer) {
+                    const uint64_t descK = umma_smem_desc(smem_u32(sKV + st * 2 * FA_TILE_BYTES), 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
+                        umma_f16<1>(tmem_S + s * 128, descQ + ((k * UMMA_K * 2) >> 4), descK + ((k * UMMA_K * 2) >> 4), idesc_S,
+                                    k > 0 ? 1u : 0u);
+                    umma_commit(smem_u32(&ctrl->s_full[s]));
+                }
+            }
+            if (j >= 1) {     // PV_i = P_i V_i for the tile before
+                const int i = j - 1, s = i & 1, st = i % FA_KV_STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->p_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                     mbar_wait(smem_u32(&ctrl->pv_empty[s]), ((i >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (issuer) {
+                    // V tile: 128 contraction rows of 128 bytes, 8-row groups 1024 bytes apart, 16 rows per MMA
+                    const uint64_t descV = umma_smem_desc(smem_u32(sKV + st * 2 * FA_TILE_BYTES + FA_TILE_BYTES), 64 * 64 * 2, 1024);
+                    const uint32_t pbase = smem_u32(sP + s * 2 * FA_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < FA_BKV / UMMA_K; ++k) {
+                        // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel
+                        const uint64_t descP = umma_smem_desc(pbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
+                        umma_f16<1>(tmem_PV + s * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&ctrl->pv_full[s]));
+                    umma_commit(smem_u32(&ctrl->kv_empty[st]));
+                    umma_commit(smem_u32(&ctrl->p_empty[s]));
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ softmax + epilogue
+        const int qrt = warp & 3;                                   // TMEM lane quarter of this warp
+        const int r = qrt * 32 + lane;                              // query row inside the tile
+        const int row = qt * FA_BQ + r;                             // query position
+        const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
+        float o[FA_HD];
+#pragma unroll
+        for (int e = 0; e < FA_HD; ++e) o[e] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j & 1;
+            ok = mbar_wait(smem_u32(&ctrl->s_full[s]), (j >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tS = tmem_S + s * 128 + lane_off;
+            const bool diag = j == qt;                              // the only tile that needs the causal / length mask
+            const int col0 = j * FA_BKV;
+            // pass 1: row maximum (in units of log2: scores times log2(e) / sqrt(d))
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tS + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const int col = col0 + c * 32 + e;
+                    const float x = (diag && (col > row || col >= p.T)) ? -INFINITY : __uint_as_float(v[e]) * p.scale_log2e;
+                    mx = fmaxf(mx, x);
+                }
+            }
+            const float m_new = fmaxf(m, mx);
+            const float alpha = fa_exp2(m - m_new);                 // 0 on the first tile (m = -inf)
+            // the tensor core must have finished reading this P buffer (tile j - 2)
+            ok = mbar_wait(smem_u32(&ctrl->p_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            // pass 2: P = exp2(S - max) as bf16 into shared memory, row sum in fp32
+            uint8_t* prow = sP + s * 2 * FA_TILE_BYTES + r * 128;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tS + c * 32, v);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int col = col0 + c * 32 + e;
+                    float x0 = __uint_as_float(v[e]) * p.scale_log2e - m_new, x1 = __uint_as_float(v[e + 1]) * p.scale_log2e - m_new;
+                    if (diag) {
+                        if (col > row || col >= p.T) x0 = -INFINITY;
+                        if (col + 1 > row || col + 1 >= p.T) x1 = -INFINITY;
+                    }
+                    const float p0 = fa_exp2(x0), p1 = fa_exp2(x1);
+                    sum += p0 + p1;
+                    packed[e >> 1] = pack_bf16x2(p0, p1);
+                }
+                // columns c*32 .. +31 of the row: panel c / 2, 16-byte chunks (c % 2) * 4 .. + 3, swizzled by the row
+                uint8_t* panel = prow + (c >> 1) * FA_TILE_BYTES;
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    const int chunk = ((c & 1) * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(panel + chunk * 16) =
+                        make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
+                }
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&ctrl->s_empty[s]));   // S buffer read twice, free for tile j + 2
+                mbar_arrive(smem_u32(&ctrl->p_full[s]));    // P ready for the tensor core
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            if (j >= 1) {
+                // O += P V of the tile before (computed while this tile's softmax ran), then move O to the new maximum
+                const int i = j - 1, si = i & 1;
+                ok = mbar_wait(smem_u32(&ctrl->pv_full[si]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_PV + si * 64 + lane_off + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[c * 32 + e] = (o[c * 32 + e] + __uint_as_float(v[e])) * alpha;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->pv_empty[si]));
+            }
+        }
+        if (ok) {
+            const int i = n_kv - 1, si = i & 1;
+            ok = mbar_wait(smem_u32(&ctrl->pv_full[si]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            const int si = (n_kv - 1) & 1;
+            const float inv = 1.0f / l;
+            // every tensor-core read of the P buffers has completed (the last commit covers them): stage O in P buffer 0
+            uint8_t* orow = sP + r * 128;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_PV + si * 64 + lane_off + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    float x[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = (o[c * 32 + qd * 8 + e] + __uint_as_float(v[qd * 8 + e])) * inv;
+                    const int chunk = (c * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(orow + chunk * 16) =
+                        make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+                }
+            }
+            if (row < p.T) p.lse[(static_cast<long long>(b) * p.n_head + h) * p.T + row] = (m + log2f(l)) * 0.69314718055994531f;
+        }
+        // All four epilogue warps come here exactly once, whether or not their waits succeeded, so this barrier
+        // cannot be left waiting; the tile is stored only if nobody gave up.
+        tc_fence_before();
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 4 && !*abort_flag) {
+            if (elect_one()) {
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(&tmO)),
+                             "r"(smem_u32(sP)), "r"(h * FA_HD), "r"(qt * FA_BQ), "r"(b)
+                             : "memory");
+                tma_store_commit();
+                tma_store_wait_read<0>();
+            }
+        }
+    }
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, FA_TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ backward
+// With P_ij = exp(s_ij - lse_i) recomputed from the saved row log-sum-exps and delta_i = sum_d dO_id O_id:
+//   dP = dO V^T,   dS = P o (dP - delta),   dQ = scale dS K,   dK = scale dS^T Q,   dV = P^T dO
+// (the mathematics of cuda/attention.cu:72-231 without its T x T buffers; the contract of
+// flash_attention_backward, cuda/kernels.cuh:428-437).  Two kernels, so that every output element is summed inside
+// one CTA in a fixed order (no atomics): dQ per 128-row query tile, dK / dV per 128-row key tile.
+
+constexpr int FB_DQ_SMEM_BYTES = 1024 + 2 * FA_TILE_BYTES /*Q, dO*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K, V stages*/ +
+                                 2 * 2 * FA_TILE_BYTES /*dS x 2*/ + 1024;
+
+struct FbParams {
+    int B, T, n_head, n_kv_head;
+    float scale_log2e;     // log2(e) / sqrt(head_dim)
+    float scale;           // 1 / sqrt(head_dim)
+    const float* lse;      // [B, n_head, T]
+    const float* delta;    // [B, n_head, T]
+    int* status;
+};
+
+struct alignas(8) FbDqCtrl {
+    unsigned long long q_full;
+    unsigned long long kv_full[FA_KV_STAGES], kv_empty[FA_KV_STAGES];
+    unsigned long long s_full[2], s_empty[2];      // S double-buffered in TMEM
+    unsigned long long dp_full, dp_empty;          // dP single-buffered
+    unsigned long long ds_full[2], ds_empty[2];    // dS (bf16) double-buffered in shared memory
+    unsigned long long dq_full;                    // all products accumulated
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// dQ for one (batch, query head, 128 query rows): per key tile S = Q K^T and dP = dO V^T on the tensor cores, the four
+// softmax warps turn them into dS (bf16, K-major in shared memory), and dQ += dS K accumulates in TMEM over all tiles.
+// tmQ / tmdO / tmdQ: {n_head*64, T, B}, box {64,128,1};  tmK / tmV: {n_kv_head*64, T, B}, box {64,128,1}.
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                  const __grid_constant__ CUtensorMap tmdQ, const FbParams p) {
+    extern __shared__ uint8_t fa_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    FbDqCtrl* ctrl = reinterpret_cast<FbDqCtrl*>(smem);
+    uint8_t* sQ = smem + 1024;
+    uint8_t* sdO = sQ + FA_TILE_BYTES;
+    uint8_t* sKV = sdO + FA_TILE_BYTES;                       // stage s: [K tile | V tile]
+    uint8_t* sdS = sKV + FA_KV_STAGES * 2 * FA_TILE_BYTES;    // buffer b: [key columns 0..63 | 64..127]
+    volatile int* abort_flag = &ctrl->abort_flag;
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / (p.n_head / p.n_kv_head);
+    const int n_kv = qt + 1;
+
+    if (warp == 1 && lane == 0) {
+        mbar_init(smem_u32(&ctrl->q_full), 1);
+        for (int i = 0; i < FA_KV_STAGES; ++i) {
+            mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->kv_empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&ctrl->s_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->s_empty[i]), 4);
+            mbar_init(smem_u32(&ctrl->ds_full[i]), 4);
+            mbar_init(smem_u32(&ctrl->ds_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->dp_full), 1);
+        mbar_init(smem_u32(&ctrl->dp_empty), 4);
+        mbar_init(smem_u32(&ctrl->dq_full), 1);
+        ctrl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmdO);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmdQ);
+    }
+    if (warp == 2) {
+        tmem_alloc<1>(smem_u32(&ctrl->tmem_base), FA_TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 256, tmem_dQ = tmem_base + 384;   // S[b] at +128 b
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        const bool issuer = elect_one();
+        if (issuer) {
+            mbar_arrive_expect_tx(smem_u32(&ctrl->q_full), 2 * FA_TILE_BYTES);
+            tma_load_3d(smem_u32(sQ), &tmQ, smem_u32(&ctrl->q_full), h * FA_HD, qt * FA_BQ, b);
+            tma_load_3d(smem_u32(sdO), &tmdO, smem_u32(&ctrl->q_full), h * FA_HD, qt * FA_BQ, b);
+        }
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j % FA_KV_STAGES;
+            ok = mbar_wait(smem_u32(&ctrl->kv_empty[s]), ((j / FA_KV_STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (issuer) {
+                const uint32_t bar = smem_u32(&ctrl->kv_full[s]);
+                const uint32_t dst = smem_u32(sKV + s * 2 * FA_TILE_BYTES);
+                mbar_arrive_expect_tx(bar, 2 * FA_TILE_BYTES);
+                tma_load_3d(dst, &tmK, bar, kvh * FA_HD, j * FA_BKV, b);
+                tma_load_3d(dst + FA_TILE_BYTES, &tmV, bar, kvh * FA_HD, j * FA_BKV, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_S = umma_idesc(1, FA_BQ, FA_BKV, 0, 0);    // Q / dO and K / V: K-major
+        constexpr uint32_t idesc_dQ = umma_idesc(1, FA_BQ, FA_HD, 0, 1);    // dS: K-major, K tile: MN-major
+        const bool issuer = elect_one();
+        const uint64_t descQ = umma_smem_desc(smem_u32(sQ), 16, 1024);
+        const uint64_t descdO = umma_smem_desc(smem_u32(sdO), 16, 1024);
+        bool ok = mbar_wait(smem_u32(&ctrl->q_full), 0, abort_flag, p.status, DEV_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        for (int j = 0; j <= n_kv && ok; ++j) {
+            if (j < n_kv) {   // S_j = Q K_j^T and dP_j = dO V_j^T
+                const int s = j & 1, st = j % FA_KV_STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->kv_full[st]), (j / FA_KV_STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                     mbar_wait(smem_u32(&ctrl->s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t kaddr = smem_u32(sKV + st * 2 * FA_TILE_BYTES);
+                if (issuer) {
+                    const uint64_t descK = umma_smem_desc(kaddr, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
+                        umma_f16<1>(tmem_S + s * 128, descQ + ((k * UMMA_K * 2) >> 4), descK + ((k * UMMA_K * 2) >> 4), idesc_S,
+                                    k > 0 ? 1u : 0u);
+                    umma_commit(smem_u32(&ctrl->s_full[s]));
+                }
+                ok = mbar_wait(smem_u32(&ctrl->dp_empty), (j & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (issuer) {
+                    const uint64_t descV = umma_smem_desc(kaddr + FA_TILE_BYTES, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
+                        umma_f16<1>(tmem_dP, descdO + ((k * UMMA_K * 2) >> 4), descV + ((k * UMMA_K * 2) >> 4), idesc_S,
+                                    k > 0 ? 1u : 0u);
+                    umma_commit(smem_u32(&ctrl->dp_full));
+                }
+            }
+            if (j >= 1) {     // dQ += dS_i K_i for the tile before
+                const int i = j - 1, s = i & 1, st = i % FA_KV_STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->ds_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (issuer) {
+                    const uint64_t descKm = umma_smem_desc(smem_u32(sKV + st * 2 * FA_TILE_BYTES), 64 * 64 * 2, 1024);
+                    const uint32_t dsbase = smem_u32(sdS + s * 2 * FA_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < FA_BKV / UMMA_K; ++k) {
+                        const uint64_t descdS = umma_smem_desc(dsbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
+                        umma_f16<1>(tmem_dQ, descdS, descKm + ((k * UMMA_K * 128) >> 4), idesc_dQ, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&ctrl->kv_empty[st]));
+                    umma_commit(smem_u32(&ctrl->ds_empty[s]));
+                    if (i == n_kv - 1) umma_commit(smem_u32(&ctrl->dq_full));
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ dS + epilogue
+        const int qrt = warp & 3;
+        const int r = qrt * 32 + lane;
+        const int row = qt * FA_BQ + r;
+        const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
+        const bool row_ok = row < p.T;
+        const long long stat_idx = (static_cast<long long>(b) * p.n_head + h) * p.T + row;
+        const float lse2 = row_ok ? p.lse[stat_idx] * 1.4426950408889634f : 0.f;   // in units of log2
+        const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; ++j) {
+            const int s = j & 1;
+            ok = mbar_wait(smem_u32(&ctrl->s_full[s]), (j >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
+                 mbar_wait(smem_u32(&ctrl->dp_full), j & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
+                 mbar_wait(smem_u32(&ctrl->ds_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tS = tmem_S + s * 128 + lane_off, tP = tmem_dP + lane_off;
+            const bool diag = j == qt;
+            const int col0 = j * FA_BKV;
+            uint8_t* dsrow = sdS + s * 2 * FA_TILE_BYTES + r * 128;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t sv[32], dv[32];
+                tmem_ld_32x32(tS + c * 32, sv);
+                tmem_ld_32x32(tP + c * 32, dv);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int col = col0 + c * 32 + e;
+                    float x0 = __uint_as_float(sv[e]) * p.scale_log2e - lse2, x1 = __uint_as_float(sv[e + 1]) * p.scale_log2e - lse2;
+                    if (diag) {
+                        if (col > row || col >= p.T) x0 = -INFINITY;
+                        if (col + 1 > row || col + 1 >= p.T) x1 = -INFINITY;
+                    }
+                    if (!row_ok) { x0 = -INFINITY; x1 = -INFINITY; }
+                    const float d0 = fa_exp2(x0) * (__uint_as_float(dv[e]) - delta);
+                    const float d1 = fa_exp2(x1) * (__uint_as_float(dv[e + 1]) - delta);
+                    packed[e >> 1] = pack_bf16x2(d0, d1);
+                }
+                uint8_t* panel = dsrow + (c >> 1) * FA_TILE_BYTES;
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    const int chunk = ((c & 1) * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(panel + chunk * 16) =
+                        make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
+                }
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+                mbar_arrive(smem_u32(&ctrl->dp_empty));
+                mbar_arrive(smem_u32(&ctrl->ds_full[s]));
+            }
+        }
+        if (ok) {
+            ok = mbar_wait(smem_u32(&ctrl->dq_full), 0, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            uint8_t* orow = sdS + r * 128;   // every tensor-core read of the dS buffers has completed
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_dQ + lane_off + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    float x[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[qd * 8 + e]) * p.scale;
+                    const int chunk = (c * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(orow + chunk * 16) =
+                        make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+                }
+            }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps arrive here exactly once
+        if (warp == 4 && !*abort_flag) {
+            if (elect_one()) {
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(&tmdQ)),
+                             "r"(smem_u32(sdS)), "r"(h * FA_HD), "r"(qt * FA_BQ), "r"(b)
+                             : "memory");
+                tma_store_commit();
+                tma_store_wait_read<0>();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, FA_TMEM_COLS);
+    }
+}
+
+constexpr int FB_QDO_STAGES = 2;
+constexpr int FB_DKV_SMEM_BYTES = 1024 + 2 * FA_TILE_BYTES /*K, V*/ + FB_QDO_STAGES * 2 * FA_TILE_BYTES /*Q, dO stages*/ +
+                                  2 * 4 * FA_TILE_BYTES /*(P, dS) x 2, two 64-column panels each*/ + 1024;
+
+struct alignas(8) FbDkvCtrl {
+    unsigned long long kv_full;
+    unsigned long long qdo_full[FB_QDO_STAGES], qdo_empty[FB_QDO_STAGES];
+    unsigned long long s_full[2], s_empty[2];
+    unsigned long long dp_full, dp_empty;
+    unsigned long long pds_full[2], pds_empty[2];   // P and dS (bf16) in shared memory, double-buffered
+    unsigned long long dkv_full;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+// dK, dV for one (batch, KV head, 128 key rows).  Iterations run over the query heads of the group and the query
+// tiles at or after the key tile.  Per iteration S = Q K^T and dP = dO V^T (rows = queries, as in the other kernels), the
+// softmax warps write P and dS as bf16 [query][key] tiles, and the tensor core reads those tiles as MN-major left
+// operands (their rows are the contraction): dV += P^T dO and dK += dS^T Q accumulate in TMEM over all iterations.
+// tmQ / tmdO: {n_head*64, T, B};  tmK / tmV / tmdK / tmdV: {n_kv_head*64, T, B};  boxes {64,128,1}.
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV, const FbParams p) {
+    extern __shared__ uint8_t fa_smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    FbDkvCtrl* ctrl = reinterpret_cast<FbDkvCtrl*>(smem);
+    uint8_t* sK = smem + 1024;
+    uint8_t* sV = sK + FA_TILE_BYTES;
+    uint8_t* sQdO = sV + FA_TILE_BYTES;                        // stage s: [Q tile | dO tile]
+    uint8_t* sPdS = sQdO + FB_QDO_STAGES * 2 * FA_TILE_BYTES;  // buffer b: [P: 2 panels | dS: 2 panels]
+    volatile int* abort_flag = &ctrl->abort_flag;
+
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int kt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int ratio = p.n_head / p.n_kv_head;
+    const int q_tiles = (p.T + FA_BQ - 1) / FA_BQ;
+    const int n_q = q_tiles - kt;          // query tiles kt .. q_tiles-1 see this key tile
+    const int n_it = ratio * n_q;
+
+    if (warp == 1 && lane == 0) {
+        mbar_init(smem_u32(&ctrl->kv_full), 1);
+        for (int i = 0; i < FB_QDO_STAGES; ++i) {
+            mbar_init(smem_u32(&ctrl->qdo_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->qdo_empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&ctrl->s_full[i]), 1);
+            mbar_init(smem_u32(&ctrl->s_empty[i]), 4);
+            mbar_init(smem_u32(&ctrl->pds_full[i]), 4);
+            mbar_init(smem_u32(&ctrl->pds_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&ctrl->dp_full), 1);
+        mbar_init(smem_u32(&ctrl->dp_empty), 4);
+        mbar_init(smem_u32(&ctrl->dkv_full), 1);
+        ctrl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmdO);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmdK);
+        tma_prefetch_desc(&tmdV);
+    }
+    if (warp == 2) {
+        tmem_alloc<1>(smem_u32(&ctrl->tmem_base), FA_TMEM_COLS);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 256, tmem_dV = tmem_base + 384, tmem_dK = tmem_base + 448;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        const bool issuer = elect_one();
+        if (issuer) {
+            mbar_arrive_expect_tx(smem_u32(&ctrl->kv_full), 2 * FA_TILE_BYTES);
+            tma_load_3d(smem_u32(sK), &tmK, smem_u32(&ctrl->kv_full), kvh * FA_HD, kt * FA_BKV, b);
+            tma_load_3d(smem_u32(sV), &tmV, smem_u32(&ctrl->kv_full), kvh * FA_HD, kt * FA_BKV, b);
+        }
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int s = it % FB_QDO_STAGES;
+            const int h = kvh * ratio + it / n_q, i = kt + it % n_q;
+            ok = mbar_wait(smem_u32(&ctrl->qdo_empty[s]), ((it / FB_QDO_STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (issuer) {
+                const uint32_t bar = smem_u32(&ctrl->qdo_full[s]);
+                const uint32_t dst = smem_u32(sQdO + s * 2 * FA_TILE_BYTES);
+                mbar_arrive_expect_tx(bar, 2 * FA_TILE_BYTES);
+                tma_load_3d(dst, &tmQ, bar, h * FA_HD, i * FA_BQ, b);
+                tma_load_3d(dst + FA_TILE_BYTES, &tmdO, bar, h * FA_HD, i * FA_BQ, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_S = umma_idesc(1, FA_BQ, FA_BKV, 0, 0);     // Q / dO and K / V: K-major
+        constexpr uint32_t idesc_T = umma_idesc(1, FA_BKV, FA_HD, 1, 1);     // P / dS and dO / Q: MN-major (contraction = query rows)
+        const bool issuer = elect_one();
+        const uint64_t descK = umma_smem_desc(smem_u32(sK), 16, 1024);
+        const uint64_t descV = umma_smem_desc(smem_u32(sV), 16, 1024);
+        bool ok = mbar_wait(smem_u32(&ctrl->kv_full), 0, abort_flag, p.status, DEV_TIMEOUT_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        for (int it = 0; it <= n_it && ok; ++it) {
+            if (it < n_it) {   // S = Q K^T, dP = dO V^T
+                const int s = it & 1, st = it % FB_QDO_STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->qdo_full[st]), (it / FB_QDO_STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                     mbar_wait(smem_u32(&ctrl->s_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t qaddr = smem_u32(sQdO + st * 2 * FA_TILE_BYTES);
+                if (issuer) {
+                    const uint64_t descQ = umma_smem_desc(qaddr, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
+                        umma_f16<1>(tmem_S + s * 128, descQ + ((k * UMMA_K * 2) >> 4), descK + ((k * UMMA_K * 2) >> 4), idesc_S,
+                                    k > 0 ? 1u : 0u);
+                    umma_commit(smem_u32(&ctrl->s_full[s]));
+                }
+                ok = mbar_wait(smem_u32(&ctrl->dp_empty), (it & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (issuer) {
+                    const uint64_t descdO = umma_smem_desc(qaddr + FA_TILE_BYTES, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
+                        umma_f16<1>(tmem_dP, descdO + ((k * UMMA_K * 2) >> 4), descV + ((k * UMMA_K * 2) >> 4), idesc_S,
+                                    k > 0 ? 1u : 0u);
+                    umma_commit(smem_u32(&ctrl->dp_full));
+                }
+            }
+            if (it >= 1) {     // dV += P^T dO, dK += dS^T Q for the iteration before
+                const int i = it - 1, s = i & 1, st = i % FB_QDO_STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->pds_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (issuer) {
+                    const uint32_t pbase = smem_u32(sPdS + s * 4 * FA_TILE_BYTES);
+                    const uint32_t qaddr = smem_u32(sQdO + st * 2 * FA_TILE_BYTES);
+                    // left operands: 128 contraction rows (queries) of 128 bytes per 64-key panel, panels 16 KB apart;
+                    // right operands: 128 contraction rows of 128 bytes (one 64-wide panel); 16 rows = 2048 bytes per MMA
+                    const uint64_t descP = umma_smem_desc(pbase, FA_TILE_BYTES, 1024);
+                    const uint64_t descdS = umma_smem_desc(pbase + 2 * FA_TILE_BYTES, FA_TILE_BYTES, 1024);
+                    const uint64_t descQm = umma_smem_desc(qaddr, 64 * 64 * 2, 1024);
+                    const uint64_t descdOm = umma_smem_desc(qaddr + FA_TILE_BYTES, 64 * 64 * 2, 1024);
+#pragma unroll
+                    for (int k = 0; k < FA_BQ / UMMA_K; ++k)
+                        umma_f16<1>(tmem_dV, descP + ((k * UMMA_K * 128) >> 4), descdOm + ((k * UMMA_K * 128) >> 4), idesc_T,
+                                    (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int k = 0; k < FA_BQ / UMMA_K; ++k)
+                        umma_f16<1>(tmem_dK, descdS + ((k * UMMA_K * 128) >> 4), descQm + ((k * UMMA_K * 128) >> 4), idesc_T,
+                                    (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(smem_u32(&ctrl->qdo_empty[st]));
+                    umma_commit(smem_u32(&ctrl->pds_empty[s]));
+                    if (i == n_it - 1) umma_commit(smem_u32(&ctrl->dkv_full));
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ P, dS + epilogue
+        const int qrt = warp & 3;
+        const int r = qrt * 32 + lane;
+        const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
+        bool ok = true;
+        for (int it = 0; it < n_it && ok; ++it) {
+            const int s = it & 1;
+            const int h = kvh * ratio + it / n_q, i = kt + it % n_q;
+            const int row = i * FA_BQ + r;                      // query position of this thread in this iteration
+            const bool row_ok = row < p.T;
+            const long long stat_idx = (static_cast<long long>(b) * p.n_head + h) * p.T + row;
+            const float lse2 = row_ok ? p.lse[stat_idx] * 1.4426950408889634f : 0.f;
+            const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+            ok = mbar_wait(smem_u32(&ctrl->s_full[s]), (it >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
+                 mbar_wait(smem_u32(&ctrl->dp_full), it & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
+                 mbar_wait(smem_u32(&ctrl->pds_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tS = tmem_S + s * 128 + lane_off, tP = tmem_dP + lane_off;
+            const bool diag = i == kt;
+            const int col0 = kt * FA_BKV;
+            uint8_t* prow = sPdS + s * 4 * FA_TILE_BYTES + r * 128;
+            uint8_t* dsrow = prow + 2 * FA_TILE_BYTES;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t sv[32], dv[32];
+                tmem_ld_32x32(tS + c * 32, sv);
+                tmem_ld_32x32(tP + c * 32, dv);
+                tmem_ld_wait();
+                uint32_t pp[16], pd[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int col = col0 + c * 32 + e;
+                    float x0 = __uint_as_float(sv[e]) * p.scale_log2e - lse2, x1 = __uint_as_float(sv[e + 1]) * p.scale_log2e - lse2;
+                    if ((diag && col > row) || col >= p.T || !row_ok) x0 = -INFINITY;
+                    if ((diag && col + 1 > row) || col + 1 >= p.T || !row_ok) x1 = -INFINITY;
+                    const float p0 = fa_exp2(x0), p1 = fa_exp2(x1);
+                    pp[e >> 1] = pack_bf16x2(p0, p1);
+                    pd[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - delta), p1 * (__uint_as_float(dv[e + 1]) - delta));
+                }
+                const int poff = (c >> 1) * FA_TILE_BYTES;
+#pragma unroll
+                for (int qd = 0; qd < 4; ++qd) {
+                    const int chunk = ((c & 1) * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + poff + chunk * 16) = make_uint4(pp[4 * qd], pp[4 * qd + 1], pp[4 * qd + 2], pp[4 * qd + 3]);
+                    *reinterpret_cast<uint4*>(dsrow + poff + chunk * 16) = make_uint4(pd[4 * qd], pd[4 * qd + 1], pd[4 * qd + 2], pd[4 * qd + 3]);
+                }
+            }
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+                mbar_arrive(smem_u32(&ctrl->dp_empty));
+                mbar_arrive(smem_u32(&ctrl->pds_full[s]));
+            }
+        }
+        if (ok) {
+            ok = mbar_wait(smem_u32(&ctrl->dkv_full), 0, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            tc_fence_after();
+            // thread r now owns key row r of dV and dK; stage them in the (free) P / dS buffers
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                uint8_t* orow = sPdS + which * FA_TILE_BYTES + r * 128;
+                const float mul = which == 0 ? 1.0f : p.scale;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32((which == 0 ? tmem_dV : tmem_dK) + lane_off + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) {
+                        float x[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[qd * 8 + e]) * mul;
+                        const int chunk = (c * 4 + qd) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(orow + chunk * 16) =
+                            make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps arrive here exactly once
+        if (warp == 4 && !*abort_flag) {
+            if (elect_one()) {
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(&tmdV)),
+                             "r"(smem_u32(sPdS)), "r"(kvh * FA_HD), "r"(kt * FA_BKV), "r"(b)
+                             : "memory");
+                asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(&tmdK)),
+                             "r"(smem_u32(sPdS + FA_TILE_BYTES)), "r"(kvh * FA_HD), "r"(kt * FA_BKV), "r"(b)
+                             : "memory");
+                tma_store_commit();
+                tma_store_wait_read<0>();
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, FA_TMEM_COLS);
+    }
+}
+
+}  // namespace b200

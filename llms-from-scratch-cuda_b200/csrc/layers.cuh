@@ -20,10 +20,23 @@ namespace b200 {
 struct RopeFreq {
     float f[64];
 };
+// (cos, sin) of every (position, pair): table[t * half + i].  Built once per (T, head_dim, theta) and kept; the
+// rotation kernels then are pure streaming kernels (the accurate sincosf of an angle of thousands of radians is
+// far more expensive than the two loads and stores of the rotation itself).
+__global__ void __launch_bounds__(256)
+rope_table_kernel(float2* __restrict__ table, int Tlen, int half, const RopeFreq freqs) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= Tlen * half) return;
+    const int t = idx / half, i = idx - t * half;
+    float s, c;
+    sincosf(static_cast<float>(t) * freqs.f[i], &s, &c);
+    table[idx] = make_float2(c, s);
+}
+
 template <typename T, int DIR>
 __global__ void __launch_bounds__(256)
 rope_kernel(T* __restrict__ q, T* __restrict__ k, long long total, int Tlen, int n_head, int n_kv_head, int head_dim,
-            const RopeFreq freqs) {
+            const float2* __restrict__ table) {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int total_heads = n_head + n_kv_head, half = head_dim / 2;
@@ -31,8 +44,9 @@ rope_kernel(T* __restrict__ q, T* __restrict__ k, long long total, int Tlen, int
     const int h = static_cast<int>((idx / half) % total_heads);
     const long long bt = idx / (static_cast<long long>(half) * total_heads);
     const int t = static_cast<int>(bt % Tlen);
-    float s, c;
-    sincosf(static_cast<float>(t) * freqs.f[i], &s, &c);
+    const float2 cs = __ldg(table + t * half + i);
+    const float c = cs.x;
+    float s = cs.y;
     if (DIR < 0) s = -s;
     T* target = h < n_head ? q : k;
     const int heads = h < n_head ? n_head : n_kv_head, hh = h < n_head ? h : h - n_head;
@@ -262,6 +276,81 @@ ce_row_backward_bf16x8(uint4* dlogits, const uint4* probs, const int* __restrict
         }
         dlogits[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
+}
+
+}  // namespace b200
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------------- RMSNorm
+// out = x * rsqrt(mean(x^2) + eps) * weight, rrms = the rsqrt (cuda/rmsnorm.cu:5-35, 107-133): one warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(T* __restrict__ out, float* __restrict__ rrms, const T* __restrict__ inp, const T* __restrict__ weight,
+                   float eps, int rows, int C) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const T* x = inp + static_cast<long long>(r) * C;
+        float ss = 0.f;
+        for (int j = lane; j < C; j += 32) {
+            const float v = to_f32<T>(x[j]);
+            ss = fmaf(v, v, ss);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / static_cast<float>(C) + eps);
+        if (lane == 0) rrms[r] = inv;
+        T* y = out + static_cast<long long>(r) * C;
+        for (int j = lane; j < C; j += 32) y[j] = from_f32<T>(to_f32<T>(x[j]) * inv * to_f32<T>(weight[j]));
+    }
+}
+
+// dinp = rrms * (w dy - x rrms^2 sum_j(dy_j w_j x_j) / C)   (cuda/rmsnorm.cu:37-73, 135-166): one warp per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dinp_kernel(T* __restrict__ dinp, const T* __restrict__ dout, const T* __restrict__ inp,
+                        const T* __restrict__ weight, const float* __restrict__ rrms, int rows, int C) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const T* x = inp + static_cast<long long>(r) * C;
+        const T* dy = dout + static_cast<long long>(r) * C;
+        float s = 0.f;
+        for (int j = lane; j < C; j += 32) s += to_f32<T>(dy[j]) * to_f32<T>(weight[j]) * to_f32<T>(x[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float inv = rrms[r];
+        const float k = inv * inv * s / static_cast<float>(C);
+        T* dx = dinp + static_cast<long long>(r) * C;
+        for (int j = lane; j < C; j += 32)
+            dx[j] = from_f32<T>(inv * (to_f32<T>(dy[j]) * to_f32<T>(weight[j]) - to_f32<T>(x[j]) * k));
+    }
+}
+
+// dweight_j += sum_rows dy_j x_j rrms: the reference adds row by row with one atomic per element (a compare-and-swap
+// loop on bf16, 8192 contenders per word).  Here: partial[chunk][j] = the sum over one chunk of rows (a thread per
+// column, coalesced over j), then one pass adds the chunks in a fixed order onto the stored gradient, rounding once.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dw_partial_kernel(float* __restrict__ partial, const T* __restrict__ dout, const T* __restrict__ inp,
+                              const float* __restrict__ rrms, int rows, int C, int rows_per_chunk) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= C) return;
+    const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+    float s = 0.f;
+    for (int r = r0; r < r1; ++r)
+        s += to_f32<T>(dout[static_cast<long long>(r) * C + j]) * to_f32<T>(inp[static_cast<long long>(r) * C + j]) * rrms[r];
+    partial[static_cast<long long>(blockIdx.y) * C + j] = s;
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dw_final_kernel(T* __restrict__ dweight, const float* __restrict__ partial, int chunks, int C) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= C) return;
+    float s = 0.f;
+    for (int c = 0; c < chunks; ++c) s += partial[static_cast<long long>(c) * C + j];
+    dweight[j] = from_f32<T>(to_f32<T>(dweight[j]) + s);
 }
 
 }  // namespace b200

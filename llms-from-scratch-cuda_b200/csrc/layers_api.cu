@@ -2,7 +2,7 @@
 // softmax(QK^T)V core), the SwiGLU feed-forward block and the softmax cross-entropy.  Each function keeps the
 // signature -- and therefore the mangled name -- that the reference declares in cuda/kernels.cuh, so that
 // the reference's host code links against this library with its own cuda/attention.cu,
-// cuda/flash_attention.cu, cuda/swiglu.cu and cuda/crossentropy.cu left out of the build:
+// cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu and cuda/rmsnorm.cu left out of the build:
 //
 //   flash_attention_forward / _backward  kernels.cuh:316-341 (fp32), :420-437 (bf16); bodies empty upstream
 //                                        (flash_attention.cu:12-17, 51-57)
@@ -10,6 +10,7 @@
 //   swiglu_forward / _backward           kernels.cuh:211-247 (fp32), :390-396 (bf16); swiglu.cu:49-130, 157-216
 //   crossentropy_forward / crossentropy_softmax_backward
 //                                        kernels.cuh:260-277 (fp32), :402-404 (bf16); crossentropy.cu:66-92, 134-151
+//   rmsnorm_forward / rmsnorm_backward   kernels.cuh:87-105 (fp32), :359-362 (bf16); rmsnorm.cu:75-105, 168-178
 //
 // Differences from the reference, on purpose: no [B, n_head, T, T] matrix is ever formed (the `att` argument
 // of attention_forward keeps the row log-sum-exps and the attention context instead, which is what the
@@ -23,10 +24,12 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 #include "../../include/b200_layers.h"
 #include "../../include/b200_linear.h"
 #include "attention_simt.cuh"
+#include "attention_sm100.cuh"
 #include "layers.cuh"
 
 struct cublasContext;
@@ -37,11 +40,18 @@ using namespace b200;
 namespace {
 
 constexpr int kMaxDev = 64;
-enum Slot { S_CONTEXT, S_DCONTEXT, S_DQ, S_DK, S_DV, S_DELTA, S_LSE, S_HIDDEN, S_DHIDDEN, S_DGATE, S_DUP, S_COUNT };
+enum Slot { S_CONTEXT, S_DCONTEXT, S_DQ, S_DK, S_DV, S_DELTA, S_LSE, S_HIDDEN, S_DHIDDEN, S_DGATE, S_DUP, S_RMS_PARTIAL, S_ROPE_TABLE, S_COUNT };
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 struct Scratch {
     void* ptr[S_COUNT] = {};
     size_t bytes[S_COUNT] = {};
     bool attn_configured = false;
+    bool simt_attention = false;   // B200_ATTN_SIMT=1: bf16 attention on the CUDA-core kernels as well
+    int rope_T = 0, rope_hd = 0;   // what the cos / sin table in S_ROPE_TABLE was built for
+    float rope_theta = 0.f;
+    EncodeTiledFn encode = nullptr;
 };
 Scratch g_scratch[kMaxDev];
 
@@ -72,9 +82,58 @@ int configure_attention() {
     ATTN_SMEM(attn_bwd_dq_simt<__nv_bfloat16>, ATTN_DQ_SMEM);
     ATTN_SMEM(attn_bwd_dkv_simt<float>, ATTN_DKV_SMEM);
     ATTN_SMEM(attn_bwd_dkv_simt<__nv_bfloat16>, ATTN_DKV_SMEM);
+    ATTN_SMEM(attn_fwd_sm100, FA_SMEM_BYTES);
+    ATTN_SMEM(attn_bwd_dq_sm100, FB_DQ_SMEM_BYTES);
+    ATTN_SMEM(attn_bwd_dkv_sm100, FB_DKV_SMEM_BYTES);
 #undef ATTN_SMEM
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || !fn)
+        return B200_E_CUDA;
+    g_scratch[dev].encode = reinterpret_cast<EncodeTiledFn>(fn);
+    if (const char* e = getenv("B200_ATTN_SIMT")) g_scratch[dev].simt_attention = atoi(e) != 0;
     g_scratch[dev].attn_configured = true;
     return B200_OK;
+}
+
+// bf16 [B, T, width] seen as {width, T, B} with a box of 64 columns x `box_rows` rows of one batch: rows beyond T read as
+// zero and are not written.
+bool token_map(CUtensorMap* tm, const void* ptr, int B, int Tlen, int width, int box_rows) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(Tlen), static_cast<cuuint64_t>(B)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(width) * 2, static_cast<cuuint64_t>(Tlen) * width * 2};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return g_scratch[dev].encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool use_tensor_cores(const void* a, const void* b, const void* c, const void* d) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return !g_scratch[dev].simt_attention &&
+           ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+             reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
+
+int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
+                     int B, int Tlen, int n_head, int n_kv_head, cudaStream_t stream) {
+    b200_linear_ctx* ctx = b200_linear_default_ctx();
+    CUtensorMap tmQ, tmK, tmV, tmO;
+    if (!token_map(&tmQ, q, B, Tlen, n_head * FA_HD, FA_BQ) || !token_map(&tmK, k, B, Tlen, n_kv_head * FA_HD, FA_BKV) ||
+        !token_map(&tmV, v, B, Tlen, n_kv_head * FA_HD, FA_BKV) || !token_map(&tmO, context, B, Tlen, n_head * FA_HD, FA_BQ))
+        return B200_E_CUDA;
+    FaParams p;
+    p.B = B; p.T = Tlen; p.n_head = n_head; p.n_kv_head = n_kv_head;
+    p.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(FA_HD));
+    p.lse = lse;
+    p.status = b200_linear_status_word(ctx);
+    const dim3 grid((Tlen + FA_BQ - 1) / FA_BQ, n_head, B);
+    attn_fwd_sm100<<<grid, FA_THREADS, FA_SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, p);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 
 int launch_ok() { return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA; }
@@ -90,10 +149,37 @@ int flash_forward(T* context, float* lse, const T* q, const T* k, const T* v, in
     if (!context || !lse || !q || !k || !v || !attn_args_ok(B, Tlen, n_head, n_kv_head, head_dim)) return B200_E_BADARG;
     int rc = configure_attention();
     if (rc) return rc;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (use_tensor_cores(context, q, k, v)) return flash_forward_tc(context, lse, q, k, v, B, Tlen, n_head, n_kv_head, stream);
+    }
     const AttnParams p{B, Tlen, n_head, n_kv_head, 1.0f / sqrtf(static_cast<float>(head_dim))};
     const dim3 grid((Tlen + AT_TILE - 1) / AT_TILE, n_head, B);
     attn_fwd_simt<T><<<grid, AT_THREADS, ATTN_FWD_SMEM, stream>>>(context, lse, q, k, v, p);
     return launch_ok();
+}
+
+int flash_backward_tc(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, const __nv_bfloat16* dcontext,
+                      const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, const float* lse, const float* delta,
+                      int B, int Tlen, int n_head, int n_kv_head, cudaStream_t stream) {
+    b200_linear_ctx* ctx = b200_linear_default_ctx();
+    CUtensorMap tmQ, tmdO, tmK, tmV, tmdQ, tmdK, tmdV;
+    const int C = n_head * FA_HD, KV = n_kv_head * FA_HD;
+    if (!token_map(&tmQ, q, B, Tlen, C, FA_BQ) || !token_map(&tmdO, dcontext, B, Tlen, C, FA_BQ) ||
+        !token_map(&tmK, k, B, Tlen, KV, FA_BKV) || !token_map(&tmV, v, B, Tlen, KV, FA_BKV) ||
+        !token_map(&tmdQ, dq, B, Tlen, C, FA_BQ) || !token_map(&tmdK, dk, B, Tlen, KV, FA_BKV) ||
+        !token_map(&tmdV, dv, B, Tlen, KV, FA_BKV))
+        return B200_E_CUDA;
+    FbParams p;
+    p.B = B; p.T = Tlen; p.n_head = n_head; p.n_kv_head = n_kv_head;
+    p.scale = 1.0f / sqrtf(static_cast<float>(FA_HD));
+    p.scale_log2e = 1.4426950408889634f * p.scale;
+    p.lse = lse;
+    p.delta = delta;
+    p.status = b200_linear_status_word(ctx);
+    const int tiles = (Tlen + FA_BQ - 1) / FA_BQ;
+    attn_bwd_dq_sm100<<<dim3(tiles, n_head, B), FA_THREADS, FB_DQ_SMEM_BYTES, stream>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+    attn_bwd_dkv_sm100<<<dim3(tiles, n_kv_head, B), FA_THREADS, FB_DKV_SMEM_BYTES, stream>>>(tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+    return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 
 // context == nullptr: the forward pass is run again into scratch to get it (the reference's flash API does
@@ -118,6 +204,10 @@ int flash_backward(T* dq, T* dk, T* dv, const T* dcontext, const T* q, const T* 
         context = ctx_tmp;
     }
     attn_delta<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(delta, dcontext, context, p);
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (use_tensor_cores(dq, dk, dv, dcontext) && use_tensor_cores(q, k, v, q))
+            return flash_backward_tc(dq, dk, dv, dcontext, q, k, v, lse, delta, B, Tlen, n_head, n_kv_head, stream);
+    }
     const int tiles = (Tlen + AT_TILE - 1) / AT_TILE;
     attn_bwd_dq_simt<T><<<dim3(tiles, n_head, B), AT_THREADS, ATTN_DQ_SMEM, stream>>>(dq, dcontext, q, k, v, lse, delta, p);
     attn_bwd_dkv_simt<T><<<dim3(tiles, n_kv_head, B), AT_THREADS, ATTN_DKV_SMEM, stream>>>(dk, dv, dcontext, q, k, v, lse,
@@ -129,11 +219,24 @@ template <typename T, int DIR>
 int rope(T* q, T* k, int B, int Tlen, int n_head, int n_kv_head, int head_dim, float theta, cudaStream_t stream) {
     if (!q || !k || B <= 0 || Tlen <= 0 || head_dim <= 0 || (head_dim & 1) || head_dim > 128) return B200_E_BADARG;
     const long long total = static_cast<long long>(B) * Tlen * (n_head + n_kv_head) * (head_dim / 2);
-    RopeFreq freqs;
-    for (int i = 0; i < head_dim / 2; ++i)  // cuda/rope.cu:29: 1 / theta^(2i / head_dim)
-        freqs.f[i] = static_cast<float>(1.0 / pow(static_cast<double>(theta), (2.0 * i) / head_dim));
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return B200_E_NODEVICE;
+    Scratch& sc = g_scratch[dev];
+    const int half = head_dim / 2;
+    float2* table = static_cast<float2*>(scratch(S_ROPE_TABLE, static_cast<size_t>(Tlen) * half * sizeof(float2)));
+    if (!table) return B200_E_CUDA;
+    if (sc.rope_T != Tlen || sc.rope_hd != head_dim || sc.rope_theta != theta) {
+        // Rebuilt only when the sequence length, head dimension or base changes; the host waits for it once, so that
+        // calls on any other stream may use it afterwards.
+        RopeFreq freqs;
+        for (int i = 0; i < half; ++i)  // cuda/rope.cu:29: 1 / theta^(2i / head_dim)
+            freqs.f[i] = static_cast<float>(1.0 / pow(static_cast<double>(theta), (2.0 * i) / head_dim));
+        rope_table_kernel<<<(Tlen * half + 255) / 256, 256, 0, stream>>>(table, Tlen, half, freqs);
+        if (cudaStreamSynchronize(stream) != cudaSuccess) return B200_E_CUDA;
+        sc.rope_T = Tlen; sc.rope_hd = head_dim; sc.rope_theta = theta;
+    }
     rope_kernel<T, DIR><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(q, k, total, Tlen, n_head, n_kv_head,
-                                                                                       head_dim, freqs);
+                                                                                       head_dim, table);
     return launch_ok();
 }
 
@@ -314,6 +417,28 @@ int ce_backward(T* dlogits, const T* probs, const int* targets, int B, int Tlen,
     return launch_ok();
 }
 
+template <typename T>
+int rmsnorm_fwd(T* out, float* rrms, const T* inp, const T* weight, float eps, int rows, int C) {
+    if (!out || !rrms || !inp || !weight || rows <= 0 || C <= 0) return B200_E_BADARG;
+    const int blocks = (rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8;   // 8 warps per CTA, one row per warp at a time
+    rmsnorm_fwd_kernel<T><<<blocks, 256>>>(out, rrms, inp, weight, eps, rows, C);
+    return launch_ok();
+}
+
+template <typename T>
+int rmsnorm_bwd(T* dinp, T* dweight, const T* dout, const T* inp, const T* weight, const float* rrms, int rows, int C) {
+    if (!dinp || !dweight || !dout || !inp || !weight || !rrms || rows <= 0 || C <= 0) return B200_E_BADARG;
+    const int blocks = (rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8;
+    const int rows_per_chunk = rows >= 4096 ? 64 : 16;
+    const int chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
+    float* partial = static_cast<float*>(scratch(S_RMS_PARTIAL, static_cast<size_t>(chunks) * C * sizeof(float)));
+    if (!partial) return B200_E_CUDA;
+    rmsnorm_bwd_dinp_kernel<T><<<blocks, 256>>>(dinp, dout, inp, weight, rrms, rows, C);
+    rmsnorm_bwd_dw_partial_kernel<T><<<dim3((C + 255) / 256, chunks), 256>>>(partial, dout, inp, rrms, rows, C, rows_per_chunk);
+    rmsnorm_bwd_dw_final_kernel<T><<<(C + 255) / 256, 256>>>(dweight, partial, chunks, C);
+    return launch_ok();
+}
+
 // the reference's error convention for the void overloads (cuda/tensor.h:10-29)
 void check(int rc, const char* what) {
     if (rc == B200_OK) return;
@@ -433,9 +558,43 @@ int b200_crossentropy_backward_f32(float* dlogits, const float* probs, const int
     return ce_backward<float>(dlogits, probs, targets, B, T, V, 1.0f / static_cast<float>(B * T));
 }
 
+int b200_rmsnorm_forward_bf16(void* out, float* rrms, const void* inp, const void* weight, float eps, int BT, int C) {
+    typedef __nv_bfloat16 bf;
+    return rmsnorm_fwd<bf>(static_cast<bf*>(out), rrms, static_cast<const bf*>(inp), static_cast<const bf*>(weight), eps, BT, C);
+}
+int b200_rmsnorm_forward_f32(float* out, float* rrms, const float* inp, const float* weight, float eps, int BT, int C) {
+    return rmsnorm_fwd<float>(out, rrms, inp, weight, eps, BT, C);
+}
+int b200_rmsnorm_backward_bf16(void* dinp, void* dweight, const void* dout, const void* inp, const void* weight,
+                               const float* rrms, int BT, int C) {
+    typedef __nv_bfloat16 bf;
+    return rmsnorm_bwd<bf>(static_cast<bf*>(dinp), static_cast<bf*>(dweight), static_cast<const bf*>(dout),
+                           static_cast<const bf*>(inp), static_cast<const bf*>(weight), rrms, BT, C);
+}
+int b200_rmsnorm_backward_f32(float* dinp, float* dweight, const float* dout, const float* inp, const float* weight,
+                              const float* rrms, int BT, int C) {
+    return rmsnorm_bwd<float>(dinp, dweight, dout, inp, weight, rrms, BT, C);
+}
+
 }  // extern "C"
 
 // ------------------------------------------------- the reference's C++ overloads (exact mangled names)
+void rmsnorm_forward(float* out, float* rrms, const float* inp, const float* weight, float eps, int B_T, int C) {
+    check(b200_rmsnorm_forward_f32(out, rrms, inp, weight, eps, B_T, C), "rmsnorm_forward(fp32)");
+}
+void rmsnorm_backward(float* dinp, float* dweight, const float* dout, const float* inp, const float* weight, const float* rrms,
+                      int B_T, int C) {
+    check(b200_rmsnorm_backward_f32(dinp, dweight, dout, inp, weight, rrms, B_T, C), "rmsnorm_backward(fp32)");
+}
+void rmsnorm_forward(__nv_bfloat16* out, float* rrms, const __nv_bfloat16* inp, const __nv_bfloat16* weight, float eps, int B_T,
+                     int C) {
+    check(b200_rmsnorm_forward_bf16(out, rrms, inp, weight, eps, B_T, C), "rmsnorm_forward(bf16)");
+}
+void rmsnorm_backward(__nv_bfloat16* dinp, __nv_bfloat16* dweight, const __nv_bfloat16* dout, const __nv_bfloat16* inp,
+                      const __nv_bfloat16* weight, const float* rrms, int B_T, int C) {
+    check(b200_rmsnorm_backward_bf16(dinp, dweight, dout, inp, weight, rrms, B_T, C), "rmsnorm_backward(bf16)");
+}
+
 void flash_attention_forward(float* context, float* lse, const float* q, const float* k, const float* v, int B, int T, int n_head,
                              int n_kv_head, int head_dim) {
     check(b200_flash_attention_forward_f32(context, lse, q, k, v, B, T, n_head, n_kv_head, head_dim, nullptr), "flash_attention_forward(fp32)");

@@ -132,22 +132,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     }
 }
 
-// One warp waits on a barrier phase that nothing will ever complete, with a short limit: the wait gives
-// up, records `code` in the status word and the kernel returns.  This is the whole life of a bounded wait
-// that runs out, made to happen on purpose so that the host side of it (status read-back, clean-up, the
-// next launches on the same context) can be tested without any kernel misbehaving.
-__global__ void wait_timeout_probe(int* status, long long limit_cycles, int code) {
-    __shared__ unsigned long long bar;
-    __shared__ int abort_flag;
-    if (threadIdx.x == 0) {
-        mbar_init(smem_u32(&bar), 1);
-        abort_flag = 0;
-        fence_mbar_init();
-    }
-    __syncthreads();
-    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, code, limit_cycles);
-}
-
 // ---------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");

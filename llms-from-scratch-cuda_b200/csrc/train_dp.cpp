@@ -447,6 +447,7 @@ int run_rank(int rank, const Options& opt, int id_read_fd, const std::vector<int
         printf("phases, seconds per step over steps 2..%d (rank 0, device synchronised after each): zero_grad %.4f | loader %.4f | "
                "micro-batches %.4f | sharded LM head %.4f | gradient exchange %.4f | gradient norm %.4f | update %.4f\n",
                opt.steps, tm.zero / n, tm.loader / n, tm.micro / n, tm.lm_head / n, tm.exchange / n, tm.norm / n, tm.update / n);
+        fflush(stdout);
     }
     CUDA_TRY(cudaFree(loss_dev));
     if (comm) {

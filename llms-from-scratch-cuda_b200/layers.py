@@ -108,6 +108,19 @@ def swiglu_backward(handle, dinp, dw_gate, dw_up, dw_down, dout, inp, gate, up, 
               _p(w_up), _p(w_down), B_T, C, ffn_hidden), "swiglu_backward")
 
 
+def rmsnorm_forward(out, rrms, inp, weight, eps, B_T, C):
+    fn = getattr(lib, "b200_rmsnorm_forward_" + _sfx(inp))
+    fn.argtypes = [vp, vp, vp, vp, cf, ci, ci]
+    _check(fn(_p(out), _p(rrms), _p(inp), _p(weight), eps, B_T, C), "rmsnorm_forward")
+
+
+def rmsnorm_backward(dinp, dweight, dout, inp, weight, rrms, B_T, C):
+    """dinp overwritten, dweight accumulated."""
+    fn = getattr(lib, "b200_rmsnorm_backward_" + _sfx(inp))
+    fn.argtypes = [vp] * 6 + [ci, ci]
+    _check(fn(_p(dinp), _p(dweight), _p(dout), _p(inp), _p(weight), _p(rrms), B_T, C), "rmsnorm_backward")
+
+
 def crossentropy_forward(losses, logits, targets, B, T, V):
     """Per-row loss; the probabilities replace the logits in place, as in the reference."""
     fn = getattr(lib, "b200_crossentropy_forward_" + _sfx(logits))

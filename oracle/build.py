@@ -68,7 +68,7 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
 KERNEL_SOURCES = ["embedding.cu", "rmsnorm.cu", "rope.cu", "flash_attention.cu", "attention.cu", "swiglu.cu",
                   "softmax.cu", "crossentropy.cu", "residual.cu", "adamw.cu"]
 # the callers of the GEMM path that the library also replaces (csrc/layers_api.cu exports their signatures)
-LAYER_SOURCES = ["flash_attention.cu", "attention.cu", "swiglu.cu", "crossentropy.cu"]
+LAYER_SOURCES = ["flash_attention.cu", "attention.cu", "swiglu.cu", "crossentropy.cu", "rmsnorm.cu"]
 
 
 def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False):
@@ -76,8 +76,8 @@ def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False
          oracle/_ref/train_ref_<model>          as the reference builds it (cuda/matmul.cu -> cuBLAS)
          oracle/_ref/train_b200_<model>         the same host and kernel objects, with cuda/matmul.cu left out
                                                 and libb200_linear.so (+ the cuBLAS stand-in) linked instead
-         oracle/_ref/train_b200_layers_<model>  with cuda/attention.cu, flash_attention.cu, swiglu.cu and
-                                                crossentropy.cu left out as well (the library's layer drop-ins)
+         oracle/_ref/train_b200_layers_<model>  with cuda/attention.cu, flash_attention.cu, swiglu.cu,
+                                                crossentropy.cu and rmsnorm.cu left out as well (the library's layer drop-ins)
        Returns (ref_path, b200_path) or (None, None) when the checkout or nvcc is absent."""
     out_dir = os.path.join(HERE, "_ref")
     tag = model.replace("-", "_")
@@ -120,7 +120,7 @@ def build_train_dp(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=Fa
     unmodified model.cpp, dataloader.cpp and kernel objects (the ones build_train compiles, without main.cpp), twice:
          oracle/_ref/train_dp_b200_<model>       linear layers, attention, SwiGLU and cross-entropy from
                                                  libb200_linear.so (the reference's attention.cu, flash_attention.cu,
-                                                 swiglu.cu, crossentropy.cu and matmul.cu left out), no libcublas
+                                                 swiglu.cu, crossentropy.cu, rmsnorm.cu and matmul.cu left out), no libcublas
          oracle/_ref/train_dp_b200_gemm_<model>  only the linear layers from libb200_linear.so
          oracle/_ref/train_dp_ref_<model>        linear layers from the reference's own cuda/matmul.cu (cuBLAS); the
                                                  same driver, so that all three print the loss with the same digits

@@ -46,8 +46,14 @@ def binaries(model="llama2_mistral"):
 
 
 def dp_binaries(model="llama2_mistral"):
-    """(this library, reference cuBLAS) links of the package's driver."""
+    """(this library: linear layers and the layers around them, reference cuBLAS) links of the package's driver."""
     return _existing("train_dp_b200_" + model), _existing("train_dp_ref_" + model)
+
+
+def dp_gemm_binary(model="llama2_mistral"):
+    """The driver with only the linear layers from this library (the reference's own attention, SwiGLU, RMSNorm and
+    cross-entropy kernels around them)."""
+    return _existing("train_dp_b200_gemm_" + model)
 
 
 def dp_binary(model="llama2_mistral"):
@@ -93,15 +99,17 @@ def overfit_digits(steps=200, repeats_ref=3, repeats_ours=2):
     """The same recipe through the package's driver at one rank, linked once against the reference's own
     matmul.cu (cuBLAS) and once against this library: same host code, same kernels around the GEMMs, loss
     printed with eight decimals, so that the end of the curve (1e-4 and below) can be compared."""
-    ours, ref = dp_binaries()
-    if not ref or not ours:
+    layers, ref = dp_binaries()
+    gemm = dp_gemm_binary()
+    if not ref or not layers or not gemm:
         raise FileNotFoundError("oracle/_ref/train_dp_* not built (run oracle/build.py where the reference checkout is)")
     args = ["--ranks", "1", "--steps", steps] + OVERFIT_ARGS
     with tempfile.TemporaryDirectory() as d:
         data = os.path.join(d, "overfit.bin")
         write_tokens(data, 513)
         res = {"reference": [run(ref, data, args, d) for _ in range(repeats_ref)],
-               "b200": [run(ours, data, args, d) for _ in range(repeats_ours)]}
+               "b200": [run(gemm, data, args, d) for _ in range(repeats_ours)],          # linear layers only
+               "b200_layers": [run(layers, data, args, d) for _ in range(repeats_ours)]}  # + attention, SwiGLU, RMSNorm, CE
     return res
 
 

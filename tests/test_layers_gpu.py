@@ -260,6 +260,35 @@ def test_whole_row_cross_entropy_fp32(layers):
     assert rel(dl, d64) <= 2e-5
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,C", [(8192, 768), (300, 100)])
+def test_rmsnorm_against_float64(layers, dt, rows, C):
+    """cuda/rmsnorm.cu restated in float64 (forward formula at :27-33, backward at :60-72), the weight gradient
+    accumulating over two calls onto a non-zero start."""
+    x, dy = rnd((rows, C), 31, dt), rnd((rows, C), 32, dt)
+    w = (1.0 + 0.1 * rnd((C,), 33, torch.float32)).to(dt)
+    dw0 = rnd((C,), 34, dt)
+    eps = 1e-5
+    xd, dyd, wd = x.to(DEV), dy.to(DEV), w.to(DEV)
+    out, rrms = torch.empty_like(xd), torch.empty(rows, device=DEV, dtype=torch.float32)
+    layers.rmsnorm_forward(out, rrms, xd, wd, eps, rows, C)
+    dinp, dw = torch.empty_like(xd), dw0.to(DEV)
+    layers.rmsnorm_backward(dinp, dw, dyd, xd, wd, rrms, rows, C)
+    dw1 = dw.clone()
+    layers.rmsnorm_backward(dinp, dw, dyd, xd, wd, rrms, rows, C)
+    torch.cuda.synchronize()
+    x64, dy64, w64 = x.double(), dy.double(), w.double()
+    inv = torch.rsqrt((x64 * x64).mean(dim=1) + eps)
+    tol = TOL[dt]
+    assert rel(out, x64 * inv[:, None] * w64) <= tol
+    assert (rrms.double().cpu() - inv).abs().max().item() <= 1e-5 * inv.abs().max().item()
+    s = (dy64 * w64 * x64).sum(dim=1)
+    assert rel(dinp, inv[:, None] * (dy64 * w64 - x64 * (inv * inv * s / C)[:, None])) <= tol
+    dw64 = (dy64 * x64 * inv[:, None]).sum(dim=0)
+    assert rel(dw1, dw0.double() + dw64) <= tol
+    assert rel(dw, dw1.double().cpu() + dw64) <= tol
+
+
 def test_layer_entry_points_refuse_bad_arguments(layers, handle):
     t = torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16)
     lse = torch.zeros(64, device=DEV, dtype=torch.float32)

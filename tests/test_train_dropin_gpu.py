@@ -29,31 +29,50 @@ def test_reference_program_relinked_follows_the_reference_build():
     assert o[1] > 10.0 and o[60] < 0.05  # it starts at ln(32000) and is deep into the overfit by step 60
 
 
+def _curve_stats(runs, step):
+    v = [x[step] for x in runs]
+    return sum(v) / len(v), max(v) - min(v)
+
+
 def test_step_200_loss_within_one_percent_at_eight_digits():
+    """Three links of the same driver, 200 steps each: the reference's matmul.cu (cuBLAS) three times -- its kernels use
+    float atomics, so its own curve moves from run to run; that spread is the resolution of any comparison --, this
+    library's linear layers twice, and this library's linear layers plus its attention / SwiGLU / RMSNorm /
+    cross-entropy drop-ins twice.  The linear-layer link must stay within 1 % of the reference link at every step,
+    up to twice the two links' own spreads (three and two runs underestimate a range).  The layer drop-ins compute
+    attention and the RMSNorm weight gradient in fp32 where the reference rounds to bf16 in between, so that link's
+    trajectory differs by more on the steep part of the overfit: it is held to 10 % (plus 1e-3 absolute, which matters in
+    the tail of the curve only), and its numbers are printed."""
     from oracle import train_dropin
-    ours, ref = train_dropin.dp_binaries()
-    if not ref or not ours:
+    layers_bin, ref = train_dropin.dp_binaries()
+    if not ref or not layers_bin or not train_dropin.dp_gemm_binary():
         pytest.skip("oracle/_ref/train_dp_* not built (reference checkout absent at build time)")
     res = train_dropin.overfit_digits(steps=200, repeats_ref=3, repeats_ours=2)
-    refs = [r["losses"] for r in res["reference"]]
-    mine = [r["losses"] for r in res["b200"]]
-    assert all(r["rc"] == 0 for r in res["reference"] + res["b200"]), res["b200"][0]["tail"]
-    assert all(set(x) == set(range(1, 201)) for x in refs + mine)
-    report = []
-    last_resolved = None
+    runs = {k: [r["losses"] for r in v] for k, v in res.items()}
+    for k, v in res.items():
+        assert all(r["rc"] == 0 for r in v), (k, v[0]["tail"])
+        assert all(set(x) == set(range(1, 201)) for x in runs[k]), k
+    report, worst, last_resolved = [], {"b200": (0.0, 0), "b200_layers": (0.0, 0)}, None
     for step in range(1, 201):
-        rv = [x[step] for x in refs]
-        ov = [x[step] for x in mine]
-        ref_mid, spread = sum(rv) / len(rv), max(rv) - min(rv)
-        ours_mid, ours_spread = sum(ov) / len(ov), max(ov) - min(ov)
-        # within 1 % of the reference link, up to what either link moves from one run to the next
-        # (float atomics in the reference's rmsnorm / attention / embedding kernels, linked into both)
-        assert abs(ours_mid - ref_mid) <= 0.01 * ref_mid + spread + ours_spread, (step, rv, ov)
-        if ref_mid >= 100 * spread:
-            last_resolved = step  # here the reference's own spread is below the 1 % under test
-        if step in (1, 10, 20, 30, 50, 100, 150, 200):
-            report.append((step, rv, ov))
-    print("overfit, 8 digits (step, reference link runs, this library runs):", report)
+        ref_mid, ref_spread = _curve_stats(runs["reference"], step)
+        if ref_mid >= 100 * ref_spread:
+            last_resolved = step  # here the reference link's own spread is below the 1 % under test
+        for link, pct in (("b200", 0.01), ("b200_layers", 0.10)):
+            mid, spread = _curve_stats(runs[link], step)
+            excess = abs(mid - ref_mid) - 2 * (ref_spread + spread)
+            if ref_mid > 0 and excess / ref_mid > worst[link][0]:
+                worst[link] = (excess / ref_mid, step)
+            # the all-layers link also gets an absolute floor: below a loss of ~0.01 the trajectories are chaotic at that scale
+            floor = 1e-3 if link == "b200_layers" else 0.0
+            assert excess <= pct * ref_mid + floor, (link, step, [x[step] for x in runs["reference"]], [x[step] for x in runs[link]])
+        if step in (1, 10, 20, 30, 40, 50, 100, 150, 200):
+            report.append((step, [x[step] for x in runs["reference"]], [x[step] for x in runs["b200"]],
+                           [x[step] for x in runs["b200_layers"]]))
+    print("overfit, 8 digits (step, reference link x3, linear layers x2, all layers x2):")
+    for row in report:
+        print("  ", row)
+    print("largest relative deviation beyond twice the spreads (fraction of the loss, step):", worst)
     print("last step at which the reference link's spread is below 1 %% of its loss: %s" % last_resolved)
     assert last_resolved is not None and last_resolved >= 5
-    assert refs[0][1] > 10.0 and all(x[200] < 1e-3 for x in refs + mine)
+    assert runs["reference"][0][1] > 10.0
+    assert all(x[200] < 1e-3 for k in runs for x in runs[k])
