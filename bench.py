@@ -481,14 +481,14 @@ def run_vocab_parallel(torch, dist, pkg, h, dev, world, rank):
     return rec
 
 
-def run_train_step(dist, world, rank, args):
+def run_train_step(dist, world, rank, args, link="b200"):
     """The metric's second half: tokens/s of a whole LLaMA-2/Mistral-125M training step (B=16, T=512, 16 micro-batches
     = 131072 tokens per optimizer step, bf16, AdamW) on the ranks of this run, through the package's multi-GPU
     driver csrc/train_dp.cpp (the reference's own model objects with this library's linear layers, one process per
     GPU, NCCL gradient sum).  Rank 0 starts the driver, which forks its own ranks; the ranks of this benchmark hold
     no kernels meanwhile (they wait on the host).  Present only where the binary was built."""
     import tempfile
-    binary = os.path.join(ROOT, "oracle", "_ref", "train_dp_b200_llama2_mistral")
+    binary = os.path.join(ROOT, "oracle", "_ref", "train_dp_%s_llama2_mistral" % link)
     store = None
     if world > 1:
         from torch.distributed.distributed_c10d import _get_default_store
@@ -522,8 +522,10 @@ def run_train_step(dist, world, rank, args):
                 rec = {"metric": "LLaMA-125M train tok/s", "tokens_per_s": int(toks[-1]), "ranks": world,
                        "tokens_per_step": batch * seq * accum, "steps": steps, "timed": "wall clock of step 2 (step 1 carries set-up)",
                        "losses": losses, "phases_s_per_step": phases.group(1) if phases else None, "wall_s": round(wall, 1),
-                       "what": "csrc/train_dp.cpp around the reference's ModelBF16, linear layers from this library, "
-                               "micro-batches dealt to the ranks, one NCCL gradient sum per step"}
+                       "what": ("csrc/train_dp.cpp around the reference's ModelBF16; linear layers, attention, SwiGLU, RMSNorm and "
+                                "cross-entropy from this library; micro-batches dealt to the ranks, one NCCL gradient sum per step")
+                               if link == "b200" else
+                               "the same driver at one rank with the reference's own, unmodified kernels and cuda/matmul.cu (cuBLAS)"}
         if store is not None:
             store.set("b200_train_step_done", "1")
     elif store is not None:
@@ -649,6 +651,8 @@ def run_reference(args):
             us = e0.elapsed_time(e1) / 10 * 1e3
             fl = 2.0 * TOKENS * b["N"] * b["K"] * (1 if kind == "fwd_nn" else 2)
             per.append({"proj": b["name"], "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1)})
+    if args.train_step:
+        base["train_step"] = run_train_step(None, 1, 0, args, link="ref")
     if args.breakdown:
         calls = [(b["name"] + ":fwd", (lambda b=b: lib.ref_matmul_forward_bf16(hd, b["C"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"]))) for b in bufs]
         calls += [(b["name"] + ":bwd", (lambda b=b: lib.ref_matmul_backward_bf16(hd, b["dA"].data_ptr(), b["dB"].data_ptr(), b["dC"].data_ptr(), b["A"].data_ptr(), b["B"].data_ptr(), TOKENS, b["N"], b["K"]))) for b in reversed(bufs)]
@@ -863,6 +867,52 @@ def run_ce_shard(args):
     print(json.dumps(line))
 
 
+def run_attention(args):
+    """The fused causal grouped-query attention core (csrc/attention_sm100.cuh: what fills the reference's empty
+    flash_attention_forward / flash_attention_backward, cuda/flash_attention.cu:12-17,51-57) timed alone on the two
+    model shapes: LLaMA-2/Mistral 125M (B=16, T=512) and LLaMA-3 272M (B=2, T=8192); 12 query heads, 4 KV heads,
+    head dimension 64, bf16.  FLOP counted for the causal half only: forward 4*B*nh*T^2*64/2, backward 2.5 x that."""
+    import importlib
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    layers = importlib.import_module(pkg.__name__ + ".layers")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = measured_peaks()
+    out = {"metric": "fused causal GQA attention core, bf16, head_dim 64, 12 query / 4 KV heads", "unit": "TFLOP/s",
+           "peak": peaks["bf16_tflops"], "peak_source": peaks["source"], "cases": []}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    shapes = [(16, 512), (2, 8192)] if args.attn_shape is None else [tuple(int(x) for x in args.attn_shape.split("x"))]
+    for B, T in shapes:
+        nh, nkv, hd = 12, 4, 64
+        g = torch.Generator(device=dev).manual_seed(B * T)
+        q = torch.randn(B * T, nh * hd, device=dev, generator=g).to(torch.bfloat16)
+        k = torch.randn(B * T, nkv * hd, device=dev, generator=g).to(torch.bfloat16)
+        v = torch.randn(B * T, nkv * hd, device=dev, generator=g).to(torch.bfloat16)
+        do = torch.randn(B * T, nh * hd, device=dev, generator=g).to(torch.bfloat16)
+        ctx, lse = torch.empty_like(q), torch.empty(B, nh, T, device=dev, dtype=torch.float32)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        fwd = lambda: layers.flash_attention_forward(ctx, lse, q, k, v, B, T, nh, nkv, hd)
+        bwd = lambda: layers.flash_attention_backward(dq, dk, dv, do, q, k, v, lse, B, T, nh, nkv, hd, context=ctx)
+        rec = {"B": B, "T": T}
+        for name, fn, mult in (("forward", fwd, 1.0), ("backward", bwd, 2.5)):
+            for _ in range(args.reps):
+                fn()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(args.reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / args.reps * 1e3
+            flop = mult * 4.0 * B * nh * T * T * hd / 2
+            rec[name] = {"us": round(us, 1), "tflops": round(flop / us / 1e6, 1),
+                         "frac_of_measured_peak": round(flop / us / 1e6 / peaks["bf16_tflops"], 3)}
+        out["cases"].append(rec)
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None, help="profile mode: <projection>:<fwd_nn|dgrad_nt|wgrad_tn>")
@@ -882,12 +932,16 @@ def main():
     ap.add_argument("--no-vocab-parallel", dest="vocab_parallel", action="store_false",
                     help="skip the vocabulary-sharded LM head + cross-entropy sub-record")
     ap.add_argument("--train-step-timeout", type=float, default=600.0)
+    ap.add_argument("--attention", action="store_true", help="time the fused attention core on the two model shapes")
+    ap.add_argument("--attn-shape", default=None, help="BxT for --attention (default: 16x512 and 2x8192)")
     ap.add_argument("--no-train-step", dest="train_step", action="store_false",
                     help="skip the whole-training-step sub-record (the multi-GPU driver, 2 optimizer steps)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.ce_shard:
+    if args.attention:
+        run_attention(args)
+    elif args.ce_shard:
         run_ce_shard(args)
     elif args.sweep:
         run_sweep(args)

@@ -2,8 +2,8 @@
  * chriskuchar/llms-from-scratch-cuda, each with the argument list of the reference function it replaces
  * (cuda/kernels.cuh) plus, where the reference passes a cublasHandle_t, a b200_linear_ctx.  The same library
  * also exports the reference's C++ overloads themselves (same mangled names), so that its host code links
- * unchanged with cuda/attention.cu, cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu and cuda/rmsnorm.cu
- * left out.
+ * unchanged with cuda/attention.cu, cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu, cuda/rmsnorm.cu and
+ * cuda/residual.cu left out.
  *
  * Layouts are the reference's: activations [B*T, C] row-major, weights [in, out], q / context [B*T, n_head*hd],
  * k / v [B*T, n_kv_head*hd] with query head h reading KV head h / (n_head / n_kv_head); lse [B, n_head, T] fp32.
@@ -99,6 +99,13 @@ int b200_rmsnorm_backward_bf16(void* dinp, void* dweight, const void* dout, cons
                                const float* rrms, int BT, int C);
 int b200_rmsnorm_backward_f32(float* dinp, float* dweight, const float* dout, const float* inp, const float* weight,
                               const float* rrms, int BT, int C);
+
+/* residual_forward (out = a + b, out may be a) and residual_backward (da += dout, db += dout),
+ * cuda/residual.cu:32-49 (fp32), :68-78 (bf16); n elements. */
+int b200_residual_forward_bf16(void* out, const void* a, const void* b, long long n);
+int b200_residual_forward_f32(float* out, const float* a, const float* b, long long n);
+int b200_residual_backward_bf16(void* da, void* db, const void* dout, long long n);
+int b200_residual_backward_f32(float* da, float* db, const float* dout, long long n);
 
 #ifdef __cplusplus
 }

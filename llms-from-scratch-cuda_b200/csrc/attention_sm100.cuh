@@ -52,7 +52,7 @@ struct alignas(8) FaCtrl {
 
 __device__ __forceinline__ float fa_exp2(float x) {
     float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // pure: the compiler may reorder and interleave these
     return y;
 }
 

@@ -354,3 +354,193 @@ rmsnorm_bwd_dw_final_kernel(T* __restrict__ dweight, const float* __restrict__ p
 }
 
 }  // namespace b200
+
+namespace b200 {
+
+// --------------------------------------------------------------------------------------- residual add
+// out = a + b (cuda/residual.cu:9-16, 52-57; out may alias a) and da += dout, db += dout (:22-29, 59-66), 16 bytes per
+// thread and array where the length and the pointers allow, one element per thread otherwise.
+__device__ __forceinline__ uint4 bf16x8_add(const uint4& x, const uint4& y) {
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 r = __floats2bfloat162_rn(__uint_as_float(xw[j] << 16) + __uint_as_float(yw[j] << 16),
+                                                 __uint_as_float(xw[j] & 0xFFFF0000u) + __uint_as_float(yw[j] & 0xFFFF0000u));
+        o[j] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+__device__ __forceinline__ uint4 f32x4_add(const uint4& x, const uint4& y) {
+    return make_uint4(__float_as_uint(__uint_as_float(x.x) + __uint_as_float(y.x)), __float_as_uint(__uint_as_float(x.y) + __uint_as_float(y.y)),
+                      __float_as_uint(__uint_as_float(x.z) + __uint_as_float(y.z)), __float_as_uint(__uint_as_float(x.w) + __uint_as_float(y.w)));
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_forward_vec(uint4* out, const uint4* a, const uint4* b, long long nvec) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride)
+        out[i] = sizeof(T) == 2 ? bf16x8_add(a[i], b[i]) : f32x4_add(a[i], b[i]);
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_backward_vec(uint4* da, uint4* db, const uint4* dout, long long nvec) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        const uint4 d = dout[i];
+        da[i] = sizeof(T) == 2 ? bf16x8_add(da[i], d) : f32x4_add(da[i], d);
+        db[i] = sizeof(T) == 2 ? bf16x8_add(db[i], d) : f32x4_add(db[i], d);
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_forward_scalar(T* out, const T* a, const T* b, long long n0, long long n) {
+    const long long i = n0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<T>(to_f32<T>(a[i]) + to_f32<T>(b[i]));
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_backward_scalar(T* da, T* db, const T* dout, long long n0, long long n) {
+    const long long i = n0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float d = to_f32<T>(dout[i]);
+        da[i] = from_f32<T>(to_f32<T>(da[i]) + d);
+        db[i] = from_f32<T>(to_f32<T>(db[i]) + d);
+    }
+}
+
+// RoPE on bf16, eight elements (four rotation pairs) per thread; head_dim a multiple of 8, 16-byte aligned rows.
+template <int DIR>
+__global__ void __launch_bounds__(256)
+rope_kernel_bf16x8(uint4* __restrict__ q, uint4* __restrict__ k, long long total_vec, int Tlen, int n_head, int n_kv_head,
+                   int head_dim, const float2* __restrict__ table) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total_vec) return;
+    const int vec_per_head = head_dim / 8, total_heads = n_head + n_kv_head, half = head_dim / 2;
+    const int vi = static_cast<int>(idx % vec_per_head);
+    const int h = static_cast<int>((idx / vec_per_head) % total_heads);
+    const long long bt = idx / (static_cast<long long>(vec_per_head) * total_heads);
+    const int t = static_cast<int>(bt % Tlen);
+    uint4* target = h < n_head ? q : k;
+    const int heads = h < n_head ? n_head : n_kv_head, hh = h < n_head ? h : h - n_head;
+    uint4* p = target + (bt * heads + hh) * vec_per_head + vi;
+    const uint4 u = *p;
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 cs = __ldg(table + t * half + vi * 4 + j);
+        const float c = cs.x, s = DIR < 0 ? -cs.y : cs.y;
+        const float x0 = __uint_as_float(w[j] << 16), x1 = __uint_as_float(w[j] & 0xFFFF0000u);
+        __nv_bfloat162 r = __floats2bfloat162_rn(x0 * c - x1 * s, x0 * s + x1 * c);
+        o[j] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    *p = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// RMSNorm on bf16 with 16-byte accesses (C a multiple of 8, 16-byte aligned rows): one warp per row, the row kept in
+// registers between the reduction and the output (up to 32 * 8 * RMS_VEC_MAX = 2048 columns; wider rows take the
+// generic kernels).
+constexpr int RMS_VEC_MAX = 8;
+__device__ __forceinline__ void bf16x8_unpack(const uint4& u, float (&x)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        x[2 * j] = __uint_as_float(w[j] << 16);
+        x[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ uint4 bf16x8_pack(const float (&x)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 r = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&r);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_bf16x8(uint4* __restrict__ out, float* __restrict__ rrms, const uint4* __restrict__ inp,
+                   const uint4* __restrict__ weight, float eps, int rows, int C) {
+    const int lane = threadIdx.x & 31, nvec = C / 8;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const uint4* x4 = inp + static_cast<long long>(r) * nvec;
+        uint4 xv[RMS_VEC_MAX];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < RMS_VEC_MAX; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                xv[i] = x4[v];
+                float x[8];
+                bf16x8_unpack(xv[i], x);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) ss = fmaf(x[e], x[e], ss);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / static_cast<float>(C) + eps);
+        if (lane == 0) rrms[r] = inv;
+        uint4* y4 = out + static_cast<long long>(r) * nvec;
+#pragma unroll
+        for (int i = 0; i < RMS_VEC_MAX; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                float x[8], w[8];
+                bf16x8_unpack(xv[i], x);
+                bf16x8_unpack(__ldg(weight + v), w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * w[e];
+                y4[v] = bf16x8_pack(x);
+            }
+        }
+    }
+}
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dinp_bf16x8(uint4* __restrict__ dinp, const uint4* __restrict__ dout, const uint4* __restrict__ inp,
+                        const uint4* __restrict__ weight, const float* __restrict__ rrms, int rows, int C) {
+    const int lane = threadIdx.x & 31, nvec = C / 8;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const uint4* x4 = inp + static_cast<long long>(r) * nvec;
+        const uint4* d4 = dout + static_cast<long long>(r) * nvec;
+        uint4 xv[RMS_VEC_MAX], dv[RMS_VEC_MAX];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < RMS_VEC_MAX; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                xv[i] = x4[v];
+                dv[i] = d4[v];
+                float x[8], d[8], w[8];
+                bf16x8_unpack(xv[i], x);
+                bf16x8_unpack(dv[i], d);
+                bf16x8_unpack(__ldg(weight + v), w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s += d[e] * w[e] * x[e];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float inv = rrms[r];
+        const float kk = inv * inv * s / static_cast<float>(C);
+        uint4* o4 = dinp + static_cast<long long>(r) * nvec;
+#pragma unroll
+        for (int i = 0; i < RMS_VEC_MAX; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                float x[8], d[8], w[8];
+                bf16x8_unpack(xv[i], x);
+                bf16x8_unpack(dv[i], d);
+                bf16x8_unpack(__ldg(weight + v), w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = inv * (d[e] * w[e] - x[e] * kk);
+                o4[v] = bf16x8_pack(x);
+            }
+        }
+    }
+}
+
+}  // namespace b200

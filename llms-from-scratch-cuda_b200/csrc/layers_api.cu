@@ -2,7 +2,7 @@
 // softmax(QK^T)V core), the SwiGLU feed-forward block and the softmax cross-entropy.  Each function keeps the
 // signature -- and therefore the mangled name -- that the reference declares in cuda/kernels.cuh, so that
 // the reference's host code links against this library with its own cuda/attention.cu,
-// cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu and cuda/rmsnorm.cu left out of the build:
+// cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu, cuda/rmsnorm.cu and cuda/residual.cu left out of the build:
 //
 //   flash_attention_forward / _backward  kernels.cuh:316-341 (fp32), :420-437 (bf16); bodies empty upstream
 //                                        (flash_attention.cu:12-17, 51-57)
@@ -11,6 +11,7 @@
 //   crossentropy_forward / crossentropy_softmax_backward
 //                                        kernels.cuh:260-277 (fp32), :402-404 (bf16); crossentropy.cu:66-92, 134-151
 //   rmsnorm_forward / rmsnorm_backward   kernels.cuh:87-105 (fp32), :359-362 (bf16); rmsnorm.cu:75-105, 168-178
+//   residual_forward / residual_backward kernels.cuh:280-289 (fp32), :407-408 (bf16); residual.cu:32-49, 68-78
 //
 // Differences from the reference, on purpose: no [B, n_head, T, T] matrix is ever formed (the `att` argument
 // of attention_forward keeps the row log-sum-exps and the attention context instead, which is what the
@@ -235,6 +236,14 @@ int rope(T* q, T* k, int B, int Tlen, int n_head, int n_kv_head, int head_dim, f
         if (cudaStreamSynchronize(stream) != cudaSuccess) return B200_E_CUDA;
         sc.rope_T = Tlen; sc.rope_hd = head_dim; sc.rope_theta = theta;
     }
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if ((head_dim % 8) == 0 && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15) == 0) {
+            const long long total_vec = total / 4;
+            rope_kernel_bf16x8<DIR><<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(
+                reinterpret_cast<uint4*>(q), reinterpret_cast<uint4*>(k), total_vec, Tlen, n_head, n_kv_head, head_dim, table);
+            return launch_ok();
+        }
+    }
     rope_kernel<T, DIR><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(q, k, total, Tlen, n_head, n_kv_head,
                                                                                        head_dim, table);
     return launch_ok();
@@ -421,6 +430,14 @@ template <typename T>
 int rmsnorm_fwd(T* out, float* rrms, const T* inp, const T* weight, float eps, int rows, int C) {
     if (!out || !rrms || !inp || !weight || rows <= 0 || C <= 0) return B200_E_BADARG;
     const int blocks = (rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8;   // 8 warps per CTA, one row per warp at a time
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if ((C % 8) == 0 && C <= 32 * 8 * RMS_VEC_MAX &&
+            ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(inp) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0) {
+            rmsnorm_fwd_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(out), rrms, reinterpret_cast<const uint4*>(inp),
+                                                reinterpret_cast<const uint4*>(weight), eps, rows, C);
+            return launch_ok();
+        }
+    }
     rmsnorm_fwd_kernel<T><<<blocks, 256>>>(out, rrms, inp, weight, eps, rows, C);
     return launch_ok();
 }
@@ -433,9 +450,51 @@ int rmsnorm_bwd(T* dinp, T* dweight, const T* dout, const T* inp, const T* weigh
     const int chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
     float* partial = static_cast<float*>(scratch(S_RMS_PARTIAL, static_cast<size_t>(chunks) * C * sizeof(float)));
     if (!partial) return B200_E_CUDA;
-    rmsnorm_bwd_dinp_kernel<T><<<blocks, 256>>>(dinp, dout, inp, weight, rrms, rows, C);
+    bool vec = false;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        vec = (C % 8) == 0 && C <= 32 * 8 * RMS_VEC_MAX &&
+              ((reinterpret_cast<uintptr_t>(dinp) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(inp) |
+                reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+        if (vec)
+            rmsnorm_bwd_dinp_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(dinp), reinterpret_cast<const uint4*>(dout),
+                                                     reinterpret_cast<const uint4*>(inp), reinterpret_cast<const uint4*>(weight),
+                                                     rrms, rows, C);
+    }
+    if (!vec) rmsnorm_bwd_dinp_kernel<T><<<blocks, 256>>>(dinp, dout, inp, weight, rrms, rows, C);
     rmsnorm_bwd_dw_partial_kernel<T><<<dim3((C + 255) / 256, chunks), 256>>>(partial, dout, inp, rrms, rows, C, rows_per_chunk);
     rmsnorm_bwd_dw_final_kernel<T><<<(C + 255) / 256, 256>>>(dweight, partial, chunks, C);
+    return launch_ok();
+}
+
+template <typename T>
+int residual_fwd(T* out, const T* a, const T* b, long long n) {
+    if (!out || !a || !b || n <= 0) return B200_E_BADARG;
+    constexpr int VEC = 16 / sizeof(T);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0;
+    const long long nvec = aligned ? n / VEC : 0;
+    if (nvec > 0) {
+        const long long blocks = (nvec + 255) / 256;
+        residual_forward_vec<T><<<static_cast<unsigned>(blocks < 148 * 32 ? blocks : 148 * 32), 256>>>(
+            reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b), nvec);
+    }
+    const long long done = nvec * VEC;
+    if (done < n) residual_forward_scalar<T><<<static_cast<unsigned>((n - done + 255) / 256), 256>>>(out, a, b, done, n);
+    return launch_ok();
+}
+
+template <typename T>
+int residual_bwd(T* da, T* db, const T* dout, long long n) {
+    if (!da || !db || !dout || n <= 0) return B200_E_BADARG;
+    constexpr int VEC = 16 / sizeof(T);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(da) | reinterpret_cast<uintptr_t>(db) | reinterpret_cast<uintptr_t>(dout)) & 15) == 0;
+    const long long nvec = aligned ? n / VEC : 0;
+    if (nvec > 0) {
+        const long long blocks = (nvec + 255) / 256;
+        residual_backward_vec<T><<<static_cast<unsigned>(blocks < 148 * 32 ? blocks : 148 * 32), 256>>>(
+            reinterpret_cast<uint4*>(da), reinterpret_cast<uint4*>(db), reinterpret_cast<const uint4*>(dout), nvec);
+    }
+    const long long done = nvec * VEC;
+    if (done < n) residual_backward_scalar<T><<<static_cast<unsigned>((n - done + 255) / 256), 256>>>(da, db, dout, done, n);
     return launch_ok();
 }
 
@@ -558,6 +617,17 @@ int b200_crossentropy_backward_f32(float* dlogits, const float* probs, const int
     return ce_backward<float>(dlogits, probs, targets, B, T, V, 1.0f / static_cast<float>(B * T));
 }
 
+int b200_residual_forward_bf16(void* out, const void* a, const void* b, long long n) {
+    typedef __nv_bfloat16 bf;
+    return residual_fwd<bf>(static_cast<bf*>(out), static_cast<const bf*>(a), static_cast<const bf*>(b), n);
+}
+int b200_residual_forward_f32(float* out, const float* a, const float* b, long long n) { return residual_fwd<float>(out, a, b, n); }
+int b200_residual_backward_bf16(void* da, void* db, const void* dout, long long n) {
+    typedef __nv_bfloat16 bf;
+    return residual_bwd<bf>(static_cast<bf*>(da), static_cast<bf*>(db), static_cast<const bf*>(dout), n);
+}
+int b200_residual_backward_f32(float* da, float* db, const float* dout, long long n) { return residual_bwd<float>(da, db, dout, n); }
+
 int b200_rmsnorm_forward_bf16(void* out, float* rrms, const void* inp, const void* weight, float eps, int BT, int C) {
     typedef __nv_bfloat16 bf;
     return rmsnorm_fwd<bf>(static_cast<bf*>(out), rrms, static_cast<const bf*>(inp), static_cast<const bf*>(weight), eps, BT, C);
@@ -579,6 +649,18 @@ int b200_rmsnorm_backward_f32(float* dinp, float* dweight, const float* dout, co
 }  // extern "C"
 
 // ------------------------------------------------- the reference's C++ overloads (exact mangled names)
+void residual_forward(float* out, const float* a, const float* b, int N) {
+    check(b200_residual_forward_f32(out, a, b, N), "residual_forward(fp32)");
+}
+void residual_backward(float* da, float* db, const float* dout, int N) {
+    check(b200_residual_backward_f32(da, db, dout, N), "residual_backward(fp32)");
+}
+void residual_forward(__nv_bfloat16* out, const __nv_bfloat16* a, const __nv_bfloat16* b, int N) {
+    check(b200_residual_forward_bf16(out, a, b, N), "residual_forward(bf16)");
+}
+void residual_backward(__nv_bfloat16* da, __nv_bfloat16* db, const __nv_bfloat16* dout, int N) {
+    check(b200_residual_backward_bf16(da, db, dout, N), "residual_backward(bf16)");
+}
 void rmsnorm_forward(float* out, float* rrms, const float* inp, const float* weight, float eps, int B_T, int C) {
     check(b200_rmsnorm_forward_f32(out, rrms, inp, weight, eps, B_T, C), "rmsnorm_forward(fp32)");
 }

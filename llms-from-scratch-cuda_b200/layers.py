@@ -121,6 +121,20 @@ def rmsnorm_backward(dinp, dweight, dout, inp, weight, rrms, B_T, C):
     _check(fn(_p(dinp), _p(dweight), _p(dout), _p(inp), _p(weight), _p(rrms), B_T, C), "rmsnorm_backward")
 
 
+def residual_forward(out, a, b, N):
+    """out = a + b (out may be a)."""
+    fn = getattr(lib, "b200_residual_forward_" + _sfx(a))
+    fn.argtypes = [vp, vp, vp, ctypes.c_longlong]
+    _check(fn(_p(out), _p(a), _p(b), N), "residual_forward")
+
+
+def residual_backward(da, db, dout, N):
+    """da += dout, db += dout."""
+    fn = getattr(lib, "b200_residual_backward_" + _sfx(dout))
+    fn.argtypes = [vp, vp, vp, ctypes.c_longlong]
+    _check(fn(_p(da), _p(db), _p(dout), N), "residual_backward")
+
+
 def crossentropy_forward(losses, logits, targets, B, T, V):
     """Per-row loss; the probabilities replace the logits in place, as in the reference."""
     fn = getattr(lib, "b200_crossentropy_forward_" + _sfx(logits))

@@ -68,7 +68,7 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
 KERNEL_SOURCES = ["embedding.cu", "rmsnorm.cu", "rope.cu", "flash_attention.cu", "attention.cu", "swiglu.cu",
                   "softmax.cu", "crossentropy.cu", "residual.cu", "adamw.cu"]
 # the callers of the GEMM path that the library also replaces (csrc/layers_api.cu exports their signatures)
-LAYER_SOURCES = ["flash_attention.cu", "attention.cu", "swiglu.cu", "crossentropy.cu", "rmsnorm.cu"]
+LAYER_SOURCES = ["flash_attention.cu", "attention.cu", "swiglu.cu", "crossentropy.cu", "rmsnorm.cu", "residual.cu"]
 
 
 def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False):

@@ -280,3 +280,31 @@ def test_bounded_wait_that_runs_out_is_reported_and_the_context_survives(pkg, ha
     assert np.abs(db.float().cpu().numpy() - want).max() / np.abs(want).max() <= 1e-2
     with pytest.raises(pkg.LinearError):
         handle.selftest_wait_timeout(0)
+
+
+def test_context_belongs_to_its_device(pkg, handle):
+    """A context is tied to the device that was current when it was created (its kernels' shared-memory opt-in, scratch
+    and tensor maps are that device's): a call made with another device current is refused, and a second context on the
+    second device works (the opt-in is tracked per device)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    dt = torch.bfloat16
+    a0 = torch.randn(256, 256, device="cuda:0").to(dt)
+    try:
+        torch.cuda.set_device(1)
+        with pytest.raises(pkg.LinearError) as e:
+            pkg.matmul_forward(handle, a0.clone(), a0, a0, 256, 256, 256)
+        assert e.value.code == 1
+        h1 = pkg.Handle()
+        a1 = torch.randn(512, 768, device="cuda:1").to(dt)
+        b1 = torch.randn(768, 512, device="cuda:1").to(dt)
+        c1 = torch.empty(512, 512, device="cuda:1", dtype=dt)
+        pkg.matmul_forward(h1, c1, a1, b1, 512, 512, 768)
+        h1.sync()
+        want = a1.double() @ b1.double()
+        assert ((c1.double() - want).abs().max() / want.abs().max()).item() <= 1e-2
+        h1.destroy()
+    finally:
+        torch.cuda.set_device(0)
+    pkg.matmul_forward(handle, a0.clone(), a0, a0, 256, 256, 256)
+    handle.sync()

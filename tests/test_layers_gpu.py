@@ -289,6 +289,28 @@ def test_rmsnorm_against_float64(layers, dt, rows, C):
     assert rel(dw, dw1.double().cpu() + dw64) <= tol
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,offset", [(8192 * 768, 0), (1000003, 0), (4099, 1)])
+def test_residual_add_is_exact(layers, dt, n, offset):
+    """out = a + b and da += dout, db += dout (cuda/residual.cu): one rounding per element, so the result equals the
+    same arithmetic in torch bit for bit; lengths that are not a multiple of the vector width and unaligned starts
+    included; the in-place form the model uses (out = a)."""
+    a = rnd((n + offset,), 41, dt).to(DEV)[offset:]
+    b = rnd((n + offset,), 42, dt).to(DEV)[offset:]
+    want = (a.float() + b.float()).to(dt)
+    out = torch.empty(n + offset, device=DEV, dtype=dt)[offset:]
+    layers.residual_forward(out, a, b, n)
+    x = a.clone() if offset == 0 else None
+    if x is not None:
+        layers.residual_forward(x, x, b, n)
+    da, db = rnd((n + offset,), 43, dt).to(DEV)[offset:], rnd((n + offset,), 44, dt).to(DEV)[offset:]
+    want_da, want_db = (da.float() + a.float()).to(dt), (db.float() + a.float()).to(dt)
+    layers.residual_backward(da, db, a, n)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want) and (x is None or torch.equal(x, want))
+    assert torch.equal(da, want_da) and torch.equal(db, want_db)
+
+
 def test_layer_entry_points_refuse_bad_arguments(layers, handle):
     t = torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16)
     lse = torch.zeros(64, device=DEV, dtype=torch.float32)
