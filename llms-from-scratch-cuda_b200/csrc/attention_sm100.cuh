@@ -13,7 +13,9 @@
 // and the running output lives in registers: O = O * exp2(old max - new max) + PV (read back from TMEM).
 // S and PV are double-buffered in TMEM and P, K/V in shared memory, so the tensor core computes the next
 // tile's S and this tile's PV while the softmax warps work.
-// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4..7 = softmax + epilogue.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4..11 = softmax + epilogue: warps w and w + 4 share
+// a TMEM lane quarter (32 query rows) and split its 128 key columns (and the 64 output columns) in halves, so that every
+// scheduler has two warps to interleave; the two threads of a row exchange their partial maxima through shared memory.
 // Every wait is bounded (ptx.cuh): on expiry the CTA records a code in *status and leaves.
 #pragma once
 #include <cuda_bf16.h>
@@ -26,10 +28,11 @@ namespace b200 {
 constexpr int FA_BQ = 128;        // query rows per CTA = TMEM lanes
 constexpr int FA_BKV = 128;       // key/value rows per tile
 constexpr int FA_HD = 64;         // head dimension
-constexpr int FA_THREADS = 256;
+constexpr int FA_THREADS = 384;   // warps 0-3: producer, MMA issuer, TMEM allocator, idle; warps 4-11: softmax / epilogue
+constexpr int FA_SOFTMAX_WARPS = 8;
 constexpr int FA_TILE_BYTES = 128 * 64 * 2;                 // one 128 x 64 bf16 tile, 128-byte rows
 constexpr int FA_KV_STAGES = 3;   // K/V tiles in flight: a stage is free again only after its P V product
-constexpr int FA_SMEM_BYTES = 1024 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
+constexpr int FA_SMEM_BYTES = 4096 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
                               2 * 2 * FA_TILE_BYTES /*P x 2: two 64-column panels each*/ + 1024 /*alignment*/;
 constexpr int FA_TMEM_COLS = 512;  // S: 2 x 128 columns, PV: 2 x 64 columns
 
@@ -46,9 +49,15 @@ struct alignas(8) FaCtrl {
     unsigned long long s_full[2], s_empty[2];
     unsigned long long p_full[2], p_empty[2];
     unsigned long long pv_full[2], pv_empty[2];
+    unsigned long long xchg[2];        // the two halves of every row have published their partial maximum (per tile parity)
+    unsigned long long lsum;           // ... and their partial row sums (once, at the end)
     uint32_t tmem_base;
     int abort_flag;
+    float part[2][2][FA_BQ];           // [tile parity][half][row]: partial row maxima
+    float lpart[2][FA_BQ];             // [half][row]: partial row sums
 };
+constexpr int FA_CTRL_BYTES = 4096;
+static_assert(sizeof(FaCtrl) <= FA_CTRL_BYTES, "control block");
 
 __device__ __forceinline__ float fa_exp2(float x) {
     float y;
@@ -64,7 +73,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     extern __shared__ uint8_t fa_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     FaCtrl* ctrl = reinterpret_cast<FaCtrl*>(smem);
-    uint8_t* sQ = smem + 1024;
+    uint8_t* sQ = smem + FA_CTRL_BYTES;
     uint8_t* sKV = sQ + FA_TILE_BYTES;            // stage s: [K tile | V tile]
     uint8_t* sP = sKV + FA_KV_STAGES * 2 * FA_TILE_BYTES;   // buffer b: [columns 0..63 | columns 64..127]
     volatile int* abort_flag = &ctrl->abort_flag;
@@ -84,12 +93,14 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             for (int i = 0; i < 2; ++i) {
                 mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-                mbar_init(smem_u32(&ctrl->s_empty[i]), 4);
-                mbar_init(smem_u32(&ctrl->p_full[i]), 4);
+                mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
+                mbar_init(smem_u32(&ctrl->p_full[i]), FA_SOFTMAX_WARPS);
                 mbar_init(smem_u32(&ctrl->p_empty[i]), 1);
                 mbar_init(smem_u32(&ctrl->pv_full[i]), 1);
-                mbar_init(smem_u32(&ctrl->pv_empty[i]), 4);
+                mbar_init(smem_u32(&ctrl->pv_empty[i]), FA_SOFTMAX_WARPS);
+                mbar_init(smem_u32(&ctrl->xchg[i]), FA_SOFTMAX_WARPS);
             }
+            mbar_init(smem_u32(&ctrl->lsum), FA_SOFTMAX_WARPS);
             ctrl->abort_flag = 0;
             fence_mbar_init();
         }
@@ -182,12 +193,14 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ softmax + epilogue
         const int qrt = warp & 3;                                   // TMEM lane quarter of this warp
+        const int half = (warp - 4) >> 2;                           // which 64 key columns / 32 output columns of the row
         const int r = qrt * 32 + lane;                              // query row inside the tile
         const int row = qt * FA_BQ + r;                             // query position
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
-        float o[FA_HD];
+        constexpr int HC = FA_BKV / 2, HO = FA_HD / 2;              // columns of S and of O per thread
+        float o[HO];
 #pragma unroll
-        for (int e = 0; e < FA_HD; ++e) o[e] = 0.f;
+        for (int e = 0; e < HO; ++e) o[e] = 0.f;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
@@ -196,67 +209,70 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tS = tmem_S + s * 128 + lane_off;
+            const uint32_t tS = tmem_S + s * 128 + lane_off + half * HC;
             const bool diag = j == qt;                              // the only tile that needs the causal / length mask
-            const int col0 = j * FA_BKV;
-            // pass 1: row maximum (in units of log2: scores times log2(e) / sqrt(d))
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tS + c * 32, v);
-                tmem_ld_wait();
+            const int col0 = j * FA_BKV + half * HC;
+            // This thread's half of the row of S comes into registers with one wait, scaled to units of log2 (scores
+            // times log2(e) / sqrt(d)) and masked; the S buffer is free for tile j + 2 at once.
+            float x[HC];
+            tmem_ld_32x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+            tmem_ld_32x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+            // partial row maximum: four independent chains, then the other half's through shared memory
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (diag) {
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const int col = col0 + c * 32 + e;
-                    const float x = (diag && (col > row || col >= p.T)) ? -INFINITY : __uint_as_float(v[e]) * p.scale_log2e;
-                    mx = fmaxf(mx, x);
+                for (int e = 0; e < HC; ++e) {
+                    const int col = col0 + e;
+                    x[e] = (col > row || col >= p.T) ? -INFINITY : x[e] * p.scale_log2e;
+                    mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < HC; ++e) {
+                    x[e] *= p.scale_log2e;
+                    mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
                 }
             }
-            const float m_new = fmaxf(m, mx);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            ctrl->part[s][half][r] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->xchg[s]));
+            ok = mbar_wait(smem_u32(&ctrl->xchg[s]), (j >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_PEER);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const float m_new = fmaxf(m, fmaxf(mx, ctrl->part[s][half ^ 1][r]));
             const float alpha = fa_exp2(m - m_new);                 // 0 on the first tile (m = -inf)
             // the tensor core must have finished reading this P buffer (tile j - 2)
             ok = mbar_wait(smem_u32(&ctrl->p_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // pass 2: P = exp2(S - max) as bf16 into shared memory, row sum in fp32
-            uint8_t* prow = sP + s * 2 * FA_TILE_BYTES + r * 128;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tS + c * 32, v);
-                tmem_ld_wait();
+            // P = exp2(S - max) as bf16 into this half's 64-column panel, partial row sum in fp32 (four chains again)
+            uint8_t* panel = sP + s * 2 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    const int col = col0 + c * 32 + e;
-                    float x0 = __uint_as_float(v[e]) * p.scale_log2e - m_new, x1 = __uint_as_float(v[e + 1]) * p.scale_log2e - m_new;
-                    if (diag) {
-                        if (col > row || col >= p.T) x0 = -INFINITY;
-                        if (col + 1 > row || col + 1 >= p.T) x1 = -INFINITY;
-                    }
-                    const float p0 = fa_exp2(x0), p1 = fa_exp2(x1);
-                    sum += p0 + p1;
+                    const float p0 = fa_exp2(x[c * 32 + e] - m_new), p1 = fa_exp2(x[c * 32 + e + 1] - m_new);
+                    sum4[(e >> 1) & 3] += p0 + p1;
                     packed[e >> 1] = pack_bf16x2(p0, p1);
                 }
-                // columns c*32 .. +31 of the row: panel c / 2, 16-byte chunks (c % 2) * 4 .. + 3, swizzled by the row
-                uint8_t* panel = prow + (c >> 1) * FA_TILE_BYTES;
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {
-                    const int chunk = ((c & 1) * 4 + qd) ^ (r & 7);
+                for (int qd = 0; qd < 4; ++qd) {   // 16-byte chunks c * 4 .. + 3 of the 128-byte row, swizzled by the row
+                    const int chunk = (c * 4 + qd) ^ (r & 7);
                     *reinterpret_cast<uint4*>(panel + chunk * 16) =
                         make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
                 }
             }
-            tc_fence_before();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&ctrl->s_empty[s]));   // S buffer read twice, free for tile j + 2
-                mbar_arrive(smem_u32(&ctrl->p_full[s]));    // P ready for the tensor core
-            }
-            l = l * alpha + sum;
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->p_full[s]));    // this warp's part of P is ready for the tensor core
+            l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m = m_new;
             if (j >= 1) {
                 // O += P V of the tile before (computed while this tile's softmax ran), then move O to the new maximum
@@ -265,52 +281,53 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
+                uint32_t pv[HO];
+                tmem_ld_32x32(tmem_PV + si * 64 + lane_off + half * HO, pv);
+                tmem_ld_wait();
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_PV + si * 64 + lane_off + c * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) o[c * 32 + e] = (o[c * 32 + e] + __uint_as_float(v[e])) * alpha;
-                }
+                for (int e = 0; e < HO; ++e) o[e] = (o[e] + __uint_as_float(pv[e])) * alpha;
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctrl->pv_empty[si]));
             }
         }
         if (ok) {
+            // the two halves of a row add up their partial sums
+            ctrl->lpart[half][r] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->lsum));
             const int i = n_kv - 1, si = i & 1;
-            ok = mbar_wait(smem_u32(&ctrl->pv_full[si]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+            ok = mbar_wait(smem_u32(&ctrl->lsum), 0, abort_flag, p.status, DEV_TIMEOUT_PEER) &&
+                 mbar_wait(smem_u32(&ctrl->pv_full[si]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
             tc_fence_after();
             const int si = (n_kv - 1) & 1;
-            const float inv = 1.0f / l;
+            const float l_row = l + ctrl->lpart[half ^ 1][r];
+            const float inv = 1.0f / l_row;
             // every tensor-core read of the P buffers has completed (the last commit covers them): stage O in P buffer 0
             uint8_t* orow = sP + r * 128;
+            uint32_t v[HO];
+            tmem_ld_32x32(tmem_PV + si * 64 + lane_off + half * HO, v);
+            tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_PV + si * 64 + lane_off + c * 32, v);
-                tmem_ld_wait();
+            for (int qd = 0; qd < 4; ++qd) {
+                float y[8];
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {
-                    float x[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) x[e] = (o[c * 32 + qd * 8 + e] + __uint_as_float(v[qd * 8 + e])) * inv;
-                    const int chunk = (c * 4 + qd) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(orow + chunk * 16) =
-                        make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
-                }
+                for (int e = 0; e < 8; ++e) y[e] = (o[qd * 8 + e] + __uint_as_float(v[qd * 8 + e])) * inv;
+                const int chunk = (half * 4 + qd) ^ (r & 7);
+                *reinterpret_cast<uint4*>(orow + chunk * 16) =
+                    make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
             }
-            if (row < p.T) p.lse[(static_cast<long long>(b) * p.n_head + h) * p.T + row] = (m + log2f(l)) * 0.69314718055994531f;
+            if (half == 0 && row < p.T)
+                p.lse[(static_cast<long long>(b) * p.n_head + h) * p.T + row] = (m + log2f(l_row)) * 0.69314718055994531f;
         }
-        // All four epilogue warps come here exactly once, whether or not their waits succeeded, so this barrier
+        // All eight epilogue warps come here exactly once, whether or not their waits succeeded, so this barrier
         // cannot be left waiting; the tile is stored only if nobody gave up.
         tc_fence_before();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (warp == 4 && !*abort_flag) {
             if (elect_one()) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
@@ -391,12 +408,12 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->s_empty[i]), 4);
-            mbar_init(smem_u32(&ctrl->ds_full[i]), 4);
+            mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctrl->ds_full[i]), FA_SOFTMAX_WARPS);
             mbar_init(smem_u32(&ctrl->ds_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctrl->dp_full), 1);
-        mbar_init(smem_u32(&ctrl->dp_empty), 4);
+        mbar_init(smem_u32(&ctrl->dp_empty), FA_SOFTMAX_WARPS);
         mbar_init(smem_u32(&ctrl->dq_full), 1);
         ctrl->abort_flag = 0;
         fence_mbar_init();
@@ -502,6 +519,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ dS + epilogue
         const int qrt = warp & 3;
+        const int half = (warp - 4) >> 2;   // which 64 key columns (and which 32 columns of dQ) of the row
         const int r = qrt * 32 + lane;
         const int row = qt * FA_BQ + r;
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
@@ -523,7 +541,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             const int col0 = j * FA_BKV;
             uint8_t* dsrow = sdS + s * 2 * FA_TILE_BYTES + r * 128;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 2 * half; c < 2 * half + 2; ++c) {
                 uint32_t sv[32], dv[32];
                 tmem_ld_32x32(tS + c * 32, sv);
                 tmem_ld_32x32(tP + c * 32, dv);
@@ -566,8 +584,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (ok) {
             tc_fence_after();
             uint8_t* orow = sdS + r * 128;   // every tensor-core read of the dS buffers has completed
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            {
+                const int c = half;
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_dQ + lane_off + c * 32, v);
                 tmem_ld_wait();
@@ -584,7 +602,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         tc_fence_before();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps arrive here exactly once
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // all eight warps arrive here exactly once
         if (warp == 4 && !*abort_flag) {
             if (elect_one()) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
@@ -653,12 +671,12 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->s_empty[i]), 4);
-            mbar_init(smem_u32(&ctrl->pds_full[i]), 4);
+            mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctrl->pds_full[i]), FA_SOFTMAX_WARPS);
             mbar_init(smem_u32(&ctrl->pds_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctrl->dp_full), 1);
-        mbar_init(smem_u32(&ctrl->dp_empty), 4);
+        mbar_init(smem_u32(&ctrl->dp_empty), FA_SOFTMAX_WARPS);
         mbar_init(smem_u32(&ctrl->dkv_full), 1);
         ctrl->abort_flag = 0;
         fence_mbar_init();
@@ -775,6 +793,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ P, dS + epilogue
         const int qrt = warp & 3;
+        const int half = (warp - 4) >> 2;   // which 64 key columns of the row; in the epilogue: dV (0) or dK (1)
         const int r = qrt * 32 + lane;
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
         bool ok = true;
@@ -798,7 +817,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             uint8_t* prow = sPdS + s * 4 * FA_TILE_BYTES + r * 128;
             uint8_t* dsrow = prow + 2 * FA_TILE_BYTES;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 2 * half; c < 2 * half + 2; ++c) {
                 uint32_t sv[32], dv[32];
                 tmem_ld_32x32(tS + c * 32, sv);
                 tmem_ld_32x32(tP + c * 32, dv);
@@ -837,9 +856,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         if (ok) {
             tc_fence_after();
-            // thread r now owns key row r of dV and dK; stage them in the (free) P / dS buffers
-#pragma unroll
-            for (int which = 0; which < 2; ++which) {
+            // thread (r, half) now owns key row r of dV (half 0) or dK (half 1); stage them in the (free) P / dS buffers
+            {
+                const int which = half;
                 uint8_t* orow = sPdS + which * FA_TILE_BYTES + r * 128;
                 const float mul = which == 0 ? 1.0f : p.scale;
 #pragma unroll
@@ -861,7 +880,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         tc_fence_before();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 128;" ::: "memory");   // all four warps arrive here exactly once
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // all eight warps arrive here exactly once
         if (warp == 4 && !*abort_flag) {
             if (elect_one()) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
