@@ -2,8 +2,8 @@
  * chriskuchar/llms-from-scratch-cuda, each with the argument list of the reference function it replaces
  * (cuda/kernels.cuh) plus, where the reference passes a cublasHandle_t, a b200_linear_ctx.  The same library
  * also exports the reference's C++ overloads themselves (same mangled names), so that its host code links
- * unchanged with cuda/attention.cu, cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu, cuda/rmsnorm.cu and
- * cuda/residual.cu left out.
+ * unchanged with cuda/attention.cu, cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu, cuda/rmsnorm.cu,
+ * cuda/residual.cu and cuda/adamw.cu left out.
  *
  * Layouts are the reference's: activations [B*T, C] row-major, weights [in, out], q / context [B*T, n_head*hd],
  * k / v [B*T, n_kv_head*hd] with query head h reading KV head h / (n_head / n_kv_head); lse [B, n_head, T] fp32.
@@ -106,6 +106,20 @@ int b200_residual_forward_bf16(void* out, const void* a, const void* b, long lon
 int b200_residual_forward_f32(float* out, const float* a, const float* b, long long n);
 int b200_residual_backward_bf16(void* da, void* db, const void* dout, long long n);
 int b200_residual_backward_f32(float* da, float* db, const float* dout, long long n);
+
+/* adamw_update (cuda/adamw.cu:42-58 fp32; :90-99 mixed precision: bf16 weights and gradients, fp32 master weights and
+ * moments), scale_grads (:153-157), fp32_to_bf16 (:165-169): the reference's arithmetic, one element per thread. */
+int b200_adamw_update_f32(float* params, const float* grads, float* m, float* v, float lr, float beta1, float beta2, float eps,
+                          float weight_decay, int t, long long n);
+int b200_adamw_update_bf16(void* params, float* master, const void* grads, float* m, float* v, float lr, float beta1,
+                           float beta2, float eps, float weight_decay, float grad_scale, int t, long long n);
+int b200_scale_f32(float* data, float scale, long long n);
+int b200_f32_to_bf16(const float* src, void* dst, long long n);
+/* compute_grad_norm_bf16, cuda/adamw.cu:171-191: *norm = the global L2 norm of (gradient / loss_scale) over the fp32
+ * embedding gradient and the bf16 rest, whose non-finite or > 65000 entries are zeroed in place.  Two-stage sum in a
+ * fixed order instead of one atomic per 256 elements; synchronises, like the reference's (the result is a host value). */
+int b200_grad_norm_bf16(float* norm, const float* dwte_fp32, long long emb_n, void* grads_bf16, long long rest_n,
+                        float loss_scale);
 
 #ifdef __cplusplus
 }

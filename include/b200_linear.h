@@ -99,6 +99,26 @@ int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out,
 int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int beta1, void* out, long long ld_out,
                              const void* x, long long ld_x, const void* y, long long ld_y, int M, int N, int K);
 
+/* Up to three bf16 products that share an operand, in ONE launch (count = 1..3; dense operands).  This is how the
+ * callers of matmul_forward / matmul_backward that issue several GEMMs on one input are served: the Q, K, V
+ * projections of cuda/attention.cu:597-599 (forward) and :671-688 (backward), gate and up of cuda/swiglu.cu:161-162
+ * and :192-202.
+ *   B200_GEMM_FWD_NN    outs[i][M, Ns[i]]   = xs[0][M, K] * ys[i][K, Ns[i]]
+ *   B200_GEMM_WGRAD_TN  outs[i][K, Ns[i]] (+)= xs[0][M, K]^T * ys[i][M, Ns[i]]
+ *   B200_GEMM_DGRAD_NT  outs[0][M, K]     (+)= sum_i xs[i][M, Ns[i]] * ys[i][K, Ns[i]]^T
+ * The first two lay the products side by side along the output columns (a column tile belongs to one product);
+ * the third runs them through one accumulator, so the sum over i is formed in fp32 and rounded to bf16 once
+ * (the reference adds the three bf16 results with residual_forward: up to three roundings).  Needs Ns[i] % 64 == 0,
+ * K % 8 == 0 (K % 64 == 0 for the weight gradient) and 16-byte-aligned pointers; anything else runs as `count` single
+ * products with beta = 1 accumulation.  No counterpart in the reference (one cuBLAS call per product). */
+int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, void* const* outs,
+                                  const void* const* xs, const void* const* ys, int M, const int* Ns, int K);
+/* matmul_backward for such a group: dA (+)= sum_i dCs[i] * Bs[i]^T (beta1_dA selects +=), dBs[i] += A^T * dCs[i];
+ * two launches side by side, like b200_linear_backward_bf16.  dA or dBs may be NULL. */
+int b200_linear_backward_bf16_grouped(b200_linear_ctx* ctx, int count, void* dA, int beta1_dA, void* const* dBs,
+                                      const void* const* dCs, const void* A, const void* const* Bs, int M,
+                                      const int* Ns, int K);
+
 /* Tuning / introspection.  A plan is what the dispatcher would launch for a bf16 product:
  * tile width BN (output columns per tile; 0 = CUDA-core kernel), cta_pair (1 = 256-row tiles
  * computed by a 2-CTA cluster), and the work split: of `tiles` output tiles the first `dp_tiles`

@@ -307,6 +307,12 @@ int max_resident_clusters(int size, int sm_count) {
 
 }  // namespace
 
+namespace {
+// The plan for an output of Mo x No with a contraction of Kc.  n_align > 0: only tile widths that divide it (a
+// grouped launch, where a tile must not straddle two products).
+void plan_dims(int Mo, int No, int Kc, int sm_count, int n_align, b200_linear_plan_t* plan);
+}  // namespace
+
 extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
                                      b200_linear_plan_t* plan) {
     (void)beta1;
@@ -323,10 +329,17 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
         plan->dp_tiles = plan->tiles;
         return B200_OK;
     }
+    plan_dims(Mo, No, Kc, sm_count, 0, plan);
+    return B200_OK;
+}
+
+namespace {
+void plan_dims(int Mo, int No, int Kc, int sm_count, int n_align, b200_linear_plan_t* plan) {
     static const int cand[6][2] = {{256, 2}, {128, 2}, {256, 1}, {192, 1}, {128, 1}, {64, 1}};
     double best = -1.0;
     for (int ci = 0; ci < 6; ++ci) {
         const int bn = cand[ci][0], ctas = cand[ci][1];
+        if (n_align > 0 && (n_align % bn) != 0) continue;
         if (bn > 64 && bn - No >= 64) continue;  // tile much wider than the output
         if (ctas == 2 && sm_count < 2) continue;
         const int slots = sm_count / ctas;
@@ -368,8 +381,8 @@ extern "C" int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, 
         }
     }
     plan->m_fastest = Mo <= No ? 1 : 0;
-    return B200_OK;
 }
+}  // namespace
 
 // ---------------------------------------------------------------- launch
 namespace {
@@ -416,7 +429,7 @@ int ensure_counters(b200_linear_ctx* ctx, int n, int set = 0) {
 }
 
 template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
-int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
+int launch_one(b200_linear_ctx* ctx, const GemmGroupMaps& gx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
                const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
     using Cfg = TileCfg<BN, CTAS>;
     if (gp.ksplit > 1) {  // the receive space of the cluster exchange must fit the pipeline stages
@@ -448,36 +461,38 @@ int launch_one(b200_linear_ctx* ctx, const CUtensorMap& tmP, const CUtensorMap& 
     attr[1].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD32, gp));
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD32, gx, gp));
     ctx->launches++;
     return B200_OK;
 }
 
 template <bool P_MN, bool Q_MN, bool BETA1>
-int launch_bn(b200_linear_ctx* ctx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+int launch_bn(b200_linear_ctx* ctx, const GemmGroupMaps& gx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
               const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
     if (ctas == 2) {
         switch (bn) {
-            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
-            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
+            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
             default: return B200_E_BADARG;
         }
     }
     switch (bn) {
-        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
-        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
-        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
-        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1>(ctx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
         default: return B200_E_BADARG;
     }
 }
 
 template <bool P_MN, bool Q_MN>
-int launch_beta(b200_linear_ctx* ctx, int bn, int ctas, int beta1, const CUtensorMap& tmP, const CUtensorMap& tmQ,
-                const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
-    return beta1 ? launch_bn<P_MN, Q_MN, true>(ctx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid)
-                 : launch_bn<P_MN, Q_MN, false>(ctx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid);
+int launch_beta(b200_linear_ctx* ctx, const GemmGroupMaps& gx, int bn, int ctas, int beta1, const CUtensorMap& tmP,
+                const CUtensorMap& tmQ, const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
+    return beta1 ? launch_bn<P_MN, Q_MN, true>(ctx, gx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid)
+                 : launch_bn<P_MN, Q_MN, false>(ctx, gx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid);
 }
+// products 1 and 2 of a launch that has none
+const GemmGroupMaps g_no_group = {};
 
 template <typename T>
 int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, const T* y, int M, int N,
@@ -527,6 +542,78 @@ void split_sms_for_backward(b200_linear_ctx* ctx, int M, int N, int K, int* sm_d
     *sm_wgrad = best_w;
 }
 
+// From a plan to the kernel's work schedule: tile shape, splits, grid, split-K scratch.  `honour_force`: take the
+// context's forced tile shape (a test / tuning knob) instead of the plan's.
+int schedule_launch(b200_linear_ctx* ctx, const b200_linear_plan_t& plan, int Mo, int No, int Kc, int sm_count, int overlap_prev,
+                    bool honour_force, GemmParams& gp, int& bn_out, int& ctas_out, int& grid_out) {
+    int rc;
+    int bn = plan.bn, ctas = plan.cta_pair ? 2 : 1, force_splits = 0, ksplit = plan.cluster_split > 1 ? plan.cluster_split : 1;
+    if (honour_force && ctx->force_bn > 0) {
+        bn = ctx->force_bn;
+        ctas = ctx->force_pair ? 2 : 1;
+        force_splits = ctx->force_splits;
+        ksplit = 1;
+        if (force_splits < 0) {  // cluster split: |splits| members per tile
+            ksplit = -force_splits;
+            force_splits = 1;
+            const int kb = ceil_div_i(Kc, BK);
+            if (ksplit > kb) ksplit = kb;
+            if (ksplit < 1) ksplit = 1;
+            const int per = ceil_div_i(kb, ksplit);
+            ksplit = ceil_div_i(kb, per);  // every member owns at least one block
+        }
+    }
+    if (ksplit > 1) force_splits = 1;
+    if (sm_count < ctas) return B200_E_NODEVICE;
+    const int max_slots = ksplit > 1 ? 0x7FFFFFFF : sm_count / ctas;  // CTAs (or pairs) resident at once
+    const Decomp d = decompose(Mo, No, Kc, bn, ctas, ksplit > 1 ? 1 : max_slots, force_splits);
+    const long long items = static_cast<long long>(d.dp_tiles) + d.sk_items;
+    if (items * ksplit * ctas > 0x7FFFFFFFLL || static_cast<long long>(d.tiles) * (d.sk_splits > 1 ? d.sk_splits : 1) > 0x7FFFFFFFLL)
+        return B200_E_TOOBIG;
+    // cluster split: one cluster per tile; otherwise a persistent grid of at most one CTA (pair) per SM
+    const int slots = items < max_slots ? static_cast<int>(items) : max_slots;
+
+    gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
+    gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
+    gp.m_fastest = plan.m_fastest;
+    // Grouped tile order (B200_LINEAR_TILE_GROUP=n): measured no gain over the plain raster on any shape,
+    // up to 8192 x 32000 x 32000, with the runs interleaved; off unless asked for.
+    gp.group = ctx->tile_group > 0 ? ctx->tile_group : 0;
+    gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
+    gp.ksplit = ksplit;
+    gp.late_wait = (overlap_prev && ctx->use_pdl && ctx->overlap_backward) ? 1 : 0;
+    gp.out = nullptr;
+    gp.status = ctx->status_dev;
+    gp.ws = nullptr;
+    gp.sk_counters = nullptr;
+    gp.sk_peer = 0;
+    if (d.sk_items > 0) {
+        // The ranges of a split tile can exchange partial sums among themselves only if they are all
+        // running at once: each must be the first work item of its own CTA (pair) of a grid that fits.
+        const int groups = bn / 32;
+        gp.sk_peer = (d.sk_items <= max_slots && d.sk_splits <= groups && !ctx->no_peer_split) ? 1 : 0;
+        size_t ws_bytes = static_cast<size_t>(d.sk_items) * ctas * BM * bn * sizeof(float);
+        if (gp.sk_peer) {
+            const int maxg = (groups + d.sk_splits - 1) / d.sk_splits;
+            ws_bytes = static_cast<size_t>(d.tiles - d.dp_tiles) * ctas * d.sk_splits * (d.sk_splits - 1) * maxg *
+                       (8 * BM * 4) * sizeof(float);
+        }
+        const int set = overlap_prev ? 1 : 0;  // never share scratch with a kernel that may still be running
+        rc = ensure_workspace(ctx, ws_bytes, set);
+        if (rc) return rc;
+        rc = ensure_counters(ctx, (d.tiles - d.dp_tiles) * ctas, set);
+        if (rc) return rc;
+        gp.ws = set ? ctx->ws2 : ctx->ws;
+        gp.sk_counters = set ? ctx->sk_counters2 : ctx->sk_counters;
+    }
+
+    gp.grp_n[0] = gp.grp_n[1] = gp.grp_k[0] = gp.grp_k[1] = GRP_NONE;
+    bn_out = bn;
+    ctas_out = ctas;
+    grid_out = slots * ctas * ksplit;
+    return B200_OK;
+}
+
 // One bf16 product on the tensor cores (or the CUDA-core kernel for TMA-unfriendly pitches).
 // overlap_prev = 1: the caller vouches that this product neither reads what the kernel launched just
 // before it on the stream writes, nor writes what that kernel touches (the weight gradient after the
@@ -570,66 +657,12 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
     else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = N; p_mn = false; q_mn = false; }
     else { Mo = K; No = N; Kc = M; p_mn = true; q_mn = true; }
 
-    int bn = plan.bn, ctas = plan.cta_pair ? 2 : 1, force_splits = 0, ksplit = plan.cluster_split > 1 ? plan.cluster_split : 1;
-    if (ctx->force_bn > 0) {
-        bn = ctx->force_bn;
-        ctas = ctx->force_pair ? 2 : 1;
-        force_splits = ctx->force_splits;
-        ksplit = 1;
-        if (force_splits < 0) {  // cluster split: |splits| members per tile
-            ksplit = -force_splits;
-            force_splits = 1;
-            const int kb = ceil_div_i(Kc, BK);
-            if (ksplit > kb) ksplit = kb;
-            if (ksplit < 1) ksplit = 1;
-            const int per = ceil_div_i(kb, ksplit);
-            ksplit = ceil_div_i(kb, per);  // every member owns at least one block
-        }
-    }
-    if (ksplit > 1) force_splits = 1;
-    if (sm_count < ctas) return B200_E_NODEVICE;
-    const int max_slots = ksplit > 1 ? 0x7FFFFFFF : sm_count / ctas;  // CTAs (or pairs) resident at once
-    const Decomp d = decompose(Mo, No, Kc, bn, ctas, ksplit > 1 ? 1 : max_slots, force_splits);
-    const long long items = static_cast<long long>(d.dp_tiles) + d.sk_items;
-    if (items * ksplit * ctas > 0x7FFFFFFFLL || static_cast<long long>(d.tiles) * (d.sk_splits > 1 ? d.sk_splits : 1) > 0x7FFFFFFFLL)
-        return B200_E_TOOBIG;
-    // cluster split: one cluster per tile; otherwise a persistent grid of at most one CTA (pair) per SM
-    const int slots = items < max_slots ? static_cast<int>(items) : max_slots;
-
     GemmParams gp;
-    gp.Mo = Mo; gp.No = No; gp.Kc = Kc;
-    gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
-    gp.m_fastest = plan.m_fastest;
-    // Grouped tile order (B200_LINEAR_TILE_GROUP=n): measured no gain over the plain raster on any shape,
-    // up to 8192 x 32000 x 32000, with the runs interleaved; off unless asked for.
-    gp.group = ctx->tile_group > 0 ? ctx->tile_group : 0;
-    gp.dp_tiles = d.dp_tiles; gp.sk_splits = d.sk_splits; gp.kb_per_sk = d.kb_per_sk; gp.sk_items = d.sk_items;
-    gp.ksplit = ksplit;
-    gp.late_wait = (overlap_prev && ctx->use_pdl && ctx->overlap_backward) ? 1 : 0;
+    int bn, ctas, grid;
+    rc = schedule_launch(ctx, plan, Mo, No, Kc, sm_count, overlap_prev, true, gp, bn, ctas, grid);
+    if (rc) return rc;
     gp.out = out;
-    gp.status = ctx->status_dev;
-    gp.ws = nullptr;
-    gp.sk_counters = nullptr;
-    gp.sk_peer = 0;
-    if (d.sk_items > 0) {
-        // The ranges of a split tile can exchange partial sums among themselves only if they are all
-        // running at once: each must be the first work item of its own CTA (pair) of a grid that fits.
-        const int groups = bn / 32;
-        gp.sk_peer = (d.sk_items <= max_slots && d.sk_splits <= groups && !ctx->no_peer_split) ? 1 : 0;
-        size_t ws_bytes = static_cast<size_t>(d.sk_items) * ctas * BM * bn * sizeof(float);
-        if (gp.sk_peer) {
-            const int maxg = (groups + d.sk_splits - 1) / d.sk_splits;
-            ws_bytes = static_cast<size_t>(d.tiles - d.dp_tiles) * ctas * d.sk_splits * (d.sk_splits - 1) * maxg *
-                       (8 * BM * 4) * sizeof(float);
-        }
-        const int set = overlap_prev ? 1 : 0;  // never share scratch with a kernel that may still be running
-        rc = ensure_workspace(ctx, ws_bytes, set);
-        if (rc) return rc;
-        rc = ensure_counters(ctx, (d.tiles - d.dp_tiles) * ctas, set);
-        if (rc) return rc;
-        gp.ws = set ? ctx->ws2 : ctx->ws;
-        gp.sk_counters = set ? ctx->sk_counters2 : ctx->sk_counters;
-    }
+    const int ksplit = gp.ksplit;
 
     // Operand P has Mo rows, operand Q has No rows; x,y map onto them per product.
     // K-major: [rows][Kc], box {BK, rows-per-CTA}.  MN-major: [Kc][rows], one 3-D copy of all the
@@ -656,10 +689,116 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
         if (rc) return rc;
     }
 
-    const int grid = slots * ctas * ksplit;
-    if (p_mn) return launch_beta<true, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
-    if (q_mn) return launch_beta<false, true>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
-    return launch_beta<false, false>(ctx, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    if (p_mn) return launch_beta<true, true>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    if (q_mn) return launch_beta<false, true>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    return launch_beta<false, false>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+}
+
+// Up to three products in one launch (dense operands).
+//   FWD_NN   outs[i][M, Ns[i]]  = xs[0][M, K] * ys[i][K, Ns[i]]              (one input, several weights)
+//   WGRAD_TN outs[i][K, Ns[i]] (+)= xs[0][M, K]^T * ys[i][M, Ns[i]]          (one input, several output gradients)
+//   DGRAD_NT outs[0][M, K]     (+)= sum_i xs[i][M, Ns[i]] * ys[i][K, Ns[i]]^T (one accumulator over all of them:
+//                                   the sum is formed in fp32 and rounded once)
+// The first two concatenate the products along the output columns (each column tile belongs to one product), the
+// third along the contraction.  Shapes or pointers that the tensor-core kernel cannot take this way run as `count`
+// single products instead (the input gradient then accumulates through beta = 1, one rounding per product).
+int gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, void* const* outs, const void* const* xs,
+                      const void* const* ys, int M, const int* Ns, int K, int overlap_prev = 0, int sm_limit = 0) {
+    if (!ctx || !outs || !xs || !ys || !Ns || count < 1 || count > 3 || M <= 0 || K <= 0 || which < 0 || which > 2)
+        return B200_E_BADARG;
+    if (!on_context_device(ctx)) return B200_E_BADARG;
+    const bool k_concat = which == B200_GEMM_DGRAD_NT;
+    long long n_total = 0;
+    int n_align = 0;
+    bool fast = count > 1 && (K % 8) == 0 && (which != B200_GEMM_WGRAD_TN || (K % 64) == 0);
+    uintptr_t bits = 0;
+    for (int i = 0; i < count; ++i) {
+        if (Ns[i] <= 0 || !ys[i] || !(k_concat ? xs[i] : xs[0]) || !(k_concat ? outs[0] : outs[i])) return B200_E_BADARG;
+        n_total += Ns[i];
+        if ((Ns[i] % 64) != 0) fast = false;
+        int a = n_align, b = Ns[i];
+        while (b) { const int t = a % b; a = b; b = t; }
+        n_align = a;   // gcd
+        bits |= reinterpret_cast<uintptr_t>(ys[i]) | reinterpret_cast<uintptr_t>(k_concat ? xs[i] : xs[0]) |
+                reinterpret_cast<uintptr_t>(k_concat ? outs[0] : outs[i]);
+    }
+    if ((bits & 15) != 0 || n_total > 0x7FFFFFFF) fast = false;
+    if (!fast) {
+        for (int i = 0; i < count; ++i) {
+            const int rc = k_concat ? gemm_bf16(ctx, which, (beta1 || i > 0) ? 1 : 0, outs[0], xs[i], ys[i], M, Ns[i], K, 0, sm_limit)
+                                    : gemm_bf16(ctx, which, beta1, outs[i], xs[0], ys[i], M, Ns[i], K, (overlap_prev && i == 0) ? 1 : 0,
+                                                sm_limit);
+            if (rc) return rc;
+        }
+        return B200_OK;
+    }
+    int Mo, No, Kc;
+    bool p_mn, q_mn;
+    const int Nt = static_cast<int>(n_total);
+    if (which == B200_GEMM_FWD_NN) { Mo = M; No = Nt; Kc = K; p_mn = false; q_mn = true; }
+    else if (which == B200_GEMM_DGRAD_NT) { Mo = M; No = K; Kc = Nt; p_mn = false; q_mn = false; }
+    else { Mo = K; No = Nt; Kc = M; p_mn = true; q_mn = true; }
+    const int sm_count = (sm_limit > 0 && sm_limit < ctx->sm_count) ? sm_limit : ctx->sm_count;
+    b200_linear_plan_t plan;
+    memset(&plan, 0, sizeof(plan));
+    plan_dims(Mo, No, Kc, sm_count, k_concat ? 0 : n_align, &plan);
+    if (plan.bn == 0) return B200_E_BADARG;
+    GemmParams gp;
+    int bn, ctas, grid;
+    // a forced tile shape (tests, tuning) is taken when no tile of that width would straddle two products
+    const bool honour_force = ctx->force_bn > 0 && (k_concat || (n_align % ctx->force_bn) == 0);
+    int rc = schedule_launch(ctx, plan, Mo, No, Kc, sm_count, overlap_prev, honour_force, gp, bn, ctas, grid);
+    if (rc) return rc;
+    gp.out = outs[0];
+    gp.p_3d = p_mn ? 1 : 0;   // Mo % 64 == 0 and every Ns[i] % 64 == 0 were checked above
+    gp.q_3d = q_mn ? 1 : 0;
+    int acc = 0;
+    for (int i = 0; i + 1 < count; ++i) {
+        acc += Ns[i];
+        if (k_concat) gp.grp_k[i] = acc / BK;
+        else gp.grp_n[i] = acc / bn;
+    }
+    const bool need32 = gp.ksplit > 1 || gp.sk_peer;
+    CUtensorMap tmP[3], tmQ[3], tmD[3], tmD32[3];
+    for (int i = 0; i < count; ++i) {
+        const int Ni = Ns[i];
+        // P: shared by the column-concatenated products (only product 0's map is read), one per range of the contraction
+        if (k_concat || i == 0) {
+            const void* P = k_concat ? xs[i] : xs[0];
+            if (p_mn) rc = get_panel_map(ctx, P, Mo, Kc, BM / 64, &tmP[i]);
+            else rc = get_tensor_map(ctx, P, k_concat ? Ni : Kc, Mo, BK, BM, &tmP[i]);
+            if (rc) return rc;
+        } else {
+            tmP[i] = tmP[0];
+        }
+        if (q_mn) rc = get_panel_map(ctx, ys[i], Ni, Kc, bn / ctas / 64, &tmQ[i]);
+        else rc = get_tensor_map(ctx, ys[i], Ni, No, BK, bn / ctas, &tmQ[i]);   // K-concatenated: [K][Ni], contraction contiguous
+        if (rc) return rc;
+        if (!k_concat || i == 0) {
+            void* D = k_concat ? outs[0] : outs[i];
+            const int cols = k_concat ? No : Ni;
+            rc = get_tensor_map(ctx, D, cols, Mo, 64, 32, &tmD[i]);
+            if (rc) return rc;
+            tmD32[i] = tmD[i];
+            if (need32) {
+                rc = get_tensor_map(ctx, D, cols, Mo, 32, 32, &tmD32[i]);
+                if (rc) return rc;
+            }
+        } else {
+            tmD[i] = tmD[0];
+            tmD32[i] = tmD32[0];
+        }
+    }
+    GemmGroupMaps gx = {};
+    for (int i = 1; i < count; ++i) {
+        gx.p[i - 1] = tmP[i];
+        gx.q[i - 1] = tmQ[i];
+        gx.d[i - 1] = tmD[i];
+        gx.d32[i - 1] = tmD32[i];
+    }
+    if (p_mn) return launch_beta<true, true>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
+    if (q_mn) return launch_beta<false, true>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
+    return launch_beta<false, false>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
 }
 
 template <typename T, bool P_MN, bool Q_MN>
@@ -964,6 +1103,34 @@ extern "C" int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int bet
     if (ld_out < 0 || ld_x < 0 || ld_y < 0) return B200_E_BADARG;
     return gemm_bf16(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K, 0, 0, ld_out, ld_x, ld_y);
 }
+extern "C" int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, void* const* outs,
+                                             const void* const* xs, const void* const* ys, int M, const int* Ns, int K) {
+    return gemm_bf16_grouped(ctx, which, beta1, count, outs, xs, ys, M, Ns, K);
+}
+extern "C" int b200_linear_backward_bf16_grouped(b200_linear_ctx* ctx, int count, void* dA, int beta1_dA, void* const* dBs,
+                                                 const void* const* dCs, const void* A, const void* const* Bs, int M,
+                                                 const int* Ns, int K) {
+    if (!ctx || (!dA && !dBs) || !dCs || !Ns || count < 1 || count > 3 || M <= 0 || K <= 0) return B200_E_BADARG;
+    long long n_total = 0;
+    for (int i = 0; i < count; ++i) n_total += Ns[i] > 0 ? Ns[i] : 0;
+    if (n_total <= 0 || n_total > 0x7FFFFFFF) return B200_E_BADARG;
+    // as in b200_linear_backward_bf16: the two launches side by side on complementary shares of the SMs
+    int sm_dgrad = 0, sm_wgrad = 0;
+    if (dA && dBs && ctx->use_pdl && ctx->overlap_backward && ctx->partition_backward && ctx->force_bn <= 0 && ctx->sm_count >= 16)
+        split_sms_for_backward(ctx, M, static_cast<int>(n_total), K, &sm_dgrad, &sm_wgrad);
+    if (dA) {
+        if (!Bs) return B200_E_BADARG;
+        void* const outs[3] = {dA, dA, dA};
+        const int rc = gemm_bf16_grouped(ctx, B200_GEMM_DGRAD_NT, beta1_dA, count, outs, dCs, Bs, M, Ns, K, 0, sm_dgrad);
+        if (rc) return rc;
+    }
+    if (dBs) {
+        if (!A) return B200_E_BADARG;
+        const void* const xs[3] = {A, A, A};
+        return gemm_bf16_grouped(ctx, B200_GEMM_WGRAD_TN, 1, count, dBs, xs, dCs, M, Ns, K, dA ? 1 : 0, sm_wgrad);
+    }
+    return B200_OK;
+}
 extern "C" int b200_linear_gemm_f32(b200_linear_ctx* ctx, int which, int beta1, float* out, const float* x,
                                     const float* y, int M, int N, int K) {
     return gemm_f32(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K);
@@ -1100,6 +1267,7 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     gp.out = dB;
     gp.ws = nd.scratch->partials;
     gp.sk_counters = nd.scratch->counters;
+    gp.grp_n[0] = gp.grp_n[1] = gp.grp_k[0] = gp.grp_k[1] = GRP_NONE;
     gp.status = &nd.scratch->status;
 
     auto encode = [&](CUtensorMap* tm, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
@@ -1146,7 +1314,7 @@ extern "C" int b200_linear_wgrad_bf16_noalloc(void* dB, const void* A, const voi
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD, gp) != cudaSuccess) return B200_E_CUDA;
+    if (cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD, g_no_group, gp) != cudaSuccess) return B200_E_CUDA;
     return B200_OK;
 }
 

@@ -20,6 +20,7 @@
 #include <cstdint>
 
 #include "gemm_simt.cuh"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -92,6 +93,7 @@ template <typename T>
 __global__ void __launch_bounds__(AT_THREADS)
 attn_fwd_simt(T* __restrict__ context, float* __restrict__ lse, const T* __restrict__ q, const T* __restrict__ k,
               const T* __restrict__ v, const AttnParams p) {
+    griddep_sync();
     extern __shared__ __align__(16) float at_smem[];
     float* Qt = at_smem;                    // [d][r]
     float* Kt = Qt + AT_TILE_FLOATS;        // [d][c]
@@ -157,6 +159,7 @@ attn_fwd_simt(T* __restrict__ context, float* __restrict__ lse, const T* __restr
 template <typename T>
 __global__ void __launch_bounds__(256)
 attn_delta(float* __restrict__ delta, const T* __restrict__ dcontext, const T* __restrict__ context, const AttnParams p) {
+    griddep_sync();
     const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const long long total = static_cast<long long>(p.B) * p.T * p.n_head;
@@ -202,6 +205,7 @@ __global__ void __launch_bounds__(AT_THREADS)
 attn_bwd_dq_simt(T* __restrict__ dq, const T* __restrict__ dcontext, const T* __restrict__ q, const T* __restrict__ k,
                  const T* __restrict__ v, const float* __restrict__ lse, const float* __restrict__ delta,
                  const AttnParams p) {
+    griddep_sync();
     extern __shared__ __align__(16) float at_smem[];
     float* Qt = at_smem;                     // [d][r]
     float* dOt = Qt + AT_TILE_FLOATS;        // [d][r]
@@ -254,6 +258,7 @@ __global__ void __launch_bounds__(AT_THREADS)
 attn_bwd_dkv_simt(T* __restrict__ dk, T* __restrict__ dv, const T* __restrict__ dcontext, const T* __restrict__ q,
                   const T* __restrict__ k, const T* __restrict__ v, const float* __restrict__ lse,
                   const float* __restrict__ delta, const AttnParams p) {
+    griddep_sync();
     extern __shared__ __align__(16) float at_smem[];
     float* Kt = at_smem;                     // [d][c]
     float* Vt = Kt + AT_TILE_FLOATS;         // [d][c]

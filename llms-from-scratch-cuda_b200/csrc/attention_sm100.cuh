@@ -80,7 +80,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // longest rows first
+    // grid = (heads, batch, query tiles): blocks are dispatched x-fastest, so every (head, batch) pair's longest rows
+    // (the last query tile: most key tiles under the causal mask) start before anybody's short ones
+    const int qt = gridDim.z - 1 - blockIdx.z, h = blockIdx.x, b = blockIdx.y;
     const int kvh = h / (p.n_head / p.n_kv_head);
     const int n_kv = qt + 1;                      // causal: key tiles 0 .. qt
 
@@ -118,6 +120,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_sync();   // everything above touches no global memory and may overlap the previous kernel's tail
     const uint32_t tmem_base = ctrl->tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_PV = tmem_base + 256;   // S[b] at +128 b, PV[b] at +64 b
 
@@ -396,7 +399,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int qt = gridDim.z - 1 - blockIdx.z, h = blockIdx.x, b = blockIdx.y;   // longest first, as in the forward kernel
     const int kvh = h / (p.n_head / p.n_kv_head);
     const int n_kv = qt + 1;
 
@@ -432,6 +435,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_sync();   // everything above touches no global memory and may overlap the previous kernel's tail
     const uint32_t tmem_base = ctrl->tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 256, tmem_dQ = tmem_base + 384;   // S[b] at +128 b
 
@@ -657,7 +661,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
-    const int kt = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int kt = blockIdx.z, kvh = blockIdx.x, b = blockIdx.y;   // key tile 0 meets every query tile: longest first
     const int ratio = p.n_head / p.n_kv_head;
     const int q_tiles = (p.T + FA_BQ - 1) / FA_BQ;
     const int n_q = q_tiles - kt;          // query tiles kt .. q_tiles-1 see this key tile
@@ -696,6 +700,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_sync();   // everything above touches no global memory and may overlap the previous kernel's tail
     const uint32_t tmem_base = ctrl->tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 256, tmem_dV = tmem_base + 384, tmem_dK = tmem_base + 448;
 

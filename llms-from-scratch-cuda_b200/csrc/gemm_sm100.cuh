@@ -42,6 +42,13 @@ constexpr int EPI_WARPS = 8;     // warps 4..11
 constexpr int SMEM_BUDGET = 227 * 1024;
 constexpr int EPI_BUF_BYTES = 32 * 128;  // one staging buffer: 32 rows x 64 bf16, 128-byte swizzled
 
+constexpr int GRP_NONE = 0x7FFFFFFF;
+
+// Tensor maps of products 1 and 2 of a grouped launch (product 0 uses the kernel's first four maps).
+struct alignas(64) GemmGroupMaps {
+    CUtensorMap p[2], q[2], d[2], d32[2];
+};
+
 struct GemmParams {
     int Mo, No, Kc;          // output rows, output cols, contraction length
     int m_tiles, n_tiles;    // ceil(Mo/(BM*CTAS)), ceil(No/BN)
@@ -59,6 +66,12 @@ struct GemmParams {
     int ksplit;              // > 1: a cluster of CTAS*ksplit CTAs shares each tile, every member takes one
                              // range of the contraction and the sum is formed through distributed smem
     int p_3d, q_3d;          // MN-major operand described by a 3-D map: one copy per stage
+    // Grouped launch (up to three products in one): column tiles [0, grp_n[0]) belong to product 0,
+    // [grp_n[0], grp_n[1]) to product 1, the rest to product 2, each with its own Q and D maps and its own column
+    // origin ("N-concatenated": Y_i = X * W_i with X shared); contraction blocks are divided the same way by grp_k
+    // ("K-concatenated": dX = sum_i dY_i * W_i^T, one accumulator), each range with its own P and Q maps.
+    // GRP_NONE in all four for a single product.
+    int grp_n[2], grp_k[2];
     void* out;               // bf16 [Mo,No]
     float* ws;               // split partials: sk_items * CTAS blocks of BM x BN fp32
     int* sk_counters;        // one arrival counter per (split tile, CTA of the pair); zero between launches
@@ -139,6 +152,13 @@ __device__ __forceinline__ bool get_work(const GemmParams& p, int slot, int nslo
     w.m_blk = p.m_fastest ? fast : slow;
     w.n_blk = p.m_fastest ? slow : fast;
     return true;
+}
+
+// Which product of a grouped launch a column tile / contraction block belongs to, and where that product starts.
+__device__ __forceinline__ int group_of(int bound0, int bound1, int i, int& base) {
+    const int g = (i >= bound0) + (i >= bound1);
+    base = g == 0 ? 0 : (g == 1 ? bound0 : bound1);   // no indexing by g: kernel parameters are not addressable
+    return g;
 }
 
 // Cluster split: member `krank` of the cluster keeps only its own range of the contraction.
@@ -597,7 +617,7 @@ template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD32,
-                const GemmParams p) {
+                const __grid_constant__ GemmGroupMaps gx, const GemmParams p) {
     using Cfg = TileCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr bool PAIR = CTAS == 2;
@@ -659,6 +679,11 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     if (clustered) cluster_wait_acquire();
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
+    // grouped launch: the maps of product g (g = 0: the kernel's own)
+    auto map_p = [&](int g) { return g == 0 ? &tmP : (g == 1 ? &gx.p[0] : &gx.p[1]); };
+    auto map_q = [&](int g) { return g == 0 ? &tmQ : (g == 1 ? &gx.q[0] : &gx.q[1]); };
+    auto map_d = [&](int g) { return g == 0 ? &tmD : (g == 1 ? &gx.d[0] : &gx.d[1]); };
+    auto map_d32 = [&](int g) { return g == 0 ? &tmD32 : (g == 1 ? &gx.d32[0] : &gx.d32[1]); };
     // the first work item does not depend on memory: know it before the dependency wait
     WorkItem w_first;
     const bool have_first = get_work(p, slot, nslots, 0, w_first);
@@ -685,18 +710,22 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
         if (elect_one()) {
             WorkItem w = w_first;
             narrow_to_krank(p, krank, w);
+            int n_base;
+            const int gn = group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
             const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
-            const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
+            const int n0 = (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
             const int kb_end = min(w.kb1, w.kb0 + STAGES);
             {
                 const bool is_q = warp == 3;
-                const CUtensorMap* tm = is_q ? &tmQ : &tmP;
                 const bool mn = is_q ? Q_MN : P_MN;
                 const bool as3d = is_q ? (p.q_3d != 0) : (p.p_3d != 0);
                 const int panels = is_q ? Cfg::B_ROWS / 64 : BM / 64;
                 const int r0 = is_q ? n0 : m0;
                 for (int kb = w.kb0; kb < kb_end; ++kb) {
-                    const int c0 = kb * BK;
+                    int k_base;
+                    const int gk = group_of(p.grp_k[0], p.grp_k[1], kb, k_base);
+                    const CUtensorMap* tm = is_q ? map_q(gn + gk) : map_p(gk);
+                    const int c0 = (kb - k_base) * BK;
                     if (!mn) tma_prefetch_l2_2d(tm, c0, r0);
                     else if (as3d) tma_prefetch_l2_3d(tm, 0, c0, r0 >> 6);
                     else
@@ -721,8 +750,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             uint32_t issued = 0;  // number of stage fills issued so far
             bool ok = true;
             WorkItem w;
-            auto issue = [&](bool is_q, uint32_t dst, uint32_t bar, int r0, int c0) {
-                const CUtensorMap* tm = is_q ? &tmQ : &tmP;
+            auto issue = [&](bool is_q, const CUtensorMap* tm, uint32_t dst, uint32_t bar, int r0, int c0) {
                 const bool mn = is_q ? Q_MN : P_MN;
                 const bool as3d = is_q ? (p.q_3d != 0) : (p.p_3d != 0);
                 const int panels = is_q ? Cfg::B_ROWS / 64 : BM / 64;
@@ -745,8 +773,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             const bool issuer = elect_one();  // one lane, the same for the whole loop
             for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
+                int n_base;
+                const int gn = group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
-                const int n0 = w.n_blk * BN + static_cast<int>(rank) * Cfg::B_ROWS;
+                const int n0 = (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
                         ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
@@ -760,12 +790,14 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     const uint32_t local_bar = smem_u32(&ctrl->full[stage]);
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
-                    const int c0 = kb * BK;
+                    int k_base;
+                    const int gk = group_of(p.grp_k[0], p.grp_k[1], kb, k_base);
+                    const int c0 = (kb - k_base) * BK;
                     if (issuer) {
                         if (rank == 0)
                             mbar_arrive_expect_tx(local_bar, CTAS * (do_p ? Cfg::A_BYTES : Cfg::B_BYTES));
-                        if (do_p) issue(false, sP, bar, m0, c0);
-                        if (do_q) issue(true, sP + Cfg::A_BYTES, bar, n0, c0);
+                        if (do_p) issue(false, map_p(gk), sP, bar, m0, c0);
+                        if (do_q) issue(true, map_q(gn + gk), sP + Cfg::A_BYTES, bar, n0, c0);
                     }
                     ++issued;
                     stage = next_stage;
@@ -867,6 +899,11 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             const int row0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM + q * 32;
+            int n_base;
+            const int gn = group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
+            const int col_tile = (w.n_blk - n_base) * BN;   // first column of the tile inside its own product
+            const CUtensorMap* tmDg = map_d(gn);
+            const CUtensorMap* tmD32g = map_d32(gn);
             const uint32_t taddr = tmem_base + acc * Cfg::ACC_STRIDE + (static_cast<uint32_t>(q * 32) << 16);
             uint8_t* my_buf = epi_bufs + (warp - 4) * (Cfg::EPI_BUFS * EPI_BUF_BYTES);
             auto release_acc = [&]() {
@@ -878,14 +915,14 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 }
             };
             if (p.ksplit > 1) {
-                ok = epilogue_cluster_split<BN, BETA1, CTAS>(p, ctrl, tiles, &tmD32, my_buf, taddr, q, hsel, lane, warp,
-                                                             row0, w.n_blk * BN, krank, static_cast<int>(rank), old_bar,
+                ok = epilogue_cluster_split<BN, BETA1, CTAS>(p, ctrl, tiles, tmD32g, my_buf, taddr, q, hsel, lane, warp,
+                                                             row0, col_tile, krank, static_cast<int>(rank), old_bar,
                                                              old_phase, abort_flag);
                 release_acc();
                 if (!ok) break;
             } else if (w.sk_item < 0) {
-                ok = epilogue_store_bf16<BN, BETA1, false, Cfg::EPI_BUFS>(p, &tmD, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
-                                                               w.n_blk * BN, old_bar, old_phase, abort_flag);
+                ok = epilogue_store_bf16<BN, BETA1, false, Cfg::EPI_BUFS>(p, tmDg, my_buf, taddr, nullptr, 0, 0, q, hsel, row0, lane,
+                                                               col_tile, old_bar, old_phase, abort_flag);
                 release_acc();
                 if (!ok) break;
             } else if (p.sk_peer) {
@@ -893,8 +930,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 const int maxg = (G + p.sk_splits - 1) / p.sk_splits;
                 float* region = p.ws + (static_cast<size_t>(w.sk_tile) * CTAS + rank) * p.sk_splits * (p.sk_splits - 1) *
                                            maxg * (8 * BM * 4);
-                ok = epilogue_peer_split<BN, BETA1>(p, ctrl, region, p.sk_counters + w.sk_tile * CTAS + rank, &tmD32,
-                                                    my_buf, taddr, q, hsel, lane, warp, row0, w.n_blk * BN, w.sk_split,
+                ok = epilogue_peer_split<BN, BETA1>(p, ctrl, region, p.sk_counters + w.sk_tile * CTAS + rank, tmD32g,
+                                                    my_buf, taddr, q, hsel, lane, warp, row0, col_tile, w.sk_split,
                                                     old_bar, old_phase, sk_phase, abort_flag);
                 sk_phase ^= 1;
                 release_acc();
@@ -928,9 +965,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     __threadfence();
                     const float* first = p.ws + (static_cast<size_t>(w.sk_tile) * p.sk_splits * CTAS + rank) *
                                                     Cfg::PARTIAL_FLOATS;
-                    ok = epilogue_store_bf16<BN, BETA1, true, Cfg::EPI_BUFS>(p, &tmD, my_buf, 0, first,
+                    ok = epilogue_store_bf16<BN, BETA1, true, Cfg::EPI_BUFS>(p, tmDg, my_buf, 0, first,
                                                               static_cast<size_t>(CTAS) * Cfg::PARTIAL_FLOATS, p.sk_splits,
-                                                              q, hsel, row0, lane, w.n_blk * BN, old_bar, old_phase,
+                                                              q, hsel, row0, lane, col_tile, old_bar, old_phase,
                                                               abort_flag);
                     if (!ok) break;
                 }

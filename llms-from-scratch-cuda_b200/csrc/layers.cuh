@@ -8,6 +8,7 @@
 #include <cstdint>
 
 #include "gemm_simt.cuh"
+#include "ptx.cuh"
 
 namespace b200 {
 
@@ -25,6 +26,7 @@ struct RopeFreq {
 // far more expensive than the two loads and stores of the rotation itself).
 __global__ void __launch_bounds__(256)
 rope_table_kernel(float2* __restrict__ table, int Tlen, int half, const RopeFreq freqs) {
+    griddep_sync();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= Tlen * half) return;
     const int t = idx / half, i = idx - t * half;
@@ -37,6 +39,7 @@ template <typename T, int DIR>
 __global__ void __launch_bounds__(256)
 rope_kernel(T* __restrict__ q, T* __restrict__ k, long long total, int Tlen, int n_head, int n_kv_head, int head_dim,
             const float2* __restrict__ table) {
+    griddep_sync();
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int total_heads = n_head + n_kv_head, half = head_dim / 2;
@@ -63,6 +66,7 @@ __device__ __forceinline__ float sigmoid_f(float g) { return 1.0f / (1.0f + __ex
 template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_gate_kernel(T* __restrict__ hidden, const T* __restrict__ gate, const T* __restrict__ up, long long n) {
+    griddep_sync();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float g = to_f32<T>(gate[i]);
@@ -74,6 +78,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_gate_backward_kernel(T* __restrict__ dgate, T* __restrict__ dup, const T* __restrict__ dhidden,
                             const T* __restrict__ gate, const T* __restrict__ up, long long n) {
+    griddep_sync();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const float g = to_f32<T>(gate[i]), u = to_f32<T>(up[i]), dh = to_f32<T>(dhidden[i]);
@@ -86,6 +91,7 @@ swiglu_gate_backward_kernel(T* __restrict__ dgate, T* __restrict__ dup, const T*
 __global__ void __launch_bounds__(256)
 swiglu_gate_kernel_bf16x8(uint4* __restrict__ hidden, const uint4* __restrict__ gate, const uint4* __restrict__ up,
                           long long n8) {
+    griddep_sync();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
         const uint4 gv = gate[i], uv = up[i];
@@ -104,6 +110,7 @@ swiglu_gate_kernel_bf16x8(uint4* __restrict__ hidden, const uint4* __restrict__ 
 __global__ void __launch_bounds__(256)
 swiglu_gate_backward_kernel_bf16x8(uint4* __restrict__ dgate, uint4* __restrict__ dup, const uint4* __restrict__ dhidden,
                                    const uint4* __restrict__ gate, const uint4* __restrict__ up, long long n8) {
+    griddep_sync();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
         const uint4 gv = gate[i], uv = up[i], dv = dhidden[i];
@@ -167,6 +174,7 @@ __device__ __forceinline__ float ce_block_reduce(float v, float* sh, bool is_max
 template <typename T>
 __global__ void __launch_bounds__(CE_ROW_THREADS)
 ce_row_forward(float* __restrict__ losses, T* probs, const int* __restrict__ targets, int rows, long long V) {
+    griddep_sync();
     __shared__ float sh[CE_ROW_THREADS / 32];
     constexpr int VEC = 16 / sizeof(T);  // elements per 16-byte access
     for (int r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -245,6 +253,7 @@ ce_row_forward(float* __restrict__ losses, T* probs, const int* __restrict__ tar
 template <typename T>
 __global__ void __launch_bounds__(256)
 ce_row_backward(T* dlogits, const T* probs, const int* __restrict__ targets, float scale, int rows, long long V) {
+    griddep_sync();
     const long long n = static_cast<long long>(rows) * V;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -257,6 +266,7 @@ ce_row_backward(T* dlogits, const T* probs, const int* __restrict__ targets, flo
 __global__ void __launch_bounds__(256)
 ce_row_backward_bf16x8(uint4* dlogits, const uint4* probs, const int* __restrict__ targets, float scale, int rows,
                        long long V8) {
+    griddep_sync();
     const long long n = static_cast<long long>(rows) * V8;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -288,6 +298,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_kernel(T* __restrict__ out, float* __restrict__ rrms, const T* __restrict__ inp, const T* __restrict__ weight,
                    float eps, int rows, int C) {
+    griddep_sync();
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -311,6 +322,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_dinp_kernel(T* __restrict__ dinp, const T* __restrict__ dout, const T* __restrict__ inp,
                         const T* __restrict__ weight, const float* __restrict__ rrms, int rows, int C) {
+    griddep_sync();
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -330,11 +342,12 @@ rmsnorm_bwd_dinp_kernel(T* __restrict__ dinp, const T* __restrict__ dout, const 
 
 // dweight_j += sum_rows dy_j x_j rrms: the reference adds row by row with one atomic per element (a compare-and-swap
 // loop on bf16, 8192 contenders per word).  Here: partial[chunk][j] = the sum over one chunk of rows (a thread per
-// column, coalesced over j), then one pass adds the chunks in a fixed order onto the stored gradient, rounding once.
+// column, coalesced over j), then rmsnorm_bwd_dw_reduce adds the chunks in a fixed order onto the stored gradient, rounding once.
 template <typename T>
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_dw_partial_kernel(float* __restrict__ partial, const T* __restrict__ dout, const T* __restrict__ inp,
                               const float* __restrict__ rrms, int rows, int C, int rows_per_chunk) {
+    griddep_sync();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= C) return;
     const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
@@ -342,15 +355,6 @@ rmsnorm_bwd_dw_partial_kernel(float* __restrict__ partial, const T* __restrict__
     for (int r = r0; r < r1; ++r)
         s += to_f32<T>(dout[static_cast<long long>(r) * C + j]) * to_f32<T>(inp[static_cast<long long>(r) * C + j]) * rrms[r];
     partial[static_cast<long long>(blockIdx.y) * C + j] = s;
-}
-template <typename T>
-__global__ void __launch_bounds__(256)
-rmsnorm_bwd_dw_final_kernel(T* __restrict__ dweight, const float* __restrict__ partial, int chunks, int C) {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= C) return;
-    float s = 0.f;
-    for (int c = 0; c < chunks; ++c) s += partial[static_cast<long long>(c) * C + j];
-    dweight[j] = from_f32<T>(to_f32<T>(dweight[j]) + s);
 }
 
 }  // namespace b200
@@ -378,6 +382,7 @@ __device__ __forceinline__ uint4 f32x4_add(const uint4& x, const uint4& y) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 residual_forward_vec(uint4* out, const uint4* a, const uint4* b, long long nvec) {
+    griddep_sync();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride)
         out[i] = sizeof(T) == 2 ? bf16x8_add(a[i], b[i]) : f32x4_add(a[i], b[i]);
@@ -385,6 +390,7 @@ residual_forward_vec(uint4* out, const uint4* a, const uint4* b, long long nvec)
 template <typename T>
 __global__ void __launch_bounds__(256)
 residual_backward_vec(uint4* da, uint4* db, const uint4* dout, long long nvec) {
+    griddep_sync();
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
         const uint4 d = dout[i];
@@ -395,12 +401,14 @@ residual_backward_vec(uint4* da, uint4* db, const uint4* dout, long long nvec) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 residual_forward_scalar(T* out, const T* a, const T* b, long long n0, long long n) {
+    griddep_sync();
     const long long i = n0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) out[i] = from_f32<T>(to_f32<T>(a[i]) + to_f32<T>(b[i]));
 }
 template <typename T>
 __global__ void __launch_bounds__(256)
 residual_backward_scalar(T* da, T* db, const T* dout, long long n0, long long n) {
+    griddep_sync();
     const long long i = n0 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) {
         const float d = to_f32<T>(dout[i]);
@@ -414,6 +422,7 @@ template <int DIR>
 __global__ void __launch_bounds__(256)
 rope_kernel_bf16x8(uint4* __restrict__ q, uint4* __restrict__ k, long long total_vec, int Tlen, int n_head, int n_kv_head,
                    int head_dim, const float2* __restrict__ table) {
+    griddep_sync();
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= total_vec) return;
     const int vec_per_head = head_dim / 8, total_heads = n_head + n_kv_head, half = head_dim / 2;
@@ -462,6 +471,7 @@ __device__ __forceinline__ uint4 bf16x8_pack(const float (&x)[8]) {
 __global__ void __launch_bounds__(256)
 rmsnorm_fwd_bf16x8(uint4* __restrict__ out, float* __restrict__ rrms, const uint4* __restrict__ inp,
                    const uint4* __restrict__ weight, float eps, int rows, int C) {
+    griddep_sync();
     const int lane = threadIdx.x & 31, nvec = C / 8;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -501,6 +511,7 @@ rmsnorm_fwd_bf16x8(uint4* __restrict__ out, float* __restrict__ rrms, const uint
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_dinp_bf16x8(uint4* __restrict__ dinp, const uint4* __restrict__ dout, const uint4* __restrict__ inp,
                         const uint4* __restrict__ weight, const float* __restrict__ rrms, int rows, int C) {
+    griddep_sync();
     const int lane = threadIdx.x & 31, nvec = C / 8;
     const int warps = (gridDim.x * blockDim.x) >> 5;
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
@@ -541,6 +552,232 @@ rmsnorm_bwd_dinp_bf16x8(uint4* __restrict__ dinp, const uint4* __restrict__ dout
             }
         }
     }
+}
+
+
+// dinp and this block's share of dweight in one pass over dout and inp (bf16, 16-byte accesses): every warp walks its
+// rows, keeps sum_rows dy_j x_j rrms for its own columns in registers, the block's eight warps add theirs up in shared
+// memory in warp order, and partial[block][j] goes to rmsnorm_bwd_dw_reduce (fixed order: run-to-run identical).
+template <int NV>   // 16-byte vectors per lane: C <= NV * 256
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_fused_bf16x8(uint4* __restrict__ dinp, float* __restrict__ partial, const uint4* __restrict__ dout,
+                         const uint4* __restrict__ inp, const uint4* __restrict__ weight, const float* __restrict__ rrms,
+                         int rows, int C) {
+    griddep_sync();
+    __shared__ float sh[NV * 256];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nvec = C / 8;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    float dw[NV][8];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dw[i][e] = 0.f;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const uint4* x4 = inp + static_cast<long long>(r) * nvec;
+        const uint4* d4 = dout + static_cast<long long>(r) * nvec;
+        uint4 xv[NV], dv[NV];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                xv[i] = x4[v];
+                dv[i] = d4[v];
+                float x[8], d[8], w[8];
+                bf16x8_unpack(xv[i], x);
+                bf16x8_unpack(dv[i], d);
+                bf16x8_unpack(__ldg(weight + v), w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s += d[e] * w[e] * x[e];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        const float inv = rrms[r];
+        const float kk = inv * inv * s / static_cast<float>(C);
+        uint4* o4 = dinp + static_cast<long long>(r) * nvec;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                float x[8], d[8], w[8];
+                bf16x8_unpack(xv[i], x);
+                bf16x8_unpack(dv[i], d);
+                bf16x8_unpack(__ldg(weight + v), w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    dw[i][e] = fmaf(d[e] * x[e], inv, dw[i][e]);
+                    x[e] = inv * (d[e] * w[e] - x[e] * kk);
+                }
+                o4[v] = bf16x8_pack(x);
+            }
+        }
+    }
+    for (int turn = 0; turn < 8; ++turn) {
+        if (wid == turn) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int v = lane + 32 * i;
+                if (v < nvec) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sh[v * 8 + e] = (turn == 0 ? 0.f : sh[v * 8 + e]) + dw[i][e];
+                }
+            }
+        }
+        __syncthreads();
+    }
+    for (int j = threadIdx.x; j < C; j += 256) partial[static_cast<long long>(blockIdx.x) * C + j] = sh[j];
+}
+// dweight_j += sum over `chunks` partial rows, in the order 0, 8, 16, ... | 1, 9, ... per warp and then warp 0..7: a block
+// per 32 columns, lane = column.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dw_reduce(T* __restrict__ dweight, const float* __restrict__ partial, int chunks, int C) {
+    griddep_sync();
+    __shared__ float sh[8][32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int j = blockIdx.x * 32 + lane;
+    float s = 0.f;
+    if (j < C)
+        for (int c = wid; c < chunks; c += 8) s += partial[static_cast<long long>(c) * C + j];
+    sh[wid][lane] = s;
+    __syncthreads();
+    if (wid == 0 && j < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += sh[w][lane];
+        dweight[j] = from_f32<T>(to_f32<T>(dweight[j]) + t);
+    }
+}
+
+// delta[b, h, t] = sum_d dcontext[t, h, d] * context[t, h, d] for head dimension 64, bf16, 16 bytes per lane: a warp
+// covers four heads of one token per pass (eight lanes per head).
+__global__ void __launch_bounds__(256)
+attn_delta_bf16x8(float* __restrict__ delta, const uint4* __restrict__ dcontext, const uint4* __restrict__ context, int B,
+                  int Tlen, int n_head) {
+    griddep_sync();
+    const int lane = threadIdx.x & 31;
+    const long long rows = static_cast<long long>(B) * Tlen;
+    const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+    const int nvec = n_head * 8;   // 16-byte vectors per token
+    for (long long bt = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; bt < rows; bt += warps) {
+        const int b = static_cast<int>(bt / Tlen), t = static_cast<int>(bt % Tlen);
+        for (int v0 = 0; v0 < nvec; v0 += 32) {
+            const int v = v0 + lane;
+            float s = 0.f;
+            if (v < nvec) {
+                float x[8], y[8];
+                bf16x8_unpack(dcontext[bt * nvec + v], x);
+                bf16x8_unpack(context[bt * nvec + v], y);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s = fmaf(x[e], y[e], s);
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            const int h = v >> 3;
+            if ((lane & 7) == 0 && v < nvec) delta[(static_cast<long long>(b) * n_head + h) * Tlen + t] = s;
+        }
+    }
+}
+
+}  // namespace b200
+
+namespace b200 {
+
+// ------------------------------------------------------------------------------ optimizer (cuda/adamw.cu)
+// AdamW exactly as the reference writes it (adamw.cu:12-40 fp32, :63-88 mixed precision), one element per thread;
+// it is already at the HBM roof.  The gradient norm (adamw.cu:101-191) is where the reference loses time: one
+// atomicAdd per 256-element block onto a single word.  Here: per-CTA partial sums, then one CTA adds them in a fixed
+// order.  The bf16 variant zeroes non-finite and > 65000 entries in place, as the reference does.
+__global__ void __launch_bounds__(256)
+adamw_kernel_f32(float* params, const float* grads, float* m, float* v, float lr, float beta1, float beta2, float eps,
+                 float weight_decay, float bc1, float bc2, long long n) {
+    griddep_sync();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = grads[i], p = params[i];
+    const float mi = beta1 * m[i] + (1.0f - beta1) * g;
+    const float vi = beta2 * v[i] + (1.0f - beta2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    params[i] = p - lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + weight_decay * p);
+}
+__global__ void __launch_bounds__(256)
+adamw_kernel_bf16(__nv_bfloat16* params, float* master, const __nv_bfloat16* grads, float* m, float* v, float lr, float beta1,
+                  float beta2, float eps, float weight_decay, float grad_scale, float bc1, float bc2, long long n) {
+    griddep_sync();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = __bfloat162float(grads[i]) * grad_scale;
+    float p = master[i];
+    const float mi = beta1 * m[i] + (1.0f - beta1) * g;
+    const float vi = beta2 * v[i] + (1.0f - beta2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    p -= lr * ((mi / bc1) / (sqrtf(vi / bc2) + eps) + weight_decay * p);
+    master[i] = p;
+    params[i] = __float2bfloat16(p);
+}
+__global__ void __launch_bounds__(256) scale_kernel_f32(float* data, float scale, long long n) {
+    griddep_sync();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) data[i] *= scale;
+}
+__global__ void __launch_bounds__(256) f32_to_bf16_kernel(const float* src, __nv_bfloat16* dst, long long n) {
+    griddep_sync();
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = __float2bfloat16(src[i]);
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float* sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    v = threadIdx.x < 8 ? sh[threadIdx.x] : 0.f;
+    if (threadIdx.x < 32) {
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;  // valid in thread 0
+}
+// partial[blockIdx.x] = sum over this CTA's grid-stride share of (g * scale)^2
+__global__ void __launch_bounds__(256)
+sumsq_partial_f32(float* __restrict__ partial, const float* __restrict__ g, float scale, long long n) {
+    griddep_sync();
+    __shared__ float sh[8];
+    float s = 0.f;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float x = g[i] * scale;
+        s = fmaf(x, x, s);
+    }
+    s = block_sum_256(s, sh);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void __launch_bounds__(256)
+sumsq_sanitize_partial_bf16(float* __restrict__ partial, __nv_bfloat16* g, float scale, long long n) {
+    griddep_sync();
+    __shared__ float sh[8];
+    float s = 0.f;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float x = __bfloat162float(g[i]) * scale;
+        if (x != x || fabsf(x) > 65000.0f) g[i] = __float2bfloat16(0.0f);   // adamw.cu:133-135
+        else s = fmaf(x, x, s);
+    }
+    s = block_sum_256(s, sh);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+// out[0] = sum of the n partial sums, in order
+__global__ void __launch_bounds__(256) sum_partials(float* __restrict__ out, const float* __restrict__ partial, int n) {
+    griddep_sync();
+    __shared__ float sh[8];
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) s += partial[i];
+    s = block_sum_256(s, sh);
+    if (threadIdx.x == 0) out[0] = s;
 }
 
 }  // namespace b200

@@ -2,7 +2,7 @@
 // softmax(QK^T)V core), the SwiGLU feed-forward block and the softmax cross-entropy.  Each function keeps the
 // signature -- and therefore the mangled name -- that the reference declares in cuda/kernels.cuh, so that
 // the reference's host code links against this library with its own cuda/attention.cu,
-// cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu, cuda/rmsnorm.cu and cuda/residual.cu left out of the build:
+// cuda/flash_attention.cu, cuda/swiglu.cu, cuda/crossentropy.cu, cuda/rmsnorm.cu, cuda/residual.cu and cuda/adamw.cu left out of the build:
 //
 //   flash_attention_forward / _backward  kernels.cuh:316-341 (fp32), :420-437 (bf16); bodies empty upstream
 //                                        (flash_attention.cu:12-17, 51-57)
@@ -12,6 +12,8 @@
 //                                        kernels.cuh:260-277 (fp32), :402-404 (bf16); crossentropy.cu:66-92, 134-151
 //   rmsnorm_forward / rmsnorm_backward   kernels.cuh:87-105 (fp32), :359-362 (bf16); rmsnorm.cu:75-105, 168-178
 //   residual_forward / residual_backward kernels.cuh:280-289 (fp32), :407-408 (bf16); residual.cu:32-49, 68-78
+//   adamw_update, scale_grads, fp32_to_bf16, compute_grad_norm_bf16
+//                                        kernels.cuh:299-309, 411-418; adamw.cu:42-58, 90-99, 153-191
 //
 // Differences from the reference, on purpose: no [B, n_head, T, T] matrix is ever formed (the `att` argument
 // of attention_forward keeps the row log-sum-exps and the attention context instead, which is what the
@@ -41,7 +43,7 @@ using namespace b200;
 namespace {
 
 constexpr int kMaxDev = 64;
-enum Slot { S_CONTEXT, S_DCONTEXT, S_DQ, S_DK, S_DV, S_DELTA, S_LSE, S_HIDDEN, S_DHIDDEN, S_DGATE, S_DUP, S_RMS_PARTIAL, S_ROPE_TABLE, S_COUNT };
+enum Slot { S_CONTEXT, S_DCONTEXT, S_DQ, S_DK, S_DV, S_DELTA, S_LSE, S_HIDDEN, S_DHIDDEN, S_DGATE, S_DUP, S_RMS_PARTIAL, S_ROPE_TABLE, S_NORM_PARTIAL, S_COUNT };
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -112,6 +114,31 @@ bool token_map(CUtensorMap* tm, const void* ptr, int B, int Tlen, int width, int
                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Every kernel of this file begins with griddep_sync(): launched with programmatic stream serialization, its blocks
+// may be scheduled while the previous kernel's last blocks retire, and wait there until that kernel has completed.
+// B200_LINEAR_PDL=0 launches them fully serialized.
+bool layers_pdl() {
+    static const bool on = [] {
+        const char* e = getenv("B200_LINEAR_PDL");
+        return !(e && atoi(e) == 0);
+    }();
+    return on;
+}
+template <typename... Exp, typename... Act>
+void launch_pdl(void (*kern)(Exp...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Act&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = layers_pdl() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<Exp>(args)...);   // a failure is read back by the caller (cudaGetLastError)
+}
+
 bool use_tensor_cores(const void* a, const void* b, const void* c, const void* d) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -132,8 +159,8 @@ int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q,
     p.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(FA_HD));
     p.lse = lse;
     p.status = b200_linear_status_word(ctx);
-    const dim3 grid((Tlen + FA_BQ - 1) / FA_BQ, n_head, B);
-    attn_fwd_sm100<<<grid, FA_THREADS, FA_SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, p);
+    const dim3 grid(n_head, B, (Tlen + FA_BQ - 1) / FA_BQ);
+    launch_pdl(attn_fwd_sm100, grid, FA_THREADS, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 
@@ -155,7 +182,7 @@ int flash_forward(T* context, float* lse, const T* q, const T* k, const T* v, in
     }
     const AttnParams p{B, Tlen, n_head, n_kv_head, 1.0f / sqrtf(static_cast<float>(head_dim))};
     const dim3 grid((Tlen + AT_TILE - 1) / AT_TILE, n_head, B);
-    attn_fwd_simt<T><<<grid, AT_THREADS, ATTN_FWD_SMEM, stream>>>(context, lse, q, k, v, p);
+    launch_pdl(attn_fwd_simt<T>, grid, AT_THREADS, ATTN_FWD_SMEM, stream, context, lse, q, k, v, p);
     return launch_ok();
 }
 
@@ -178,8 +205,8 @@ int flash_backward_tc(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, c
     p.delta = delta;
     p.status = b200_linear_status_word(ctx);
     const int tiles = (Tlen + FA_BQ - 1) / FA_BQ;
-    attn_bwd_dq_sm100<<<dim3(tiles, n_head, B), FA_THREADS, FB_DQ_SMEM_BYTES, stream>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
-    attn_bwd_dkv_sm100<<<dim3(tiles, n_kv_head, B), FA_THREADS, FB_DKV_SMEM_BYTES, stream>>>(tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+    launch_pdl(attn_bwd_dq_sm100, dim3(n_head, B, tiles), FA_THREADS, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+    launch_pdl(attn_bwd_dkv_sm100, dim3(n_kv_head, B, tiles), FA_THREADS, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 
@@ -204,14 +231,24 @@ int flash_backward(T* dq, T* dk, T* dv, const T* dcontext, const T* q, const T* 
         if (rc) return rc;
         context = ctx_tmp;
     }
-    attn_delta<T><<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(delta, dcontext, context, p);
+    bool delta_done = false;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (head_dim == 64 && ((reinterpret_cast<uintptr_t>(dcontext) | reinterpret_cast<uintptr_t>(context)) & 15) == 0) {
+            const long long tokens = static_cast<long long>(B) * Tlen;
+            launch_pdl(attn_delta_bf16x8, static_cast<unsigned>((tokens + 7) / 8 < 148 * 16 ? (tokens + 7) / 8 : 148 * 16), 256, 0, stream,
+                       delta, reinterpret_cast<const uint4*>(dcontext), reinterpret_cast<const uint4*>(context), B, Tlen, n_head);
+            delta_done = true;
+        }
+    }
+    if (!delta_done)
+        launch_pdl(attn_delta<T>, static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream, delta, dcontext, context, p);
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
         if (use_tensor_cores(dq, dk, dv, dcontext) && use_tensor_cores(q, k, v, q))
             return flash_backward_tc(dq, dk, dv, dcontext, q, k, v, lse, delta, B, Tlen, n_head, n_kv_head, stream);
     }
     const int tiles = (Tlen + AT_TILE - 1) / AT_TILE;
-    attn_bwd_dq_simt<T><<<dim3(tiles, n_head, B), AT_THREADS, ATTN_DQ_SMEM, stream>>>(dq, dcontext, q, k, v, lse, delta, p);
-    attn_bwd_dkv_simt<T><<<dim3(tiles, n_kv_head, B), AT_THREADS, ATTN_DKV_SMEM, stream>>>(dk, dv, dcontext, q, k, v, lse,
+    launch_pdl(attn_bwd_dq_simt<T>, dim3(tiles, n_head, B), AT_THREADS, ATTN_DQ_SMEM, stream, dq, dcontext, q, k, v, lse, delta, p);
+    launch_pdl(attn_bwd_dkv_simt<T>, dim3(tiles, n_kv_head, B), AT_THREADS, ATTN_DKV_SMEM, stream, dk, dv, dcontext, q, k, v, lse,
                                                                                          delta, p);
     return launch_ok();
 }
@@ -232,22 +269,27 @@ int rope(T* q, T* k, int B, int Tlen, int n_head, int n_kv_head, int head_dim, f
         RopeFreq freqs;
         for (int i = 0; i < half; ++i)  // cuda/rope.cu:29: 1 / theta^(2i / head_dim)
             freqs.f[i] = static_cast<float>(1.0 / pow(static_cast<double>(theta), (2.0 * i) / head_dim));
-        rope_table_kernel<<<(Tlen * half + 255) / 256, 256, 0, stream>>>(table, Tlen, half, freqs);
+        launch_pdl(rope_table_kernel, (Tlen * half + 255) / 256, 256, 0, stream, table, Tlen, half, freqs);
         if (cudaStreamSynchronize(stream) != cudaSuccess) return B200_E_CUDA;
         sc.rope_T = Tlen; sc.rope_hd = head_dim; sc.rope_theta = theta;
     }
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
         if ((head_dim % 8) == 0 && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15) == 0) {
             const long long total_vec = total / 4;
-            rope_kernel_bf16x8<DIR><<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(
-                reinterpret_cast<uint4*>(q), reinterpret_cast<uint4*>(k), total_vec, Tlen, n_head, n_kv_head, head_dim, table);
+            launch_pdl(rope_kernel_bf16x8<DIR>, static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream, reinterpret_cast<uint4*>(q), reinterpret_cast<uint4*>(k), total_vec, Tlen, n_head, n_kv_head, head_dim, table);
             return launch_ok();
         }
     }
-    rope_kernel<T, DIR><<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(q, k, total, Tlen, n_head, n_kv_head,
+    launch_pdl(rope_kernel<T, DIR>, static_cast<unsigned>((total + 255) / 256), 256, 0, stream, q, k, total, Tlen, n_head, n_kv_head,
                                                                                        head_dim, table);
     return launch_ok();
 }
+
+#define TRY(expr)              \
+    do {                       \
+        int rc__ = (expr);     \
+        if (rc__) return rc__; \
+    } while (0)
 
 // GEMM dispatch by storage type.
 int gemm(b200_linear_ctx* ctx, int which, int beta1, __nv_bfloat16* out, const __nv_bfloat16* x, const __nv_bfloat16* y, int M,
@@ -263,6 +305,45 @@ int backward(b200_linear_ctx* ctx, __nv_bfloat16* dA, __nv_bfloat16* dB, const _
 }
 int backward(b200_linear_ctx* ctx, float* dA, float* dB, const float* dC, const float* A, const float* Bm, int M, int N, int K) {
     return b200_linear_backward_f32(ctx, dA, dB, dC, A, Bm, M, N, K);
+}
+
+// Several projections of one input (Q, K, V; gate, up): one launch each way for bf16 (b200_linear_gemm_bf16_grouped),
+// one product at a time for fp32 or with B200_LINEAR_GROUPED=0.
+bool grouped_launches() {
+    static const bool on = [] {
+        const char* e = getenv("B200_LINEAR_GROUPED");
+        return !(e && atoi(e) == 0);
+    }();
+    return on;
+}
+template <typename T>
+int forward_group(b200_linear_ctx* ctx, int count, T* const* outs, const T* x, const T* const* ws, int M, const int* Ns, int K) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (grouped_launches()) {
+            const void* xs[3] = {x, x, x};
+            return b200_linear_gemm_bf16_grouped(ctx, B200_GEMM_FWD_NN, 0, count, reinterpret_cast<void* const*>(outs), xs,
+                                                 reinterpret_cast<const void* const*>(ws), M, Ns, K);
+        }
+    }
+    for (int i = 0; i < count; ++i) TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, outs[i], x, ws[i], M, Ns[i], K));
+    return B200_OK;
+}
+// dA = sum_i dCs[i] * Bs[i]^T, dBs[i] += A^T * dCs[i]
+template <typename T>
+int backward_group(b200_linear_ctx* ctx, int count, T* dA, T* const* dBs, const T* const* dCs, const T* A, const T* const* Bs,
+                   int M, const int* Ns, int K) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (grouped_launches())
+            return b200_linear_backward_bf16_grouped(ctx, count, dA, 0, reinterpret_cast<void* const*>(dBs),
+                                                     reinterpret_cast<const void* const*>(dCs), A,
+                                                     reinterpret_cast<const void* const*>(Bs), M, Ns, K);
+    }
+    TRY(backward(ctx, dA, dBs[0], dCs[0], A, Bs[0], M, Ns[0], K));
+    for (int i = 1; i < count; ++i) {   // the other inputs' gradients accumulate through the beta = 1 epilogue
+        TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dA, dCs[i], Bs[i], M, Ns[i], K));
+        TRY(gemm(ctx, B200_GEMM_WGRAD_TN, 1, dBs[i], A, dCs[i], M, Ns[i], K));
+    }
+    return B200_OK;
 }
 
 // What attention_forward leaves in the caller's `att` buffer ([B, n_head, T, T] elements of T in the reference):
@@ -283,21 +364,18 @@ struct AttStash {
     }
 };
 
-#define TRY(expr)              \
-    do {                       \
-        int rc__ = (expr);     \
-        if (rc__) return rc__; \
-    } while (0)
-
 template <typename T>
 int attention_fwd(b200_linear_ctx* ctx, T* out, T* q, T* k, T* v, void* att, const T* inp, const T* wq, const T* wk,
                   const T* wv, const T* wo, int B, int Tlen, int C, int n_head, int n_kv_head, float rope_theta) {
     if (!ctx || !out || !q || !k || !v || !inp || !wq || !wk || !wv || !wo || n_head <= 0 || C % n_head != 0) return B200_E_BADARG;
     const int hd = C / n_head, kv = n_kv_head * hd, BT = B * Tlen;
     if (!attn_args_ok(B, Tlen, n_head, n_kv_head, hd)) return B200_E_BADARG;
-    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, q, inp, wq, BT, C, C));
-    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, k, inp, wk, BT, kv, C));
-    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, v, inp, wv, BT, kv, C));
+    {   // attention.cu:597-599
+        T* const outs[3] = {q, k, v};
+        const T* const ws[3] = {wq, wk, wv};
+        const int Ns[3] = {C, kv, kv};
+        TRY(forward_group<T>(ctx, 3, outs, inp, ws, BT, Ns, C));
+    }
     TRY((rope<T, +1>(q, k, B, Tlen, n_head, n_kv_head, hd, rope_theta, nullptr)));
     AttStash<T> st(att, B, Tlen, C, n_head);
     T* context = st.context;
@@ -339,12 +417,12 @@ int attention_bwd(b200_linear_ctx* ctx, T* dinp, T* dwq, T* dwk, T* dwv, T* dwo,
     TRY(backward(ctx, dcontext, dwo, dout, context, wo, BT, C, C));                       // attention.cu:640
     TRY(flash_backward<T>(dq, dk, dv, dcontext, q, k, v, lse, context, B, Tlen, n_head, n_kv_head, hd, nullptr));
     TRY((rope<T, -1>(dq, dk, B, Tlen, n_head, n_kv_head, hd, rope_theta, nullptr)));          // attention.cu:669
-    TRY(backward(ctx, dinp, dwq, dq, inp, wq, BT, C, C));                                 // attention.cu:671
-    // attention.cu:673-688: d(input) of the K and V projections added to that of the Q projection
-    TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dinp, dk, wk, BT, kv, C));
-    TRY(gemm(ctx, B200_GEMM_WGRAD_TN, 1, dwk, inp, dk, BT, kv, C));
-    TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dinp, dv, wv, BT, kv, C));
-    return gemm(ctx, B200_GEMM_WGRAD_TN, 1, dwv, inp, dv, BT, kv, C);
+    // attention.cu:671-688: the three projections' weight gradients, and d(input) = the sum of their input gradients
+    T* const dws[3] = {dwq, dwk, dwv};
+    const T* const dcs[3] = {dq, dk, dv};
+    const T* const ws[3] = {wq, wk, wv};
+    const int Ns[3] = {C, kv, kv};
+    return backward_group<T>(ctx, 3, dinp, dws, dcs, inp, ws, BT, Ns, C);
 }
 
 template <typename T>
@@ -353,10 +431,9 @@ int swiglu_gate(T* hidden, const T* gate, const T* up, long long n) {
                      ((reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
     if (vec) {
         const long long n8 = n / 8;
-        swiglu_gate_kernel_bf16x8<<<static_cast<unsigned>((n8 + 255) / 256 < 65535 * 16 ? (n8 + 255) / 256 : 65535 * 16), 256>>>(
-            reinterpret_cast<uint4*>(hidden), reinterpret_cast<const uint4*>(gate), reinterpret_cast<const uint4*>(up), n8);
+        launch_pdl(swiglu_gate_kernel_bf16x8, static_cast<unsigned>((n8 + 255) / 256 < 65535 * 16 ? (n8 + 255) / 256 : 65535 * 16), 256, 0, nullptr, reinterpret_cast<uint4*>(hidden), reinterpret_cast<const uint4*>(gate), reinterpret_cast<const uint4*>(up), n8);
     } else {
-        swiglu_gate_kernel<T><<<static_cast<unsigned>((n + 255) / 256 < 65535 * 16 ? (n + 255) / 256 : 65535 * 16), 256>>>(hidden, gate, up, n);
+        launch_pdl(swiglu_gate_kernel<T>, static_cast<unsigned>((n + 255) / 256 < 65535 * 16 ? (n + 255) / 256 : 65535 * 16), 256, 0, nullptr, hidden, gate, up, n);
     }
     return launch_ok();
 }
@@ -366,8 +443,12 @@ int swiglu_fwd(b200_linear_ctx* ctx, T* out, T* gate, T* up, T* hidden, const T*
                const T* w_down, int BT, int C, int ff) {
     if (!ctx || !out || !gate || !up || !hidden || !inp || !w_gate || !w_up || !w_down || BT <= 0 || C <= 0 || ff <= 0)
         return B200_E_BADARG;
-    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, gate, inp, w_gate, BT, ff, C));
-    TRY(gemm(ctx, B200_GEMM_FWD_NN, 0, up, inp, w_up, BT, ff, C));
+    {   // swiglu.cu:161-162
+        T* const outs[2] = {gate, up};
+        const T* const ws[2] = {w_gate, w_up};
+        const int Ns[2] = {ff, ff};
+        TRY(forward_group<T>(ctx, 2, outs, inp, ws, BT, Ns, C));
+    }
     TRY(swiglu_gate<T>(hidden, gate, up, static_cast<long long>(BT) * ff));
     return gemm(ctx, B200_GEMM_FWD_NN, 0, out, hidden, w_down, BT, C, ff);
 }
@@ -389,24 +470,26 @@ int swiglu_bwd(b200_linear_ctx* ctx, T* dinp, T* dw_gate, T* dw_up, T* dw_down, 
     const bool vec = sizeof(T) == 2 && (n % 8) == 0;
     const unsigned blocks = static_cast<unsigned>(((vec ? n / 8 : n) + 255) / 256 < 65535 * 16 ? ((vec ? n / 8 : n) + 255) / 256 : 65535 * 16);
     if (vec)
-        swiglu_gate_backward_kernel_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(dgate), reinterpret_cast<uint4*>(dup),
+        launch_pdl(swiglu_gate_backward_kernel_bf16x8, blocks, 256, 0, nullptr, reinterpret_cast<uint4*>(dgate), reinterpret_cast<uint4*>(dup),
                                                             reinterpret_cast<const uint4*>(dhidden),
                                                             reinterpret_cast<const uint4*>(gate),
                                                             reinterpret_cast<const uint4*>(up), n / 8);
     else
-        swiglu_gate_backward_kernel<T><<<blocks, 256>>>(dgate, dup, dhidden, gate, up, n);
+        launch_pdl(swiglu_gate_backward_kernel<T>, blocks, 256, 0, nullptr, dgate, dup, dhidden, gate, up, n);
     TRY(launch_ok());
-    TRY(backward(ctx, dinp, dw_gate, dgate, inp, w_gate, BT, ff, C));                      // swiglu.cu:197
-    // swiglu.cu:199-208: d(input) of the up projection added to that of the gate projection
-    TRY(gemm(ctx, B200_GEMM_DGRAD_NT, 1, dinp, dup, w_up, BT, ff, C));
-    return gemm(ctx, B200_GEMM_WGRAD_TN, 1, dw_up, inp, dup, BT, ff, C);
+    // swiglu.cu:197-208: both projections' weight gradients, and d(input) = the sum of their input gradients
+    T* const dws[2] = {dw_gate, dw_up};
+    const T* const dcs[2] = {dgate, dup};
+    const T* const ws[2] = {w_gate, w_up};
+    const int Ns[2] = {ff, ff};
+    return backward_group<T>(ctx, 2, dinp, dws, dcs, inp, ws, BT, Ns, C);
 }
 
 template <typename T>
 int ce_forward(float* losses, T* logits_probs, const int* targets, int B, int Tlen, int V) {
     if (!losses || !logits_probs || !targets || B <= 0 || Tlen <= 0 || V <= 0) return B200_E_BADARG;
     const int rows = B * Tlen;
-    ce_row_forward<T><<<rows, CE_ROW_THREADS>>>(losses, logits_probs, targets, rows, V);
+    launch_pdl(ce_row_forward<T>, rows, CE_ROW_THREADS, 0, nullptr, losses, logits_probs, targets, rows, V);
     return launch_ok();
 }
 
@@ -419,10 +502,10 @@ int ce_backward(T* dlogits, const T* probs, const int* targets, int B, int Tlen,
     const long long n = static_cast<long long>(rows) * (vec ? V / 8 : V);
     const unsigned blocks = static_cast<unsigned>((n + 255) / 256 < 148LL * 64 ? (n + 255) / 256 : 148LL * 64);
     if (vec)
-        ce_row_backward_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(dlogits), reinterpret_cast<const uint4*>(probs),
+        launch_pdl(ce_row_backward_bf16x8, blocks, 256, 0, nullptr, reinterpret_cast<uint4*>(dlogits), reinterpret_cast<const uint4*>(probs),
                                                 targets, scale, rows, V / 8);
     else
-        ce_row_backward<T><<<blocks, 256>>>(dlogits, probs, targets, scale, rows, V);
+        launch_pdl(ce_row_backward<T>, blocks, 256, 0, nullptr, dlogits, probs, targets, scale, rows, V);
     return launch_ok();
 }
 
@@ -433,12 +516,12 @@ int rmsnorm_fwd(T* out, float* rrms, const T* inp, const T* weight, float eps, i
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
         if ((C % 8) == 0 && C <= 32 * 8 * RMS_VEC_MAX &&
             ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(inp) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0) {
-            rmsnorm_fwd_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(out), rrms, reinterpret_cast<const uint4*>(inp),
+            launch_pdl(rmsnorm_fwd_bf16x8, blocks, 256, 0, nullptr, reinterpret_cast<uint4*>(out), rrms, reinterpret_cast<const uint4*>(inp),
                                                 reinterpret_cast<const uint4*>(weight), eps, rows, C);
             return launch_ok();
         }
     }
-    rmsnorm_fwd_kernel<T><<<blocks, 256>>>(out, rrms, inp, weight, eps, rows, C);
+    launch_pdl(rmsnorm_fwd_kernel<T>, blocks, 256, 0, nullptr, out, rrms, inp, weight, eps, rows, C);
     return launch_ok();
 }
 
@@ -448,21 +531,37 @@ int rmsnorm_bwd(T* dinp, T* dweight, const T* dout, const T* inp, const T* weigh
     const int blocks = (rows + 7) / 8 < 148 * 8 ? (rows + 7) / 8 : 148 * 8;
     const int rows_per_chunk = rows >= 4096 ? 64 : 16;
     const int chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
-    float* partial = static_cast<float*>(scratch(S_RMS_PARTIAL, static_cast<size_t>(chunks) * C * sizeof(float)));
+    constexpr int kFusedBlocks = 148 * 2;
+    const size_t partial_rows = chunks > kFusedBlocks ? chunks : kFusedBlocks;
+    float* partial = static_cast<float*>(scratch(S_RMS_PARTIAL, partial_rows * C * sizeof(float)));
     if (!partial) return B200_E_CUDA;
     bool vec = false;
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
         vec = (C % 8) == 0 && C <= 32 * 8 * RMS_VEC_MAX &&
               ((reinterpret_cast<uintptr_t>(dinp) | reinterpret_cast<uintptr_t>(dout) | reinterpret_cast<uintptr_t>(inp) |
                 reinterpret_cast<uintptr_t>(weight)) & 15) == 0;
+        if (vec && C <= 1024) {
+            // one pass: d(input) and the per-block partial sums of d(weight), then the fixed-order reduction
+            const int fb = (rows + 7) / 8 < kFusedBlocks ? (rows + 7) / 8 : kFusedBlocks;
+            auto args = [&](auto kern) {
+                launch_pdl(kern, fb, 256, 0, nullptr, reinterpret_cast<uint4*>(dinp), partial, reinterpret_cast<const uint4*>(dout),
+                           reinterpret_cast<const uint4*>(inp), reinterpret_cast<const uint4*>(weight), rrms, rows, C);
+            };
+            if (C <= 256) args(rmsnorm_bwd_fused_bf16x8<1>);
+            else if (C <= 512) args(rmsnorm_bwd_fused_bf16x8<2>);
+            else if (C <= 768) args(rmsnorm_bwd_fused_bf16x8<3>);
+            else args(rmsnorm_bwd_fused_bf16x8<4>);
+            launch_pdl(rmsnorm_bwd_dw_reduce<T>, (C + 31) / 32, 256, 0, nullptr, dweight, partial, fb, C);
+            return launch_ok();
+        }
         if (vec)
-            rmsnorm_bwd_dinp_bf16x8<<<blocks, 256>>>(reinterpret_cast<uint4*>(dinp), reinterpret_cast<const uint4*>(dout),
+            launch_pdl(rmsnorm_bwd_dinp_bf16x8, blocks, 256, 0, nullptr, reinterpret_cast<uint4*>(dinp), reinterpret_cast<const uint4*>(dout),
                                                      reinterpret_cast<const uint4*>(inp), reinterpret_cast<const uint4*>(weight),
                                                      rrms, rows, C);
     }
-    if (!vec) rmsnorm_bwd_dinp_kernel<T><<<blocks, 256>>>(dinp, dout, inp, weight, rrms, rows, C);
-    rmsnorm_bwd_dw_partial_kernel<T><<<dim3((C + 255) / 256, chunks), 256>>>(partial, dout, inp, rrms, rows, C, rows_per_chunk);
-    rmsnorm_bwd_dw_final_kernel<T><<<(C + 255) / 256, 256>>>(dweight, partial, chunks, C);
+    if (!vec) launch_pdl(rmsnorm_bwd_dinp_kernel<T>, blocks, 256, 0, nullptr, dinp, dout, inp, weight, rrms, rows, C);
+    launch_pdl(rmsnorm_bwd_dw_partial_kernel<T>, dim3((C + 255) / 256, chunks), 256, 0, nullptr, partial, dout, inp, rrms, rows, C, rows_per_chunk);
+    launch_pdl(rmsnorm_bwd_dw_reduce<T>, (C + 31) / 32, 256, 0, nullptr, dweight, partial, chunks, C);
     return launch_ok();
 }
 
@@ -474,11 +573,10 @@ int residual_fwd(T* out, const T* a, const T* b, long long n) {
     const long long nvec = aligned ? n / VEC : 0;
     if (nvec > 0) {
         const long long blocks = (nvec + 255) / 256;
-        residual_forward_vec<T><<<static_cast<unsigned>(blocks < 148 * 32 ? blocks : 148 * 32), 256>>>(
-            reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b), nvec);
+        launch_pdl(residual_forward_vec<T>, static_cast<unsigned>(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, nullptr, reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(a), reinterpret_cast<const uint4*>(b), nvec);
     }
     const long long done = nvec * VEC;
-    if (done < n) residual_forward_scalar<T><<<static_cast<unsigned>((n - done + 255) / 256), 256>>>(out, a, b, done, n);
+    if (done < n) launch_pdl(residual_forward_scalar<T>, static_cast<unsigned>((n - done + 255) / 256), 256, 0, nullptr, out, a, b, done, n);
     return launch_ok();
 }
 
@@ -490,11 +588,10 @@ int residual_bwd(T* da, T* db, const T* dout, long long n) {
     const long long nvec = aligned ? n / VEC : 0;
     if (nvec > 0) {
         const long long blocks = (nvec + 255) / 256;
-        residual_backward_vec<T><<<static_cast<unsigned>(blocks < 148 * 32 ? blocks : 148 * 32), 256>>>(
-            reinterpret_cast<uint4*>(da), reinterpret_cast<uint4*>(db), reinterpret_cast<const uint4*>(dout), nvec);
+        launch_pdl(residual_backward_vec<T>, static_cast<unsigned>(blocks < 148 * 32 ? blocks : 148 * 32), 256, 0, nullptr, reinterpret_cast<uint4*>(da), reinterpret_cast<uint4*>(db), reinterpret_cast<const uint4*>(dout), nvec);
     }
     const long long done = nvec * VEC;
-    if (done < n) residual_backward_scalar<T><<<static_cast<unsigned>((n - done + 255) / 256), 256>>>(da, db, dout, done, n);
+    if (done < n) launch_pdl(residual_backward_scalar<T>, static_cast<unsigned>((n - done + 255) / 256), 256, 0, nullptr, da, db, dout, done, n);
     return launch_ok();
 }
 
@@ -646,9 +743,69 @@ int b200_rmsnorm_backward_f32(float* dinp, float* dweight, const float* dout, co
     return rmsnorm_bwd<float>(dinp, dweight, dout, inp, weight, rrms, BT, C);
 }
 
+// adamw_update / scale_grads / fp32_to_bf16 / compute_grad_norm_bf16, cuda/adamw.cu:42-58, 90-99, 153-191.
+int b200_adamw_update_f32(float* params, const float* grads, float* m, float* v, float lr, float beta1, float beta2, float eps,
+                          float weight_decay, int t, long long n) {
+    if (!params || !grads || !m || !v || n <= 0 || t <= 0) return B200_E_BADARG;
+    launch_pdl(adamw_kernel_f32, static_cast<unsigned>((n + 255) / 256), 256, 0, nullptr, params, grads, m, v, lr, beta1, beta2, eps, weight_decay,
+                                                                      1.0f - powf(beta1, static_cast<float>(t)),
+                                                                      1.0f - powf(beta2, static_cast<float>(t)), n);
+    return launch_ok();
+}
+int b200_adamw_update_bf16(void* params, float* master, const void* grads, float* m, float* v, float lr, float beta1, float beta2,
+                           float eps, float weight_decay, float grad_scale, int t, long long n) {
+    if (!params || !master || !grads || !m || !v || n <= 0 || t <= 0) return B200_E_BADARG;
+    launch_pdl(adamw_kernel_bf16, static_cast<unsigned>((n + 255) / 256), 256, 0, nullptr, static_cast<__nv_bfloat16*>(params), master, static_cast<const __nv_bfloat16*>(grads), m, v, lr, beta1, beta2, eps,
+        weight_decay, grad_scale, 1.0f - powf(beta1, static_cast<float>(t)), 1.0f - powf(beta2, static_cast<float>(t)), n);
+    return launch_ok();
+}
+int b200_scale_f32(float* data, float scale, long long n) {
+    if (!data || n <= 0) return B200_E_BADARG;
+    launch_pdl(scale_kernel_f32, static_cast<unsigned>((n + 255) / 256), 256, 0, nullptr, data, scale, n);
+    return launch_ok();
+}
+int b200_f32_to_bf16(const float* src, void* dst, long long n) {
+    if (!src || !dst || n <= 0) return B200_E_BADARG;
+    launch_pdl(f32_to_bf16_kernel, static_cast<unsigned>((n + 255) / 256), 256, 0, nullptr, src, static_cast<__nv_bfloat16*>(dst), n);
+    return launch_ok();
+}
+// *norm = sqrt(sum (g / loss_scale)^2) over the fp32 embedding gradient and the bf16 rest; non-finite bf16 entries
+// are zeroed in place.  Synchronises (the result is a host value), like the reference's.
+int b200_grad_norm_bf16(float* norm, const float* dwte_fp32, long long emb_n, void* grads_bf16, long long rest_n, float loss_scale) {
+    if (!norm || !dwte_fp32 || !grads_bf16 || emb_n <= 0 || rest_n <= 0 || loss_scale == 0.f) return B200_E_BADARG;
+    constexpr int kBlocks = 148 * 8;
+    float* partial = static_cast<float*>(scratch(S_NORM_PARTIAL, (2 * kBlocks + 1) * sizeof(float)));
+    if (!partial) return B200_E_CUDA;
+    const float scale = 1.0f / loss_scale;
+    launch_pdl(sumsq_partial_f32, kBlocks, 256, 0, nullptr, partial, dwte_fp32, scale, emb_n);
+    launch_pdl(sumsq_sanitize_partial_bf16, kBlocks, 256, 0, nullptr, partial + kBlocks, static_cast<__nv_bfloat16*>(grads_bf16), scale, rest_n);
+    launch_pdl(sum_partials, 1, 256, 0, nullptr, partial + 2 * kBlocks, partial, 2 * kBlocks);
+    float h = 0.f;
+    if (cudaMemcpy(&h, partial + 2 * kBlocks, sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) return B200_E_CUDA;
+    *norm = sqrtf(h);
+    return B200_OK;
+}
+
 }  // extern "C"
 
 // ------------------------------------------------- the reference's C++ overloads (exact mangled names)
+void adamw_update(float* params, const float* grads, float* m, float* v, float lr, float beta1, float beta2, float eps,
+                  float weight_decay, int t, int N) {
+    check(b200_adamw_update_f32(params, grads, m, v, lr, beta1, beta2, eps, weight_decay, t, N), "adamw_update(fp32)");
+}
+void adamw_update(__nv_bfloat16* params, float* master_params, const __nv_bfloat16* grads, float* m, float* v, float lr, float beta1,
+                  float beta2, float eps, float weight_decay, float grad_scale, int t, int N) {
+    check(b200_adamw_update_bf16(params, master_params, grads, m, v, lr, beta1, beta2, eps, weight_decay, grad_scale, t, N),
+          "adamw_update(bf16)");
+}
+void scale_grads(float* data, float scale, int N) { check(b200_scale_f32(data, scale, N), "scale_grads"); }
+void fp32_to_bf16(const float* src, __nv_bfloat16* dst, int N) { check(b200_f32_to_bf16(src, dst, N), "fp32_to_bf16"); }
+float compute_grad_norm_bf16(float* dwte_fp32, int emb_N, __nv_bfloat16* grads_bf16, int rest_N, float loss_scale) {
+    float norm = 0.f;
+    check(b200_grad_norm_bf16(&norm, dwte_fp32, emb_N, grads_bf16, rest_N, loss_scale), "compute_grad_norm_bf16");
+    return norm;
+}
+
 void residual_forward(float* out, const float* a, const float* b, int N) {
     check(b200_residual_forward_f32(out, a, b, N), "residual_forward(fp32)");
 }

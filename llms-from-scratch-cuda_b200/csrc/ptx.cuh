@@ -353,6 +353,13 @@ __device__ __forceinline__ void griddep_wait() {
 __device__ __forceinline__ void griddep_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+// First statement of every kernel that may be launched with programmatic stream serialization: wait until the
+// kernels before it in the stream have completed and their writes are visible, then let the next kernel's blocks
+// be scheduled as this kernel's blocks retire.  A no-op in a kernel launched the plain way.
+__device__ __forceinline__ void griddep_sync() {
+    griddep_wait();
+    griddep_launch_dependents();
+}
 
 // ----------------------------------------------------------------- cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -6,6 +6,9 @@ chriskuchar/llms-from-scratch-cuda) over the C ABI declared in include/b200_laye
     attention_forward / attention_backward                 kernels.cuh:156-206, 371-388
     swiglu_forward / swiglu_backward                       kernels.cuh:211-247, 390-396
     crossentropy_forward / crossentropy_softmax_backward   kernels.cuh:260-277, 402-404
+    rmsnorm_forward / rmsnorm_backward                     kernels.cuh:85-108, 357-362
+    residual_forward / residual_backward                   kernels.cuh:280-289, 407-408
+    adamw_update / compute_grad_norm_bf16                  kernels.cuh:299-309, 411-418
 
 Same names, argument order and meaning as the reference (the cublasHandle_t argument becomes a `Handle`, first
 instead of last); the dtype overload is picked from the tensors.  Arguments are torch CUDA tensors used as
@@ -147,3 +150,27 @@ def crossentropy_softmax_backward(dlogits, probs, targets, B, T, V, loss_scale=1
     else:
         rc = lib.b200_crossentropy_backward_f32(_p(dlogits), _p(probs), _p(targets), B, T, V)
     _check(rc, "crossentropy_softmax_backward")
+
+
+def adamw_update(params, grads, m, v, lr, beta1, beta2, eps, weight_decay, t, N, master_params=None, grad_scale=1.0):
+    """One AdamW step in place.  With `master_params` (fp32) the mixed-precision overload: bf16 `params` and `grads`,
+    the gradient multiplied by `grad_scale` first (adamw.cu:63-88); otherwise all fp32 (adamw.cu:12-40)."""
+    cll = ctypes.c_longlong
+    if master_params is not None:
+        lib.b200_adamw_update_bf16.argtypes = [vp] * 5 + [cf] * 6 + [ci, cll]
+        rc = lib.b200_adamw_update_bf16(_p(params), _p(master_params), _p(grads), _p(m), _p(v), lr, beta1, beta2, eps,
+                                        weight_decay, grad_scale, t, N)
+    else:
+        lib.b200_adamw_update_f32.argtypes = [vp] * 4 + [cf] * 5 + [ci, cll]
+        rc = lib.b200_adamw_update_f32(_p(params), _p(grads), _p(m), _p(v), lr, beta1, beta2, eps, weight_decay, t, N)
+    _check(rc, "adamw_update")
+
+
+def compute_grad_norm_bf16(dwte_fp32, emb_N, grads_bf16, rest_N, loss_scale):
+    """Global L2 norm of the unscaled gradient; zeroes non-finite bf16 entries in place (adamw.cu:171-191)."""
+    cll = ctypes.c_longlong
+    lib.b200_grad_norm_bf16.argtypes = [ctypes.POINTER(cf), vp, cll, vp, cll, cf]
+    out = cf(0.0)
+    _check(lib.b200_grad_norm_bf16(ctypes.byref(out), _p(dwte_fp32), emb_N, _p(grads_bf16), rest_N, loss_scale),
+           "compute_grad_norm_bf16")
+    return out.value

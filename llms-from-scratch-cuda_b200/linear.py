@@ -198,6 +198,40 @@ def gemm_ld(handle, which, beta1, out, x, y, M, N, K):
                   "gemm_ld")
 
 
+def _ptr_array(tensors, n=3):
+    arr = (ctypes.c_void_p * n)()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr() if t is not None else None
+    return arr
+
+
+def gemm_grouped(handle, which, beta1, outs, xs, ys, M, Ns, K):
+    """Up to three bf16 products that share an operand in one launch (include/b200_linear.h,
+    b200_linear_gemm_bf16_grouped): lists of torch CUDA tensors; xs may be a single tensor for FWD_NN / WGRAD_TN,
+    outs a single tensor for DGRAD_NT."""
+    n = len(Ns)
+    outs = list(outs) if isinstance(outs, (list, tuple)) else [outs] * n
+    xs = list(xs) if isinstance(xs, (list, tuple)) else [xs] * n
+    lib.b200_linear_gemm_bf16_grouped.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    ns = (ctypes.c_int * 3)(*Ns)
+    handle._check(lib.b200_linear_gemm_bf16_grouped(handle._h, which, int(bool(beta1)), n, _ptr_array(outs), _ptr_array(xs),
+                                                    _ptr_array(ys), M, ns, K), "gemm_grouped")
+
+
+def matmul_backward_grouped(handle, dA, dBs, dCs, A, Bs, M, Ns, K, accumulate_dA=False):
+    """matmul_backward for several products on one input: dA (+)= sum_i dCs[i] Bs[i]^T, dBs[i] += A^T dCs[i]."""
+    n = len(Ns)
+    lib.b200_linear_backward_bf16_grouped.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                      ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    ns = (ctypes.c_int * 3)(*Ns)
+    handle._check(lib.b200_linear_backward_bf16_grouped(
+        handle._h, n, dA.data_ptr() if dA is not None else None, int(bool(accumulate_dA)),
+        _ptr_array(dBs) if dBs is not None else None, _ptr_array(dCs), A.data_ptr() if A is not None else None,
+        _ptr_array(Bs) if Bs is not None else None, M, ns, K), "matmul_backward_grouped")
+
+
 def plan_bf16(which, beta1, M, N, K, sm_count=148):
     p = Plan()
     rc = lib.b200_linear_plan_bf16(which, int(bool(beta1)), M, N, K, sm_count, ctypes.byref(p))

@@ -50,7 +50,8 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
     ref_src = os.path.join(reference, "cuda", "matmul.cu")
     ref_ce = os.path.join(reference, "cuda", "crossentropy.cu")
     # the layers that call the GEMMs, and what they call in turn
-    ref_layers = [os.path.join(reference, "cuda", f) for f in ("attention.cu", "swiglu.cu", "rope.cu", "softmax.cu", "residual.cu")]
+    ref_layers = [os.path.join(reference, "cuda", f) for f in ("attention.cu", "swiglu.cu", "rope.cu", "softmax.cu", "residual.cu",
+                                                                  "adamw.cu")]
     shim = os.path.join(HERE, "ref_shim.cu")
     if not os.path.exists(ref_src) or shutil.which("nvcc") is None:
         return out if os.path.exists(out) else None
@@ -68,7 +69,7 @@ def build_reference(reference=DEFAULT_REFERENCE, force=False):
 KERNEL_SOURCES = ["embedding.cu", "rmsnorm.cu", "rope.cu", "flash_attention.cu", "attention.cu", "swiglu.cu",
                   "softmax.cu", "crossentropy.cu", "residual.cu", "adamw.cu"]
 # the callers of the GEMM path that the library also replaces (csrc/layers_api.cu exports their signatures)
-LAYER_SOURCES = ["flash_attention.cu", "attention.cu", "swiglu.cu", "crossentropy.cu", "rmsnorm.cu", "residual.cu"]
+LAYER_SOURCES = ["flash_attention.cu", "attention.cu", "swiglu.cu", "crossentropy.cu", "rmsnorm.cu", "residual.cu", "adamw.cu"]
 
 
 def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False):

@@ -101,4 +101,17 @@ void ref_rope_forward_bf16(void* q, void* k, int B, int T, int n_head, int n_kv_
     rope_forward((__nv_bfloat16*)q, (__nv_bfloat16*)k, B, T, n_head, n_kv_head, head_dim, theta);
 }
 
+// cuda/adamw.cu: the optimizer step and the global gradient norm, as the reference's main.cpp calls them
+void ref_adamw_update_bf16(void* params, float* master, const void* grads, float* m, float* v, float lr, float beta1, float beta2,
+                           float eps, float weight_decay, float grad_scale, int t, int N) {
+    adamw_update((__nv_bfloat16*)params, master, (const __nv_bfloat16*)grads, m, v, lr, beta1, beta2, eps, weight_decay, grad_scale, t, N);
+}
+void ref_adamw_update_f32(float* params, const float* grads, float* m, float* v, float lr, float beta1, float beta2, float eps,
+                          float weight_decay, int t, int N) {
+    adamw_update(params, grads, m, v, lr, beta1, beta2, eps, weight_decay, t, N);
+}
+float ref_grad_norm_bf16(float* dwte, int emb_N, void* grads, int rest_N, float loss_scale) {
+    return compute_grad_norm_bf16(dwte, emb_N, (__nv_bfloat16*)grads, rest_N, loss_scale);
+}
+
 }  // extern "C"

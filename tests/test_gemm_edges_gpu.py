@@ -308,3 +308,118 @@ def test_context_belongs_to_its_device(pkg, handle):
         torch.cuda.set_device(0)
     pkg.matmul_forward(handle, a0.clone(), a0, a0, 256, 256, 256)
     handle.sync()
+
+
+def _rel(got, want):
+    return ((got.double() - want).abs().max() / want.abs().max().clamp_min(1e-30)).item()
+
+
+GROUPS = [(8192, (768, 256, 256), 768),     # Q, K, V of the 125M model
+          (2048, (2048, 2048), 768),        # gate, up
+          (1000, (128, 64, 192), 320),      # ragged token count, three different widths
+          (384, (1024, 256), 1024),         # llama3-like K / V widths
+          (520, (72, 136), 264)]            # widths that are not multiples of 64: runs as single products
+
+
+@pytest.mark.parametrize("M,Ns,K", GROUPS)
+def test_grouped_forward_and_weight_gradient(pkg, handle, M, Ns, K):
+    """Several products on one input in one launch: Y_i = X W_i and dW_i += X^T dY_i, against float64 and against the
+    single-product entry point (same arithmetic: equal up to the order of fp32 partial sums where the contraction is split)."""
+    g = torch.Generator(device=DEV).manual_seed(4321)
+    dt = torch.bfloat16
+    x = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    ws = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    outs = [torch.full((M, n), float("nan"), device=DEV, dtype=dt) for n in Ns]
+    pkg.gemm_grouped(handle, pkg.FWD_NN, 0, outs, x, ws, M, list(Ns), K)
+    handle.sync()
+    for o, w, n in zip(outs, ws, Ns):
+        assert _rel(o, x.double() @ w.double()) <= 1e-2
+        single = torch.empty_like(o)
+        pkg.gemm(handle, pkg.FWD_NN, 0, single, x, w, M, n, K)
+        handle.sync()
+        assert _rel(o, single.double()) <= 4e-3
+    dys = [torch.randn(M, n, device=DEV, generator=g).to(dt) for n in Ns]
+    olds = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    for beta in (0, 1):
+        dws = [o.clone() for o in olds]
+        pkg.gemm_grouped(handle, pkg.WGRAD_TN, beta, dws, x, dys, M, list(Ns), K)
+        handle.sync()
+        for dw, dy, old in zip(dws, dys, olds):
+            prod = x.double().T @ dy.double()
+            # beta = 1 rounds like the reference's cuBLAS call: bf16(bf16(product) + old)
+            want = (prod.to(dt).double() + old.double()) if beta else prod
+            assert _rel(dw, want) <= 1e-2, (beta, _rel(dw, want))
+
+
+@pytest.mark.parametrize("M,Ns,K", GROUPS)
+def test_grouped_input_gradient_is_one_sum(pkg, handle, M, Ns, K):
+    """dX (+)= sum_i dY_i W_i^T through one accumulator: the float64 sum rounded once."""
+    g = torch.Generator(device=DEV).manual_seed(8765)
+    dt = torch.bfloat16
+    dys = [torch.randn(M, n, device=DEV, generator=g).to(dt) for n in Ns]
+    ws = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    old = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    total = sum(dy.double() @ w.double().T for dy, w in zip(dys, ws))
+    for beta in (0, 1):
+        dx = old.clone()
+        pkg.gemm_grouped(handle, pkg.DGRAD_NT, beta, dx, dys, ws, M, list(Ns), K)
+        handle.sync()
+        assert _rel(dx, total + old.double() if beta else total) <= 1e-2, (beta,)
+    if all(n % 64 == 0 for n in Ns):   # the one-launch path: a single rounding, so far tighter than three
+        dx = torch.empty_like(old)
+        pkg.gemm_grouped(handle, pkg.DGRAD_NT, 0, dx, dys, ws, M, list(Ns), K)
+        handle.sync()
+        assert torch.equal(dx, total.to(dt)) or _rel(dx, total) <= 4e-3
+
+
+@pytest.mark.parametrize("bn,pair,splits", [(64, 0, 1), (128, 0, 1), (256, 0, 1), (128, 1, 1), (256, 1, 1), (128, 0, 3), (256, 1, 2),
+                                            (64, 0, -2), (128, 1, -3)])
+def test_grouped_launch_with_every_tile_shape_and_split(pkg, handle, bn, pair, splits):
+    """The grouped launches under forced tile widths, CTA pairs, split contraction (workspace and cluster)."""
+    g = torch.Generator(device=DEV).manual_seed(2468)
+    dt = torch.bfloat16
+    M, Ns, K = 1536, (768, 256, 256), 768
+    x = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    ws = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    dys = [torch.randn(M, n, device=DEV, generator=g).to(dt) for n in Ns]
+    olds = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    try:
+        handle.force_plan(bn, pair, splits)
+        outs = [torch.empty(M, n, device=DEV, dtype=dt) for n in Ns]
+        pkg.gemm_grouped(handle, pkg.FWD_NN, 0, outs, x, ws, M, list(Ns), K)
+        dws = [o.clone() for o in olds]
+        pkg.gemm_grouped(handle, pkg.WGRAD_TN, 1, dws, x, dys, M, list(Ns), K)
+        dx = torch.empty(M, K, device=DEV, dtype=dt)
+        pkg.gemm_grouped(handle, pkg.DGRAD_NT, 0, dx, dys, ws, M, list(Ns), K)
+        handle.sync()
+    finally:
+        handle.force_plan(-1, 0, 0)
+    for o, w in zip(outs, ws):
+        assert _rel(o, x.double() @ w.double()) <= 1e-2
+    for dw, dy, old in zip(dws, dys, olds):
+        assert _rel(dw, (x.double().T @ dy.double()).to(dt).double() + old.double()) <= 1e-2
+    assert _rel(dx, sum(dy.double() @ w.double().T for dy, w in zip(dys, ws))) <= 1e-2
+
+
+def test_grouped_backward_matches_separate_calls(pkg, handle):
+    """matmul_backward for a group (dA = sum, dB_i += ...; two launches side by side) against matmul_backward per product
+    with the input gradients added in float64."""
+    g = torch.Generator(device=DEV).manual_seed(1357)
+    dt = torch.bfloat16
+    M, Ns, K = 4096, (768, 256, 256), 768
+    a = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    bs = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    dcs = [torch.randn(M, n, device=DEV, generator=g).to(dt) for n in Ns]
+    olds = [torch.randn(K, n, device=DEV, generator=g).to(dt) for n in Ns]
+    dbs = [o.clone() for o in olds]
+    da = torch.empty(M, K, device=DEV, dtype=dt)
+    pkg.matmul_backward_grouped(handle, da, dbs, dcs, a, bs, M, list(Ns), K)
+    handle.sync()
+    da_sum = torch.zeros(M, K, dtype=torch.float64, device=DEV)
+    for b, dc, old, db, n in zip(bs, dcs, olds, dbs, Ns):
+        da1, db1 = torch.empty(M, K, device=DEV, dtype=dt), old.clone()
+        pkg.matmul_backward(handle, da1, db1, dc, a, b, M, n, K)
+        handle.sync()
+        da_sum += da1.double()
+        assert _rel(db, db1.double()) <= 4e-3
+    assert _rel(da, da_sum) <= 1e-2

@@ -261,7 +261,7 @@ def test_whole_row_cross_entropy_fp32(layers):
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("rows,C", [(8192, 768), (300, 100)])
+@pytest.mark.parametrize("rows,C", [(8192, 768), (300, 100), (1000, 1024), (77, 256), (4096, 512), (130, 2048)])
 def test_rmsnorm_against_float64(layers, dt, rows, C):
     """cuda/rmsnorm.cu restated in float64 (forward formula at :27-33, backward at :60-72), the weight gradient
     accumulating over two calls onto a non-zero start."""
@@ -309,6 +309,81 @@ def test_residual_add_is_exact(layers, dt, n, offset):
     torch.cuda.synchronize()
     assert torch.equal(out, want) and (x is None or torch.equal(x, want))
     assert torch.equal(da, want_da) and torch.equal(db, want_db)
+
+
+def _adamw64(p, g, m, v, lr, b1, b2, eps, wd, t):
+    """cuda/adamw.cu:12-40 in float64."""
+    m2 = b1 * m + (1 - b1) * g
+    v2 = b2 * v + (1 - b2) * g * g
+    p2 = p - lr * ((m2 / (1 - b1 ** t)) / ((v2 / (1 - b2 ** t)).sqrt() + eps) + wd * p)
+    return p2, m2, v2
+
+
+@pytest.mark.parametrize("n", [768 * 768, 100003])
+def test_adamw_against_float64_and_the_reference_live(layers, ref_lib, n):
+    """Three steps of both overloads against float64 (fp32 state: 1e-5 relative; the bf16 weights are the rounding of the
+    master weights, exactly), and against the reference's own adamw.cu on the same state."""
+    lr, b1, b2, eps, wd, gs = 3e-4, 0.9, 0.95, 1e-8, 0.1, 1.0 / 1024
+    p0, g_all = rnd((n,), 1, torch.float32, 0.02), [rnd((n,), 10 + t, torch.float32) for t in range(3)]
+    # fp32 overload
+    p, m, v = p0.to(DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p64, m64, v64 = p0.double(), torch.zeros(n).double(), torch.zeros(n).double()
+    for t in range(1, 4):
+        layers.adamw_update(p, g_all[t - 1].to(DEV), m, v, lr, b1, b2, eps, wd, t, n)
+        p64, m64, v64 = _adamw64(p64, g_all[t - 1].double(), m64, v64, lr, b1, b2, eps, wd, t)
+    torch.cuda.synchronize()
+    assert rel(p, p64) <= 1e-5 and rel(m, m64) <= 1e-5 and rel(v, v64) <= 1e-5
+    # mixed precision: bf16 weights and scaled bf16 gradients, fp32 master weights and moments
+    master, m, v = p0.to(DEV), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    pb = master.to(torch.bfloat16)
+    r_master, r_m, r_v, r_pb = master.clone(), m.clone(), v.clone(), pb.clone()
+    p64, m64, v64 = p0.double(), torch.zeros(n).double(), torch.zeros(n).double()
+    have_ref = hasattr(ref_lib, "ref_adamw_update_bf16")
+    if have_ref:
+        vpt, cf, ci = ctypes.c_void_p, ctypes.c_float, ctypes.c_int
+        ref_lib.ref_adamw_update_bf16.argtypes = [vpt] * 5 + [cf] * 6 + [ci, ci]
+        ref_lib.ref_adamw_update_bf16.restype = None
+    for t in range(1, 4):
+        gb = (g_all[t - 1] * 1024).to(torch.bfloat16)
+        gd = gb.to(DEV)
+        layers.adamw_update(pb, gd, m, v, lr, b1, b2, eps, wd, t, n, master_params=master, grad_scale=gs)
+        p64, m64, v64 = _adamw64(p64, gb.double() * gs, m64, v64, lr, b1, b2, eps, wd, t)
+        if have_ref:
+            ref_lib.ref_adamw_update_bf16(r_pb.data_ptr(), r_master.data_ptr(), gd.data_ptr(), r_m.data_ptr(), r_v.data_ptr(),
+                                          lr, b1, b2, eps, wd, gs, t, n)
+    torch.cuda.synchronize()
+    assert rel(master, p64) <= 1e-5 and rel(m, m64) <= 1e-5 and rel(v, v64) <= 1e-5
+    assert torch.equal(pb, master.to(torch.bfloat16))
+    if have_ref:   # the reference is built with fast-math (approximate pow, divide, sqrt): close, not bit-equal
+        assert rel(r_master, p64) <= 1e-4
+        assert rel(master, r_master.double().cpu()) <= 1e-4
+
+
+def test_gradient_norm_sanitizes_and_matches_float64(layers, ref_lib):
+    """compute_grad_norm_bf16: float64 norm of the unscaled gradient over both parts; inf / nan / > 65000 entries of
+    the bf16 part are zeroed in place and left out of the sum; twice the same answer (fixed summation order)."""
+    emb_n, rest_n, scale = 32000 * 768 // 8, 5_000_003, 1024.0
+    dwte = rnd((emb_n,), 1, torch.float32, 3.0)
+    g = rnd((rest_n,), 2, torch.float32, 50.0).to(torch.bfloat16)
+    g[17], g[4099], g[rest_n - 1] = float("inf"), float("nan"), 7.0e7 * 1.0   # 7e7 / 1024 > 65000
+    g[5] = -float("inf")
+    keep = torch.ones(rest_n, dtype=torch.bool)
+    keep[[5, 17, 4099, rest_n - 1]] = False
+    want = ((dwte.double() / scale).pow(2).sum() + (g.double()[keep] / scale).pow(2).sum()).sqrt().item()
+    dw_d, g_d = dwte.to(DEV), g.to(DEV)
+    got = layers.compute_grad_norm_bf16(dw_d, emb_n, g_d, rest_n, scale)
+    assert abs(got - want) <= 1e-5 * want, (got, want)
+    cleaned = g.clone()
+    cleaned[~keep] = 0
+    assert torch.equal(g_d.cpu(), cleaned)
+    assert layers.compute_grad_norm_bf16(dw_d, emb_n, g_d, rest_n, scale) == got
+    if hasattr(ref_lib, "ref_grad_norm_bf16"):
+        vpt, ci = ctypes.c_void_p, ctypes.c_int
+        ref_lib.ref_grad_norm_bf16.argtypes = [vpt, ci, vpt, ci, ctypes.c_float]
+        ref_lib.ref_grad_norm_bf16.restype = ctypes.c_float
+        g_r = g.to(DEV)
+        ref = ref_lib.ref_grad_norm_bf16(dw_d.data_ptr(), emb_n, g_r.data_ptr(), rest_n, scale)
+        assert abs(ref - want) <= 1e-4 * want and torch.equal(g_r, g_d)
 
 
 def test_layer_entry_points_refuse_bad_arguments(layers, handle):
