@@ -34,7 +34,8 @@ constexpr int FA_TILE_BYTES = 128 * 64 * 2;                 // one 128 x 64 bf16
 constexpr int FA_KV_STAGES = 3;   // K/V tiles in flight: a stage is free again only after its P V product
 constexpr int FA_SMEM_BYTES = 4096 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
                               2 * 2 * FA_TILE_BYTES /*P x 2: two 64-column panels each*/ + 1024 /*alignment*/;
-constexpr int FA_TMEM_COLS = 512;  // S: 2 x 128 columns, PV: 2 x 64 columns
+constexpr int FA_TMEM_COLS = 512;  // S: 2 x 128 columns, O: 2 x 64 columns (forward), dP / dQ / dK / dV (backward)
+constexpr float FA_RESCALE_STEP = 8.0f;   // a row's reference maximum moves only when the true maximum has grown by 2^8
 
 struct FaParams {
     int B, T, n_head, n_kv_head;
@@ -48,13 +49,12 @@ struct alignas(8) FaCtrl {
     unsigned long long kv_full[FA_KV_STAGES], kv_empty[FA_KV_STAGES];
     unsigned long long s_full[2], s_empty[2];
     unsigned long long p_full[2], p_empty[2];
-    unsigned long long pv_full[2], pv_empty[2];
-    unsigned long long xchg[2];        // the two halves of every row have published their partial maximum (per tile parity)
-    unsigned long long lsum;           // ... and their partial row sums (once, at the end)
+    unsigned long long pv_done;        // the P V products of one more key tile have retired (one phase per tile)
+    unsigned long long lsum;           // the two halves of every row have published their maximum and row sum (once, at the end)
     uint32_t tmem_base;
     int abort_flag;
-    float part[2][2][FA_BQ];           // [tile parity][half][row]: partial row maxima
-    float lpart[2][FA_BQ];             // [half][row]: partial row sums
+    float mpart[2][FA_BQ];             // [half][row]: reference maximum of that half of the row
+    float lpart[2][FA_BQ];             // [half][row]: its row sum, in units of 2^-maximum
 };
 constexpr int FA_CTRL_BYTES = 4096;
 static_assert(sizeof(FaCtrl) <= FA_CTRL_BYTES, "control block");
@@ -98,10 +98,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
                 mbar_init(smem_u32(&ctrl->p_full[i]), FA_SOFTMAX_WARPS);
                 mbar_init(smem_u32(&ctrl->p_empty[i]), 1);
-                mbar_init(smem_u32(&ctrl->pv_full[i]), 1);
-                mbar_init(smem_u32(&ctrl->pv_empty[i]), FA_SOFTMAX_WARPS);
-                mbar_init(smem_u32(&ctrl->xchg[i]), FA_SOFTMAX_WARPS);
             }
+            mbar_init(smem_u32(&ctrl->pv_done), 1);
             mbar_init(smem_u32(&ctrl->lsum), FA_SOFTMAX_WARPS);
             ctrl->abort_flag = 0;
             fence_mbar_init();
@@ -122,7 +120,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after();
     griddep_sync();   // everything above touches no global memory and may overlap the previous kernel's tail
     const uint32_t tmem_base = ctrl->tmem_base;
-    const uint32_t tmem_S = tmem_base, tmem_PV = tmem_base + 256;   // S[b] at +128 b, PV[b] at +64 b
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;   // S[b] at +128 b; O of key-column half h at +64 h
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -170,10 +168,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     umma_commit(smem_u32(&ctrl->s_full[s]));
                 }
             }
-            if (j >= 1) {     // PV_i = P_i V_i for the tile before
+            if (j >= 1) {     // O_h += P_ih V_ih for the tile before, h = the two 64-column halves of the key tile
                 const int i = j - 1, s = i & 1, st = i % FA_KV_STAGES;
-                ok = mbar_wait(smem_u32(&ctrl->p_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
-                     mbar_wait(smem_u32(&ctrl->pv_empty[s]), ((i >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
+                ok = mbar_wait(smem_u32(&ctrl->p_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -183,11 +180,13 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     const uint32_t pbase = smem_u32(sP + s * 2 * FA_TILE_BYTES);
 #pragma unroll
                     for (int k = 0; k < FA_BKV / UMMA_K; ++k) {
-                        // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel
+                        // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel.  Panel h (k >> 2) meets
+                        // key rows 64 h .. 64 h + 63 of V and accumulates into its own O: the halves keep separate maxima.
                         const uint64_t descP = umma_smem_desc(pbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
-                        umma_f16<1>(tmem_PV + s * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV, k > 0 ? 1u : 0u);
+                        umma_f16<1>(tmem_O + (k >> 2) * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV,
+                                    (i > 0 || (k & 3) > 0) ? 1u : 0u);
                     }
-                    umma_commit(smem_u32(&ctrl->pv_full[s]));
+                    umma_commit(smem_u32(&ctrl->pv_done));
                     umma_commit(smem_u32(&ctrl->kv_empty[st]));
                     umma_commit(smem_u32(&ctrl->p_empty[s]));
                 }
@@ -200,10 +199,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int r = qrt * 32 + lane;                              // query row inside the tile
         const int row = qt * FA_BQ + r;                             // query position
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
-        constexpr int HC = FA_BKV / 2, HO = FA_HD / 2;              // columns of S and of O per thread
-        float o[HO];
-#pragma unroll
-        for (int e = 0; e < HO; ++e) o[e] = 0.f;
+        constexpr int HC = FA_BKV / 2, HO = FA_HD / 2;              // columns of S per thread; output columns per thread
+        // Each half of a row is a softmax of its own: reference maximum m (log2 units), row sum l in units of 2^-m, and
+        // an accumulator O_half in TMEM that the tensor core adds P_half V_half to.  m follows the true maximum lazily:
+        // it moves (and O_half, l are rescaled) only when the maximum has grown by more than FA_RESCALE_STEP, so that
+        // P stays below 2^8 and the common tile costs one max, one FMA + exp2 and one add per element and no exchange.
+        // The two halves are put together once, after the last tile.
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
@@ -215,8 +216,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const uint32_t tS = tmem_S + s * 128 + lane_off + half * HC;
             const bool diag = j == qt;                              // the only tile that needs the causal / length mask
             const int col0 = j * FA_BKV + half * HC;
-            // This thread's half of the row of S comes into registers with one wait, scaled to units of log2 (scores
-            // times log2(e) / sqrt(d)) and masked; the S buffer is free for tile j + 2 at once.
+            // this thread's half of the row of S comes into registers with one wait; the S buffer is free for tile j + 2
             float x[HC];
             tmem_ld_32x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
             tmem_ld_32x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
@@ -224,36 +224,50 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
-            // partial row maximum: four independent chains, then the other half's through shared memory
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (diag) {
 #pragma unroll
                 for (int e = 0; e < HC; ++e) {
                     const int col = col0 + e;
-                    x[e] = (col > row || col >= p.T) ? -INFINITY : x[e] * p.scale_log2e;
+                    if (col > row || col >= p.T) x[e] = -INFINITY;
                     mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
                 }
             } else {
 #pragma unroll
-                for (int e = 0; e < HC; ++e) {
-                    x[e] *= p.scale_log2e;
-                    mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
-                }
+                for (int e = 0; e < HC; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], x[e]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            ctrl->part[s][half][r] = mx;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->xchg[s]));
-            ok = mbar_wait(smem_u32(&ctrl->xchg[s]), (j >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_PEER);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const float m_new = fmaxf(m, fmaxf(mx, ctrl->part[s][half ^ 1][r]));
-            const float alpha = fa_exp2(m - m_new);                 // 0 on the first tile (m = -inf)
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;   // the scale is positive
+            const bool grow = mx > m + FA_RESCALE_STEP;             // also the first finite maximum (m = -inf)
+            if (__any_sync(0xffffffffu, grow)) {
+                // rare after the first tiles: move this row's reference maximum and bring l and O_half along
+                const float m_new = grow ? mx : m;
+                const float alpha = (m_new == m) ? 1.0f : fa_exp2(m - m_new);   // 0 when m was -inf
+                if (j > 0) {
+                    // the products of tile j - 1 must have landed in O; those of tile j wait for this warp's P
+                    ok = mbar_wait(smem_u32(&ctrl->pv_done), (j - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t acc[32];
+                        tmem_ld_32x32(tmem_O + half * FA_HD + lane_off + c * 32, acc);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                        tmem_st_32x32(tmem_O + half * FA_HD + lane_off + c * 32, acc);
+                    }
+                    tmem_st_wait();
+                }
+                l *= alpha;
+                m = m_new;
+            }
             // the tensor core must have finished reading this P buffer (tile j - 2)
             ok = mbar_wait(smem_u32(&ctrl->p_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // P = exp2(S - max) as bf16 into this half's 64-column panel, partial row sum in fp32 (four chains again)
+            // P = exp2(S scale - m) as bf16 into this half's 64-column panel, row sum in fp32 (four chains)
+            const float neg_m = (m == -INFINITY) ? 0.f : -m;       // a half with nothing visible yet: P = exp2(-inf) = 0
             uint8_t* panel = sP + s * 2 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -261,7 +275,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 uint32_t packed[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    const float p0 = fa_exp2(x[c * 32 + e] - m_new), p1 = fa_exp2(x[c * 32 + e + 1] - m_new);
+                    const float p0 = fa_exp2(fmaf(x[c * 32 + e], p.scale_log2e, neg_m));
+                    const float p1 = fa_exp2(fmaf(x[c * 32 + e + 1], p.scale_log2e, neg_m));
                     sum4[(e >> 1) & 3] += p0 + p1;
                     packed[e >> 1] = pack_bf16x2(p0, p1);
                 }
@@ -273,58 +288,48 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
             fence_proxy_async_smem();
+            tc_fence_before();                                         // orders a rescale of O before the next product
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->p_full[s]));    // this warp's part of P is ready for the tensor core
-            l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            m = m_new;
-            if (j >= 1) {
-                // O += P V of the tile before (computed while this tile's softmax ran), then move O to the new maximum
-                const int i = j - 1, si = i & 1;
-                ok = mbar_wait(smem_u32(&ctrl->pv_full[si]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t pv[HO];
-                tmem_ld_32x32(tmem_PV + si * 64 + lane_off + half * HO, pv);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < HO; ++e) o[e] = (o[e] + __uint_as_float(pv[e])) * alpha;
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctrl->pv_empty[si]));
-            }
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         }
         if (ok) {
-            // the two halves of a row add up their partial sums
+            // the two halves of a row exchange (m, l); the last products must have retired
+            ctrl->mpart[half][r] = m;
             ctrl->lpart[half][r] = l;
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->lsum));
-            const int i = n_kv - 1, si = i & 1;
             ok = mbar_wait(smem_u32(&ctrl->lsum), 0, abort_flag, p.status, DEV_TIMEOUT_PEER) &&
-                 mbar_wait(smem_u32(&ctrl->pv_full[si]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
+                 mbar_wait(smem_u32(&ctrl->pv_done), (n_kv - 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
             tc_fence_after();
-            const int si = (n_kv - 1) & 1;
-            const float l_row = l + ctrl->lpart[half ^ 1][r];
+            const float m_a = ctrl->mpart[0][r], m_b = ctrl->mpart[1][r];
+            const float m_row = fmaxf(m_a, m_b);                        // finite: column `row` itself is always visible
+            const float w_a = (m_a == -INFINITY) ? 0.f : fa_exp2(m_a - m_row), w_b = (m_b == -INFINITY) ? 0.f : fa_exp2(m_b - m_row);
+            const float l_row = ctrl->lpart[0][r] * w_a + ctrl->lpart[1][r] * w_b;
             const float inv = 1.0f / l_row;
-            // every tensor-core read of the P buffers has completed (the last commit covers them): stage O in P buffer 0
+            // every tensor-core read of the P buffers has completed (the last commit covers them): stage O in P buffer 0.
+            // This thread writes output columns 32 half .. 32 half + 31 of its row: w_a O_a + w_b O_b over l.
             uint8_t* orow = sP + r * 128;
-            uint32_t v[HO];
-            tmem_ld_32x32(tmem_PV + si * 64 + lane_off + half * HO, v);
+            uint32_t va[HO], vb[HO];
+            tmem_ld_32x32(tmem_O + lane_off + half * HO, va);
+            tmem_ld_32x32(tmem_O + FA_HD + lane_off + half * HO, vb);
             tmem_ld_wait();
+            const float ca = w_a * inv, cb = w_b * inv;
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd) {
                 float y[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = (o[qd * 8 + e] + __uint_as_float(v[qd * 8 + e])) * inv;
+                for (int e = 0; e < 8; ++e)
+                    y[e] = __uint_as_float(va[qd * 8 + e]) * ca + __uint_as_float(vb[qd * 8 + e]) * cb;
                 const int chunk = (half * 4 + qd) ^ (r & 7);
                 *reinterpret_cast<uint4*>(orow + chunk * 16) =
                     make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
             }
             if (half == 0 && row < p.T)
-                p.lse[(static_cast<long long>(b) * p.n_head + h) * p.T + row] = (m + log2f(l_row)) * 0.69314718055994531f;
+                p.lse[(static_cast<long long>(b) * p.n_head + h) * p.T + row] = (m_row + log2f(l_row)) * 0.69314718055994531f;
         }
         // All eight epilogue warps come here exactly once, whether or not their waits succeeded, so this barrier
         // cannot be left waiting; the tile is stored only if nobody gave up.
@@ -535,51 +540,67 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int j = 0; j < n_kv && ok; ++j) {
             const int s = j & 1;
             ok = mbar_wait(smem_u32(&ctrl->s_full[s]), (j >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
-                 mbar_wait(smem_u32(&ctrl->dp_full), j & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
-                 mbar_wait(smem_u32(&ctrl->ds_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+                 mbar_wait(smem_u32(&ctrl->dp_full), j & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tS = tmem_S + s * 128 + lane_off, tP = tmem_dP + lane_off;
-            const bool diag = j == qt;
-            const int col0 = j * FA_BKV;
-            uint8_t* dsrow = sdS + s * 2 * FA_TILE_BYTES + r * 128;
-#pragma unroll 1
-            for (int c = 2 * half; c < 2 * half + 2; ++c) {
-                uint32_t sv[32], dv[32];
-                tmem_ld_32x32(tS + c * 32, sv);
-                tmem_ld_32x32(tP + c * 32, dv);
-                tmem_ld_wait();
-                uint32_t packed[16];
+            const uint32_t tS = tmem_S + s * 128 + lane_off + half * 64, tP = tmem_dP + lane_off + half * 64;
+            // only the diagonal tile and the tiles that reach beyond the sequence need a mask
+            const bool masked = j == qt || (j + 1) * FA_BKV > p.T || (qt + 1) * FA_BQ > p.T;
+            const int col0 = j * FA_BKV + half * 64;
+            uint8_t* panel = sdS + s * 2 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
+            // This thread's 64 columns of dP come into registers at once and the (single) dP accumulator is handed
+            // back before any arithmetic: the tensor core forms dP of the next tile while this one is turned into dS.
+            uint32_t dv[64], sv[32];
+            tmem_ld_32x32(tP, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
+            tmem_ld_32x32(tP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+            tmem_ld_32x32(tS, sv);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->dp_empty));
+            // the tensor core must have finished reading this dS buffer (tile j - 2)
+            ok = mbar_wait(smem_u32(&ctrl->ds_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int col = col0 + c * 32 + e;
-                    float x0 = __uint_as_float(sv[e]) * p.scale_log2e - lse2, x1 = __uint_as_float(sv[e + 1]) * p.scale_log2e - lse2;
-                    if (diag) {
-                        if (col > row || col >= p.T) x0 = -INFINITY;
-                        if (col + 1 > row || col + 1 >= p.T) x1 = -INFINITY;
-                    }
-                    if (!row_ok) { x0 = -INFINITY; x1 = -INFINITY; }
-                    const float d0 = fa_exp2(x0) * (__uint_as_float(dv[e]) - delta);
-                    const float d1 = fa_exp2(x1) * (__uint_as_float(dv[e + 1]) - delta);
-                    packed[e >> 1] = pack_bf16x2(d0, d1);
+            for (int c = 0; c < 2; ++c) {
+                if (c == 1) {
+                    tmem_ld_32x32(tS + 32, sv);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
                 }
-                uint8_t* panel = dsrow + (c >> 1) * FA_TILE_BYTES;
+                uint32_t packed[16];
+                if (masked) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int col = col0 + c * 32 + e;
+                        float x0 = fmaf(__uint_as_float(sv[e]), p.scale_log2e, -lse2), x1 = fmaf(__uint_as_float(sv[e + 1]), p.scale_log2e, -lse2);
+                        if (col > row || col >= p.T || !row_ok) x0 = -INFINITY;
+                        if (col + 1 > row || col + 1 >= p.T || !row_ok) x1 = -INFINITY;
+                        packed[e >> 1] = pack_bf16x2(fa_exp2(x0) * (__uint_as_float(dv[c * 32 + e]) - delta),
+                                                     fa_exp2(x1) * (__uint_as_float(dv[c * 32 + e + 1]) - delta));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float x0 = fmaf(__uint_as_float(sv[e]), p.scale_log2e, -lse2), x1 = fmaf(__uint_as_float(sv[e + 1]), p.scale_log2e, -lse2);
+                        packed[e >> 1] = pack_bf16x2(fa_exp2(x0) * (__uint_as_float(dv[c * 32 + e]) - delta),
+                                                     fa_exp2(x1) * (__uint_as_float(dv[c * 32 + e + 1]) - delta));
+                    }
+                }
 #pragma unroll
                 for (int qd = 0; qd < 4; ++qd) {
-                    const int chunk = ((c & 1) * 4 + qd) ^ (r & 7);
+                    const int chunk = (c * 4 + qd) ^ (r & 7);
                     *reinterpret_cast<uint4*>(panel + chunk * 16) =
                         make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
                 }
             }
-            tc_fence_before();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&ctrl->s_empty[s]));
-                mbar_arrive(smem_u32(&ctrl->dp_empty));
-                mbar_arrive(smem_u32(&ctrl->ds_full[s]));
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->ds_full[s]));
         }
         if (ok) {
             ok = mbar_wait(smem_u32(&ctrl->dq_full), 0, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
@@ -802,58 +823,86 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int r = qrt * 32 + lane;
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
         bool ok = true;
+        // the row statistics of an iteration are fetched one iteration ahead, off the critical path
+        auto stats = [&](int it, float& lse2, float& delta) {
+            const int h = kvh * ratio + it / n_q, i = kt + it % n_q;
+            const int row = i * FA_BQ + r;
+            const long long stat_idx = (static_cast<long long>(b) * p.n_head + h) * p.T + row;
+            const bool row_ok = row < p.T;
+            lse2 = row_ok ? p.lse[stat_idx] * 1.4426950408889634f : 0.f;
+            delta = row_ok ? p.delta[stat_idx] : 0.f;
+        };
+        float lse2_next = 0.f, delta_next = 0.f;
+        if (n_it > 0) stats(0, lse2_next, delta_next);
         for (int it = 0; it < n_it && ok; ++it) {
             const int s = it & 1;
-            const int h = kvh * ratio + it / n_q, i = kt + it % n_q;
+            const int i = kt + it % n_q;
             const int row = i * FA_BQ + r;                      // query position of this thread in this iteration
             const bool row_ok = row < p.T;
-            const long long stat_idx = (static_cast<long long>(b) * p.n_head + h) * p.T + row;
-            const float lse2 = row_ok ? p.lse[stat_idx] * 1.4426950408889634f : 0.f;
-            const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+            const float lse2 = lse2_next, delta = delta_next;
+            if (it + 1 < n_it) stats(it + 1, lse2_next, delta_next);
             ok = mbar_wait(smem_u32(&ctrl->s_full[s]), (it >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
-                 mbar_wait(smem_u32(&ctrl->dp_full), it & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
-                 mbar_wait(smem_u32(&ctrl->pds_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+                 mbar_wait(smem_u32(&ctrl->dp_full), it & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tS = tmem_S + s * 128 + lane_off, tP = tmem_dP + lane_off;
-            const bool diag = i == kt;
-            const int col0 = kt * FA_BKV;
-            uint8_t* prow = sPdS + s * 4 * FA_TILE_BYTES + r * 128;
+            const uint32_t tS = tmem_S + s * 128 + lane_off + half * 64, tP = tmem_dP + lane_off + half * 64;
+            const bool masked = i == kt || (kt + 1) * FA_BKV > p.T || (i + 1) * FA_BQ > p.T;
+            const int col0 = kt * FA_BKV + half * 64;
+            uint8_t* prow = sPdS + s * 4 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
             uint8_t* dsrow = prow + 2 * FA_TILE_BYTES;
-#pragma unroll 1
-            for (int c = 2 * half; c < 2 * half + 2; ++c) {
-                uint32_t sv[32], dv[32];
-                tmem_ld_32x32(tS + c * 32, sv);
-                tmem_ld_32x32(tP + c * 32, dv);
-                tmem_ld_wait();
-                uint32_t pp[16], pd[16];
+            // as in the dQ kernel: dP into registers at once, its accumulator handed back before the arithmetic
+            uint32_t dv[64], sv[32];
+            tmem_ld_32x32(tP, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
+            tmem_ld_32x32(tP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+            tmem_ld_32x32(tS, sv);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->dp_empty));
+            ok = mbar_wait(smem_u32(&ctrl->pds_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int col = col0 + c * 32 + e;
-                    float x0 = __uint_as_float(sv[e]) * p.scale_log2e - lse2, x1 = __uint_as_float(sv[e + 1]) * p.scale_log2e - lse2;
-                    if ((diag && col > row) || col >= p.T || !row_ok) x0 = -INFINITY;
-                    if ((diag && col + 1 > row) || col + 1 >= p.T || !row_ok) x1 = -INFINITY;
-                    const float p0 = fa_exp2(x0), p1 = fa_exp2(x1);
-                    pp[e >> 1] = pack_bf16x2(p0, p1);
-                    pd[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[e]) - delta), p1 * (__uint_as_float(dv[e + 1]) - delta));
+            for (int c = 0; c < 2; ++c) {
+                if (c == 1) {
+                    tmem_ld_32x32(tS + 32, sv);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
                 }
-                const int poff = (c >> 1) * FA_TILE_BYTES;
+                uint32_t pp[16], pd[16];
+                if (masked) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int col = col0 + c * 32 + e;
+                        float x0 = fmaf(__uint_as_float(sv[e]), p.scale_log2e, -lse2), x1 = fmaf(__uint_as_float(sv[e + 1]), p.scale_log2e, -lse2);
+                        if (col > row || col >= p.T || !row_ok) x0 = -INFINITY;
+                        if (col + 1 > row || col + 1 >= p.T || !row_ok) x1 = -INFINITY;
+                        const float p0 = fa_exp2(x0), p1 = fa_exp2(x1);
+                        pp[e >> 1] = pack_bf16x2(p0, p1);
+                        pd[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[c * 32 + e]) - delta), p1 * (__uint_as_float(dv[c * 32 + e + 1]) - delta));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float p0 = fa_exp2(fmaf(__uint_as_float(sv[e]), p.scale_log2e, -lse2));
+                        const float p1 = fa_exp2(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2e, -lse2));
+                        pp[e >> 1] = pack_bf16x2(p0, p1);
+                        pd[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[c * 32 + e]) - delta), p1 * (__uint_as_float(dv[c * 32 + e + 1]) - delta));
+                    }
+                }
 #pragma unroll
                 for (int qd = 0; qd < 4; ++qd) {
-                    const int chunk = ((c & 1) * 4 + qd) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + poff + chunk * 16) = make_uint4(pp[4 * qd], pp[4 * qd + 1], pp[4 * qd + 2], pp[4 * qd + 3]);
-                    *reinterpret_cast<uint4*>(dsrow + poff + chunk * 16) = make_uint4(pd[4 * qd], pd[4 * qd + 1], pd[4 * qd + 2], pd[4 * qd + 3]);
+                    const int chunk = (c * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * qd], pp[4 * qd + 1], pp[4 * qd + 2], pp[4 * qd + 3]);
+                    *reinterpret_cast<uint4*>(dsrow + chunk * 16) = make_uint4(pd[4 * qd], pd[4 * qd + 1], pd[4 * qd + 2], pd[4 * qd + 3]);
                 }
             }
-            tc_fence_before();
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(smem_u32(&ctrl->s_empty[s]));
-                mbar_arrive(smem_u32(&ctrl->dp_empty));
-                mbar_arrive(smem_u32(&ctrl->pds_full[s]));
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->pds_full[s]));
         }
         if (ok) {
             ok = mbar_wait(smem_u32(&ctrl->dkv_full), 0, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);
