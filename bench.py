@@ -330,6 +330,42 @@ def run_ours(args):
             per.append(rec)
             if dominant is None or us > dominant["us"]:
                 dominant = dict(rec, flop=fl, N=b["N"], K=b["K"])
+    # ---- the same projections as their callers issue them: one grouped launch per direction for Q, K, V and for
+    # gate, up (attention.cu:597-599, 671-688; swiglu.cu:161-162, 197-208), beside the sum of the single products above
+    def time_graph(call, reps=10):
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                call()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(reps):
+                    call()
+            graph.replay()
+            side.synchronize()
+            e0.record(side)
+            graph.replay()
+            e1.record(side)
+            side.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    by_name = {b["name"]: b for b in bufs}
+    grouped = []
+    for names in (("q", "k", "v"), ("gate", "up")):
+        if not all(n in by_name for n in names):
+            continue
+        g = [by_name[n] for n in names]
+        Ns, K = [b["N"] for b in g], g[0]["K"]
+        x = g[0]["A"]
+        fl = sum(2.0 * TOKENS * n * K for n in Ns)
+        single = {kind: sum(r["us"] for r in per if r["proj"] in names and r["gemm"] == kind) for kind in ("fwd_nn", "dgrad_nt", "wgrad_tn")}
+        for kind, call in (
+                ("fwd_nn", lambda: pkg.gemm_grouped(h, pkg.FWD_NN, 0, [b["C"] for b in g], x, [b["B"] for b in g], TOKENS, Ns, K)),
+                ("dgrad_nt", lambda: pkg.gemm_grouped(h, pkg.DGRAD_NT, 0, g[0]["dA"], [b["dC"] for b in g], [b["B"] for b in g], TOKENS, Ns, K)),
+                ("wgrad_tn", lambda: pkg.gemm_grouped(h, pkg.WGRAD_TN, 1, [b["dB"] for b in g], x, [b["dC"] for b in g], TOKENS, Ns, K))):
+            us = time_graph(call)
+            grouped.append({"group": "+".join(names), "gemm": kind, "us": round(us, 2), "tflops": round(fl / us / 1e6, 1),
+                            "single_products_us": round(single[kind], 2)})
     h.sync()
     h.set_stream(torch.cuda.current_stream())
     in_step = None
@@ -363,7 +399,7 @@ def run_ours(args):
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "what": "A and dC of every projection copied from pinned host memory, 24 GEMMs through the C ABI, every dA read back"},
-            "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per}
+            "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per, "grouped_gemm": grouped}
     if in_step:
         line["in_step_us"] = in_step
     if vocab_parallel is not None:

@@ -118,6 +118,13 @@ int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, in
 int b200_linear_backward_bf16_grouped(b200_linear_ctx* ctx, int count, void* dA, int beta1_dA, void* const* dBs,
                                       const void* const* dCs, const void* A, const void* const* Bs, int M,
                                       const int* Ns, int K);
+/* The forward half of swiglu_forward (cuda/swiglu.cu:161-164) in one launch: gate[M, ff] = x[M, K] w_gate[K, ff],
+ * up = x w_up, hidden = SiLU(gate) * up, the last formed in the GEMM's epilogue from the bf16-rounded gate and up (the
+ * values the reference's element-wise kernel reads back from memory).  Returns B200_E_BADARG for shapes or pointers
+ * this kernel does not take (ff % 128 != 0, K % 8 != 0, pointers not 16-byte aligned, fewer than two SMs); the
+ * caller then uses b200_linear_gemm_bf16_grouped and its own element-wise pass. */
+int b200_linear_swiglu_forward_bf16(b200_linear_ctx* ctx, void* gate, void* up, void* hidden, const void* x,
+                                    const void* w_gate, const void* w_up, int M, int ff, int K);
 
 /* Tuning / introspection.  A plan is what the dispatcher would launch for a bf16 product:
  * tile width BN (output columns per tile; 0 = CUDA-core kernel), cta_pair (1 = 256-row tiles

@@ -801,6 +801,77 @@ int gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, voi
     return launch_beta<false, false>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
 }
 
+// gate = X W_gate, up = X W_up and hidden = SiLU(gate) * up in one launch: 256-wide pair tiles whose left half is 128
+// columns of gate and whose right half is the same 128 columns of up, hidden formed in the epilogue from the rounded
+// values.  B200_E_BADARG for shapes this kernel does not take (ff % 128, K % 8, alignment, fewer than two SMs): the
+// caller then issues the products and the element-wise kernel separately.
+int gemm_swiglu_fwd(b200_linear_ctx* ctx, void* gate, void* up, void* hidden, const void* x, const void* w_gate,
+                    const void* w_up, int M, int ff, int K) {
+    if (!ctx || !gate || !up || !hidden || !x || !w_gate || !w_up || M <= 0 || ff <= 0 || K <= 0) return B200_E_BADARG;
+    if (!on_context_device(ctx)) return B200_E_BADARG;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(hidden) |
+                           reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_gate) | reinterpret_cast<uintptr_t>(w_up);
+    if ((bits & 15) != 0 || (ff % 128) != 0 || (K % 8) != 0 || ctx->sm_count < 2 || ff > 0x3FFFFFFF) return B200_E_BADARG;
+    constexpr int bn = 256, ctas = 2;
+    // the schedule of an M x 2 ff product in whole 256 x 256 pair tiles, round-robin over the CTA pairs
+    const int max_slots = ctx->sm_count / ctas;
+    const Decomp d = decompose(M, 2 * ff, K, bn, ctas, max_slots, 1);
+    const int slots = d.dp_tiles < max_slots ? d.dp_tiles : max_slots;
+    GemmParams gp;
+    gp.Mo = M; gp.No = 2 * ff; gp.Kc = K;
+    gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
+    gp.m_fastest = M <= 2 * ff ? 1 : 0;
+    gp.group = 0;
+    gp.dp_tiles = d.dp_tiles; gp.sk_splits = 1; gp.kb_per_sk = d.kb_total; gp.sk_items = 0;
+    gp.sk_peer = 0; gp.late_wait = 0; gp.ksplit = 1;
+    gp.p_3d = 0; gp.q_3d = 1;
+    gp.grp_n[0] = gp.grp_n[1] = gp.grp_k[0] = gp.grp_k[1] = GRP_NONE;
+    gp.out = gate; gp.ws = nullptr; gp.sk_counters = nullptr; gp.status = ctx->status_dev;
+    const int grid = slots * ctas;
+    int rc;
+    CUtensorMap tmP, tmQg, tmQu, tmG, tmU, tmH;
+    rc = get_tensor_map(ctx, x, K, M, BK, BM, &tmP);
+    if (rc) return rc;
+    rc = get_panel_map(ctx, w_gate, ff, K, bn / ctas / 64, &tmQg);
+    if (rc) return rc;
+    rc = get_panel_map(ctx, w_up, ff, K, bn / ctas / 64, &tmQu);
+    if (rc) return rc;
+    rc = get_tensor_map(ctx, gate, ff, M, 64, 32, &tmG);
+    if (rc) return rc;
+    rc = get_tensor_map(ctx, up, ff, M, 64, 32, &tmU);
+    if (rc) return rc;
+    rc = get_tensor_map(ctx, hidden, ff, M, 64, 32, &tmH);
+    if (rc) return rc;
+    GemmGroupMaps gx = {};
+    gx.q[0] = tmQu;
+    gx.d[0] = tmU;
+    gx.d[1] = tmH;
+    using Cfg = TileCfg<bn, ctas>;
+    static bool configured[kMaxDevices] = {};
+    auto kern = gemm_bf16_sm100<bn, false, true, false, ctas, 1>;
+    if (!configured[ctx->device]) {
+        CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured[ctx->device] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQg, tmG, tmG, gx, gp));
+    ctx->launches++;
+    return B200_OK;
+}
+
 template <typename T, bool P_MN, bool Q_MN>
 int launch_simt_layout(b200_linear_ctx* ctx, const SimtParams& sp, bool vec) {
     dim3 grid(ceil_div_i(sp.No, ST_BN), ceil_div_i(sp.Mo, ST_BM), sp.splits);
@@ -1106,6 +1177,10 @@ extern "C" int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int bet
 extern "C" int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, void* const* outs,
                                              const void* const* xs, const void* const* ys, int M, const int* Ns, int K) {
     return gemm_bf16_grouped(ctx, which, beta1, count, outs, xs, ys, M, Ns, K);
+}
+extern "C" int b200_linear_swiglu_forward_bf16(b200_linear_ctx* ctx, void* gate, void* up, void* hidden, const void* x,
+                                               const void* w_gate, const void* w_up, int M, int ff, int K) {
+    return gemm_swiglu_fwd(ctx, gate, up, hidden, x, w_gate, w_up, M, ff, K);
 }
 extern "C" int b200_linear_backward_bf16_grouped(b200_linear_ctx* ctx, int count, void* dA, int beta1_dA, void* const* dBs,
                                                  const void* const* dCs, const void* A, const void* const* Bs, int M,

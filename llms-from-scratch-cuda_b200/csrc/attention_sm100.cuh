@@ -4,18 +4,23 @@
 // flash_attention_forward (cuda/kernels.cuh:420-427) and leaves empty (cuda/flash_attention.cu:12-17), and the
 // core of its attention_forward (cuda/attention.cu:419-461,603-615).  No [B, n_head, T, T] matrix exists.
 //
-// One CTA per (batch, query head, 128 query rows).  Per 128-row key/value tile:
-//   S  = Q K^T          tcgen05.mma 128 x 128 x 64, both operands K-major from 128B-swizzled TMA tiles, S in TMEM
-//   P  = exp2(S - max)  four softmax warps: thread i owns TMEM lane i = query row i, so the row maximum and the
-//                       row sum need no exchange between threads; P goes to shared memory as bf16 in the
-//                       K-major swizzled layout the tensor core reads
-//   PV = P V            tcgen05.mma 128 x 64 x 128, V as an MN-major operand (its rows are the contraction)
-// and the running output lives in registers: O = O * exp2(old max - new max) + PV (read back from TMEM).
-// S and PV are double-buffered in TMEM and P, K/V in shared memory, so the tensor core computes the next
-// tile's S and this tile's PV while the softmax warps work.
+// One CTA per (batch, query head, 128 query rows); blocks are dispatched longest first (the last query tile of every
+// head before anybody's first).  Per 128-row key/value tile:
+//   S    = Q K^T            tcgen05.mma 128 x 128 x 64, both operands K-major from 128B-swizzled TMA tiles, S in TMEM
+//   P_h  = exp2(S_h - m_h)  h = the two 64-column halves of the tile, each a softmax of its own: thread (row, h) owns
+//                           half a row of S (TMEM lane = query row), its reference maximum m_h and its row sum, so
+//                           nothing is exchanged between threads per tile; P goes to shared memory as bf16 in the
+//                           K-major swizzled layout the tensor core reads (one 64-column panel per half)
+//   O_h += P_h V_h          tcgen05.mma 128 x 64 x 64, V as an MN-major operand (its rows are the contraction),
+//                           accumulating in TMEM over all tiles
+// m_h follows the true maximum lazily: it moves, and O_h is rescaled in TMEM (tcgen05.ld, multiply, tcgen05.st), only
+// when the maximum has grown by more than 2^FA_RESCALE_STEP, so P stays below 2^8 and after the first tiles of a row the
+// rescale is rare.  After the last tile the halves are combined: O = (w_a O_a + w_b O_b) / (w_a l_a + w_b l_b) with
+// w_h = 2^(m_h - max(m_a, m_b)).  S is double-buffered in TMEM and P, K/V in shared memory, so the tensor core computes
+// the next tile's S and this tile's products while the softmax warps work.
 // Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4..11 = softmax + epilogue: warps w and w + 4 share
-// a TMEM lane quarter (32 query rows) and split its 128 key columns (and the 64 output columns) in halves, so that every
-// scheduler has two warps to interleave; the two threads of a row exchange their partial maxima through shared memory.
+// a TMEM lane quarter (32 query rows) and take one half each (and, in the epilogue, 32 of the 64 output columns), so
+// that every scheduler has two warps to interleave.
 // Every wait is bounded (ptx.cuh): on expiry the CTA records a code in *status and leaves.
 #pragma once
 #include <cuda_bf16.h>

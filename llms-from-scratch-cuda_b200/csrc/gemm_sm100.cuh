@@ -337,6 +337,65 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
     return true;
 }
 
+// SwiGLU forward in the epilogue (EPI = 1; 256-wide pair tiles): accumulator columns 0..127 are 128 columns of
+// gate = X W_gate, columns 128..255 the same 128 columns of up = X W_up.  Epilogue warp (q, hsel) owns rows
+// row0..row0+31 and 64-column chunk hsel of both: it rounds gate and up to bf16 (what the reference's two GEMMs
+// store), forms hidden = SiLU(gate) * up from the rounded values (cuda/swiglu.cu:132-140) and stores the three
+// 32 x 64 blocks through its two staging buffers (gate -> buffer 0, up -> buffer 1, hidden -> buffer 0 again).
+__device__ __forceinline__ float epi_sigmoid(float g) { return 1.0f / (1.0f + __expf(-g)); }
+__device__ __forceinline__ void epilogue_swiglu(const GemmParams& p, const CUtensorMap* tmGate, const CUtensorMap* tmUp,
+                                                const CUtensorMap* tmHidden, uint8_t* bufs, uint32_t taddr, int hsel,
+                                                int row0, int lane, int n0) {
+    if (elect_one()) tma_store_wait_read<0>();   // whatever this warp stored earlier has been read out of both buffers
+    __syncwarp();
+    const int col0 = n0 + hsel * 64;
+    uint8_t* buf_g = bufs;
+    uint8_t* buf_u = bufs + EPI_BUF_BYTES;
+    uint32_t hid[32];   // the 64 hidden values of this thread's row, packed
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        uint32_t g[32], u[32];
+        tmem_ld_32x32(taddr + hsel * 64 + half * 32, g);
+        tmem_ld_32x32(taddr + 128 + hsel * 64 + half * 32, u);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {   // 16-byte chunk 4 * half + j of the 128-byte row
+            uint32_t pg[4], pu[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                pg[e] = pack_bf16x2(__uint_as_float(g[8 * j + 2 * e]), __uint_as_float(g[8 * j + 2 * e + 1]));
+                pu[e] = pack_bf16x2(__uint_as_float(u[8 * j + 2 * e]), __uint_as_float(u[8 * j + 2 * e + 1]));
+                const float g0 = bf16_lo(pg[e]), g1 = bf16_hi(pg[e]);
+                hid[half * 16 + 4 * j + e] = pack_bf16x2(g0 * epi_sigmoid(g0) * bf16_lo(pu[e]), g1 * epi_sigmoid(g1) * bf16_hi(pu[e]));
+            }
+            const int off = lane * 128 + (((4 * half + j) ^ (lane & 7)) << 4);   // 128-byte swizzle
+            *reinterpret_cast<uint4*>(buf_g + off) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+            *reinterpret_cast<uint4*>(buf_u + off) = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+        }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    const bool store = row0 < p.Mo;
+    if (store && elect_one()) {
+        tma_store_2d(tmGate, smem_u32(buf_g), col0, row0);
+        tma_store_commit();
+        tma_store_2d(tmUp, smem_u32(buf_u), col0, row0);
+        tma_store_commit();
+        tma_store_wait_read<1>();   // the gate block has left buffer 0
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(buf_g + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(hid[4 * j], hid[4 * j + 1], hid[4 * j + 2], hid[4 * j + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (store && elect_one()) {
+        tma_store_2d(tmHidden, smem_u32(buf_g), col0, row0);
+        tma_store_commit();
+    }
+}
+
 // Write one 32 x 32 block (this warp's rows, one 32-column group) of fp32 sums as bf16 through the
 // warp's staging buffer (64-byte swizzle) and a TMA store.  beta = 1: `begin` (called before the
 // sums are formed) starts a TMA load of the old block into the same buffer, `finish` updates it in place.
@@ -613,7 +672,10 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
 // Warp roles: 0 = TMA producer for P, 3 = TMA producer for Q, 1 = MMA issuer (even CTA only in a
 // pair), 2 = TMEM allocator, 4..11 = epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 only, so warps w and
 // w+4 share a lane quarter and split its columns between them.
-template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
+// EPI = 1: the SwiGLU forward pair (see epilogue_swiglu): BN = 256, CTAS = 2, forward layout, whole tiles only.  The even
+// CTA of a pair feeds W_gate's columns (tmQ), the odd one the same columns of W_up (gx.q[0]); outputs: gate (tmD), up
+// (gx.d[0]), hidden (gx.d[1]); a tile index counts 128-column blocks of those three matrices.
+template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS, int EPI = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD32,
@@ -621,6 +683,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     using Cfg = TileCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr bool PAIR = CTAS == 2;
+    static_assert(EPI == 0 || (BN == 256 && CTAS == 2 && !P_MN && Q_MN && !BETA1), "SwiGLU epilogue: 256-wide pair tiles, forward");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -706,7 +769,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // L2 is the point of coherence for device memory, so a line fetched early is still current when the
     // copies into shared memory read it after the wait; inside the step the operands come from HBM (the
     // working set is far larger than L2) and this takes their first-touch latency off the critical path.
-    if ((warp == 0 || warp == 3) && have_first && !p.late_wait) {
+    if (EPI == 0 && (warp == 0 || warp == 3) && have_first && !p.late_wait) {
         if (elect_one()) {
             WorkItem w = w_first;
             narrow_to_krank(p, krank, w);
@@ -774,9 +837,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 int n_base;
-                const int gn = group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
+                const int gn = EPI ? static_cast<int>(rank) : group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
-                const int n0 = (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
+                const int n0 = EPI ? w.n_blk * Cfg::B_ROWS : (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
                         ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
@@ -914,7 +977,10 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     else mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
                 }
             };
-            if (p.ksplit > 1) {
+            if constexpr (EPI == 1) {
+                epilogue_swiglu(p, &tmD, &gx.d[0], &gx.d[1], my_buf, taddr, hsel, row0, lane, w.n_blk * 128);
+                release_acc();
+            } else if (p.ksplit > 1) {
                 ok = epilogue_cluster_split<BN, BETA1, CTAS>(p, ctrl, tiles, tmD32g, my_buf, taddr, q, hsel, lane, warp,
                                                              row0, col_tile, krank, static_cast<int>(rank), old_bar,
                                                              old_phase, abort_flag);

@@ -316,6 +316,13 @@ bool grouped_launches() {
     }();
     return on;
 }
+bool fused_swiglu() {   // B200_LINEAR_FUSED_SWIGLU=0: gate / up GEMMs and the element-wise kernel separately
+    static const bool on = [] {
+        const char* e = getenv("B200_LINEAR_FUSED_SWIGLU");
+        return !(e && atoi(e) == 0);
+    }();
+    return on;
+}
 template <typename T>
 int forward_group(b200_linear_ctx* ctx, int count, T* const* outs, const T* x, const T* const* ws, int M, const int* Ns, int K) {
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
@@ -443,6 +450,14 @@ int swiglu_fwd(b200_linear_ctx* ctx, T* out, T* gate, T* up, T* hidden, const T*
                const T* w_down, int BT, int C, int ff) {
     if (!ctx || !out || !gate || !up || !hidden || !inp || !w_gate || !w_up || !w_down || BT <= 0 || C <= 0 || ff <= 0)
         return B200_E_BADARG;
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        // gate, up and hidden from one launch (SiLU(gate) * up in the GEMM's epilogue) where the shapes allow
+        if (grouped_launches() && fused_swiglu()) {
+            const int rc = b200_linear_swiglu_forward_bf16(ctx, gate, up, hidden, inp, w_gate, w_up, BT, ff, C);
+            if (rc == B200_OK) return gemm(ctx, B200_GEMM_FWD_NN, 0, out, hidden, w_down, BT, C, ff);
+            if (rc != B200_E_BADARG) return rc;
+        }
+    }
     {   // swiglu.cu:161-162
         T* const outs[2] = {gate, up};
         const T* const ws[2] = {w_gate, w_up};

@@ -232,6 +232,13 @@ def matmul_backward_grouped(handle, dA, dBs, dCs, A, Bs, M, Ns, K, accumulate_dA
         _ptr_array(Bs) if Bs is not None else None, M, ns, K), "matmul_backward_grouped")
 
 
+def swiglu_forward_gemm(handle, gate, up, hidden, x, w_gate, w_up, M, ff, K):
+    """gate = x w_gate, up = x w_up, hidden = SiLU(gate) * up in one launch (b200_linear_swiglu_forward_bf16)."""
+    lib.b200_linear_swiglu_forward_bf16.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 3
+    handle._check(lib.b200_linear_swiglu_forward_bf16(handle._h, gate.data_ptr(), up.data_ptr(), hidden.data_ptr(), x.data_ptr(),
+                                                      w_gate.data_ptr(), w_up.data_ptr(), M, ff, K), "swiglu_forward_gemm")
+
+
 def plan_bf16(which, beta1, M, N, K, sm_count=148):
     p = Plan()
     rc = lib.b200_linear_plan_bf16(which, int(bool(beta1)), M, N, K, sm_count, ctypes.byref(p))

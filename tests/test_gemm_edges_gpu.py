@@ -423,3 +423,37 @@ def test_grouped_backward_matches_separate_calls(pkg, handle):
         da_sum += da1.double()
         assert _rel(db, db1.double()) <= 4e-3
     assert _rel(da, da_sum) <= 1e-2
+
+
+@pytest.mark.parametrize("M,ff,K", [(8192, 2048, 768), (1000, 384, 320), (130, 128, 64), (4096, 1024, 1024)])
+def test_swiglu_forward_in_the_gemm_epilogue(pkg, handle, M, ff, K):
+    """gate, up, hidden from one launch: gate and up equal the single-product results bit for bit (same tile arithmetic,
+    whole tiles), hidden equals SiLU(gate) * up formed from those bf16 values (float64 reference, one bf16 rounding)."""
+    g = torch.Generator(device=DEV).manual_seed(97531)
+    dt = torch.bfloat16
+    x = torch.randn(M, K, device=DEV, generator=g).to(dt)
+    wg = (torch.randn(K, ff, device=DEV, generator=g) / K ** 0.5).to(dt)
+    wu = (torch.randn(K, ff, device=DEV, generator=g) / K ** 0.5).to(dt)
+    gate, up, hidden = (torch.full((M, ff), float("nan"), device=DEV, dtype=dt) for _ in range(3))
+    pkg.swiglu_forward_gemm(handle, gate, up, hidden, x, wg, wu, M, ff, K)
+    handle.sync()
+    assert _rel(gate, x.double() @ wg.double()) <= 1e-2 and _rel(up, x.double() @ wu.double()) <= 1e-2
+    g1, u1 = torch.empty_like(gate), torch.empty_like(up)
+    pkg.gemm(handle, pkg.FWD_NN, 0, g1, x, wg, M, ff, K)
+    pkg.gemm(handle, pkg.FWD_NN, 0, u1, x, wu, M, ff, K)
+    handle.sync()
+    assert _rel(gate, g1.double()) <= 4e-3 and _rel(up, u1.double()) <= 4e-3
+    g64, u64 = gate.double(), up.double()
+    want = g64 * torch.sigmoid(g64) * u64
+    assert _rel(hidden, want) <= 4e-3
+    # one bf16 rounding of the float64 value, up to the fast exponential: at most one unit in the last place
+    ulp = (hidden.double() - want).abs() / want.abs().clamp_min(1e-30)
+    assert ulp[want.abs() > 1e-3].max().item() <= 2 ** -7
+
+
+def test_swiglu_forward_gemm_refuses_what_it_cannot_tile(pkg, handle):
+    x = torch.zeros(64, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(64, 72, device=DEV, dtype=torch.bfloat16)
+    o = torch.zeros(64, 72, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(pkg.LinearError):
+        pkg.swiglu_forward_gemm(handle, o, o.clone(), o.clone(), x, w, w, 64, 72, 64)
