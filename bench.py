@@ -368,6 +368,35 @@ def run_ours(args):
                             "single_products_us": round(single[kind], 2)})
     h.sync()
     h.set_stream(torch.cuda.current_stream())
+    # ---- the same 24 products as this library's layer functions issue them: Q, K, V and gate, up of one input as one
+    # grouped launch per direction (16 launches in all).  Not the headline: `value` keeps one call per product, which is
+    # what the other arm's interface offers.
+    step_grouped = None
+    if all(n in by_name for n in ("q", "k", "v", "gate", "up")):
+        groups = [[by_name[n] for n in ("q", "k", "v")], [by_name[n] for n in ("gate", "up")]]
+        rest = [b for b in bufs if b["name"] not in ("q", "k", "v", "gate", "up")]
+
+        def step_device_grouped():
+            for g in groups:
+                pkg.gemm_grouped(h, pkg.FWD_NN, 0, [b["C"] for b in g], g[0]["A"], [b["B"] for b in g], TOKENS, [b["N"] for b in g], g[0]["K"])
+            for b in rest:
+                pkg.matmul_forward(h, b["C"], b["A"], b["B"], TOKENS, b["N"], b["K"])
+            for b in reversed(rest):
+                pkg.matmul_backward(h, b["dA"], b["dB"], b["dC"], b["A"], b["B"], TOKENS, b["N"], b["K"])
+            for g in reversed(groups):
+                pkg.matmul_backward_grouped(h, g[0]["dA"], [b["dB"] for b in g], [b["dC"] for b in g], g[0]["A"],
+                                            [b["B"] for b in g], TOKENS, [b["N"] for b in g], g[0]["K"])
+
+        for _ in range(max(3, args.warmup)):
+            step_device_grouped()
+        torch.cuda.synchronize()
+        preheat(torch, step_device_grouped)
+        gms = median(time_blocks(torch, step_device_grouped, args.steps))
+        h.sync()
+        step_grouped = {"ms_per_step": round(gms / args.steps, 4), "tflops": round(args.steps * STEP_FLOP / (gms * 1e-3) / 1e12, 2),
+                        "launches_per_step": 16,
+                        "what": "the same 24 products with Q, K, V and gate, up of one input issued as grouped launches "
+                                "(b200_linear_gemm_bf16_grouped / _backward_bf16_grouped), rank 0, no gradient exchange"}
     in_step = None
     if args.breakdown:
         calls = [(b["name"] + ":fwd", (lambda b=b: pkg.matmul_forward(h, b["C"], b["A"], b["B"], TOKENS, b["N"], b["K"]))) for b in bufs]
@@ -399,7 +428,7 @@ def run_ours(args):
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "what": "A and dC of every projection copied from pinned host memory, 24 GEMMs through the C ABI, every dA read back"},
-            "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per, "grouped_gemm": grouped}
+            "roofline": roofline, "cpu_baseline": cpu, "per_gemm": per, "grouped_gemm": grouped, "step_grouped": step_grouped}
     if in_step:
         line["in_step_us"] = in_step
     if vocab_parallel is not None:
@@ -427,10 +456,14 @@ def run_vocab_parallel(torch, dist, pkg, h, dev, world, rank):
     rows, V, K = 16384, 128256, 768
     shards = dmod.vocab_shards(V, world)
 
-    def lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange):
+    def lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange, fused_stats=True):
         n_rows = x.shape[0]
-        pkg.gemm_ld(h, pkg.FWD_NN, 0, logits, x, w[:, col0:col0 + cols], n_rows, cols, x.shape[1])
-        loss, d = dmod.vocab_parallel_cross_entropy(logits, targets, col0, in_place=True, exchange=exchange)
+        if fused_stats:   # row maximum / sum of exponentials / target logit from the forward GEMM's epilogue
+            stats = pkg.forward_ce_stats(h, logits, x, w[:, col0:col0 + cols], n_rows, cols, x.shape[1], targets, col0)
+        else:             # the same from a pass over the stored logits
+            pkg.gemm_ld(h, pkg.FWD_NN, 0, logits, x, w[:, col0:col0 + cols], n_rows, cols, x.shape[1])
+            stats = None
+        loss, d = dmod.vocab_parallel_cross_entropy(logits, targets, col0, in_place=True, exchange=exchange, stats=stats)
         pkg.gemm_ld(h, pkg.DGRAD_NT, 0, dx, d, w[:, col0:col0 + cols], n_rows, cols, x.shape[1])
         pkg.gemm_ld(h, pkg.WGRAD_TN, 1, dw[:, col0:col0 + cols], x, d, n_rows, cols, x.shape[1])
         if exchange:
@@ -478,16 +511,16 @@ def run_vocab_parallel(torch, dist, pkg, h, dev, world, rank):
     dx = torch.empty(rows, K, device=dev, dtype=torch.bfloat16)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def timed(col0, cols, exchange, reps=5):
+    def timed(col0, cols, exchange, reps=5, fused_stats=True):
         logits = torch.empty(rows, cols, device=dev, dtype=torch.bfloat16)
         for _ in range(2):
-            lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange)
+            lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange, fused_stats)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         e0.record()
         for _ in range(reps):
-            lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange)
+            lm_head(x, w, dw, targets, logits, dx, col0, cols, exchange, fused_stats)
         e1.record()
         if world > 1:
             dist.barrier()
@@ -503,6 +536,7 @@ def run_vocab_parallel(torch, dist, pkg, h, dev, world, rank):
     col0, cols = shards[rank]
     ms = timed(col0, cols, True)
     n1_ms = ms if world == 1 else timed(0, V, False, reps=3)
+    ms_separate = timed(col0, cols, True, fused_stats=False)   # statistics by a pass of their own over the logits
     h.sync()
     flop = 3 * 2.0 * rows * V * K
     rec = {"workload": "configs[3] LM head: 16384 tokens x 128256 vocabulary x 768, forward + cross-entropy + dgrad + wgrad(beta=1), "
@@ -512,7 +546,11 @@ def run_vocab_parallel(torch, dist, pkg, h, dev, world, rank):
            "columns_per_rank": [n for _, n in shards],
            "exchange_bytes_per_rank": {"all_reduce_max_fp32": rows * 4, "all_reduce_sum_fp32": 2 * rows * 4,
                                        "all_reduce_dx_bf16": rows * K * 2},
-           "logits_bytes_per_rank": rows * cols * 2}
+           "logits_bytes_per_rank": rows * cols * 2,
+           "ms_with_separate_statistics_pass": round(ms_separate, 3),
+           "what": "row maximum, sum of exponentials and target logit come out of the forward GEMM's epilogue "
+                   "(b200_linear_forward_ce_stats_bf16); ms_with_separate_statistics_pass is the same step with "
+                   "b200_ce_shard_stats_bf16 reading the stored logits instead"}
     rec.update(parity)
     return rec
 

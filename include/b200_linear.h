@@ -118,6 +118,19 @@ int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, in
 int b200_linear_backward_bf16_grouped(b200_linear_ctx* ctx, int count, void* dA, int beta1_dA, void* const* dBs,
                                       const void* const* dCs, const void* A, const void* const* Bs, int M,
                                       const int* Ns, int K);
+/* The LM head and the first pass of its cross-entropy in one GEMM (llama2-mistral/src/model.cpp:612-613,
+ * cuda/crossentropy.cu:96-110): logits[M, N] = x[M, K] w[K, N] stored as bf16 (row pitches ld_* in elements, 0 = dense:
+ * a vocabulary shard of w_out where it lies) and, per row, the maximum, sum exp(l - max) and the target's logit over
+ * these N columns (global columns col0 .. col0 + N - 1; row_target = 0 when the target lives elsewhere) -- the
+ * outputs of b200_ce_shard_stats_bf16, formed in the GEMM's epilogue from the rounded logits while they are in
+ * registers instead of by a pass over the stored matrix (one read of M x N x 2 bytes less).  Continue with
+ * b200_ce_shard_rescale / _loss / _backward_bf16.  B200_E_BADARG for operands the tensor-core kernel cannot take
+ * (N, K, pitches not multiples of 8, pointers not 16-byte aligned): use b200_linear_gemm_bf16_ld and
+ * b200_ce_shard_stats_bf16 then.  Asynchronous on the context's stream. */
+int b200_linear_forward_ce_stats_bf16(b200_linear_ctx* ctx, void* logits, long long ld_out, const void* x, long long ld_x,
+                                      const void* w, long long ld_w, int M, int N, int K, const int* targets, int col0,
+                                      float* row_max, float* row_sum, float* row_target);
+
 /* The forward half of swiglu_forward (cuda/swiglu.cu:161-164) in one launch: gate[M, ff] = x[M, K] w_gate[K, ff],
  * up = x w_up, hidden = SiLU(gate) * up, the last formed in the GEMM's epilogue from the bf16-rounded gate and up (the
  * values the reference's element-wise kernel reads back from memory).  Returns B200_E_BADARG for shapes or pointers

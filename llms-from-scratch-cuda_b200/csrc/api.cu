@@ -872,6 +872,83 @@ int gemm_swiglu_fwd(b200_linear_ctx* ctx, void* gate, void* up, void* hidden, co
     return B200_OK;
 }
 
+// The LM-head forward of a (vocabulary shard of a) model together with the cross-entropy statistics of its rows:
+// logits[M, N] = x[M, K] w[K, N] stored as bf16, and per row the maximum, sum exp(l - max) and the target's logit of
+// those N columns (global columns col0 .. col0 + N) -- what b200_ce_shard_stats_bf16 computes in a pass of its own over
+// the stored logits.  The GEMM's epilogue forms (max, sum) per row and tile from the rounded values while they are in
+// registers (gemm_sm100.cuh, EPI = 2); ce_merge_partials merges a row's pairs.  Operands may be pitched.
+int forward_ce_stats(b200_linear_ctx* ctx, void* logits, long long ld_out, const void* x, long long ld_x, const void* w,
+                     long long ld_w, int M, int N, int K, const int* targets, int col0, float* row_max, float* row_sum,
+                     float* row_target) {
+    if (!ctx || !logits || !x || !w || !targets || !row_max || !row_sum || !row_target || M <= 0 || N <= 0 || K <= 0 || col0 < 0)
+        return B200_E_BADARG;
+    if (!on_context_device(ctx)) return B200_E_BADARG;
+    if (ld_out == 0) ld_out = N;
+    if (ld_x == 0) ld_x = K;
+    if (ld_w == 0) ld_w = N;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w);
+    if ((bits & 15) != 0 || (N % 8) != 0 || (K % 8) != 0 || ((ld_out | ld_x | ld_w) % 8) != 0 || ld_out < N || ld_x < K || ld_w < N ||
+        ctx->sm_count < 2)
+        return B200_E_BADARG;
+    constexpr int bn = 256, ctas = 2;
+    const int max_slots = ctx->sm_count / ctas;
+    const Decomp d = decompose(M, N, K, bn, ctas, max_slots, 1);
+    const int slots = d.dp_tiles < max_slots ? d.dp_tiles : max_slots;
+    const int np = 2 * d.n_tiles;
+    int rc = ensure_workspace(ctx, static_cast<size_t>(M) * np * sizeof(float2), 0);
+    if (rc) return rc;
+    GemmParams gp;
+    gp.Mo = M; gp.No = N; gp.Kc = K;
+    gp.m_tiles = d.m_tiles; gp.n_tiles = d.n_tiles; gp.kb_total = d.kb_total;
+    gp.m_fastest = M <= N ? 1 : 0;
+    gp.group = 0;
+    gp.dp_tiles = d.dp_tiles; gp.sk_splits = 1; gp.kb_per_sk = d.kb_total; gp.sk_items = 0;
+    gp.sk_peer = 0; gp.late_wait = 0; gp.ksplit = 1;
+    gp.p_3d = 0; gp.q_3d = (N % 64) == 0 ? 1 : 0;
+    gp.grp_n[0] = gp.grp_n[1] = gp.grp_k[0] = gp.grp_k[1] = GRP_NONE;
+    gp.out = logits; gp.ws = ctx->ws; gp.sk_counters = nullptr; gp.status = ctx->status_dev;
+    CUtensorMap tmP, tmQ, tmD;
+    rc = get_tensor_map(ctx, x, K, M, BK, BM, &tmP, ld_x == K ? 0 : ld_x);
+    if (rc) return rc;
+    if (gp.q_3d) rc = get_panel_map(ctx, w, N, K, bn / ctas / 64, &tmQ, ld_w == N ? 0 : ld_w);
+    else rc = get_tensor_map(ctx, w, N, K, 64, BK, &tmQ, ld_w == N ? 0 : ld_w);
+    if (rc) return rc;
+    rc = get_tensor_map(ctx, logits, N, M, 64, 32, &tmD, ld_out == N ? 0 : ld_out);
+    if (rc) return rc;
+    using Cfg = TileCfg<bn, ctas>;
+    static bool configured[kMaxDevices] = {};
+    auto kern = gemm_bf16_sm100<bn, false, true, false, ctas, 2>;
+    if (!configured[ctx->device]) {
+        CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured[ctx->device] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(slots * ctas, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = ctx->use_pdl ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    CU_TRY(ctx, cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, tmD, tmD, g_no_group, gp));
+    ctx->launches++;
+    const int rows_per_cta = b200::CE_THREADS / 32;
+    const int want = (M + rows_per_cta - 1) / rows_per_cta;
+    const int grid = want < ctx->sm_count * 8 ? want : ctx->sm_count * 8;
+    b200::ce_merge_partials<<<grid, b200::CE_THREADS, 0, ctx->stream>>>(reinterpret_cast<const float2*>(ctx->ws), np,
+                                                                      static_cast<const __nv_bfloat16*>(logits), M, N, ld_out, targets,
+                                                                      col0, row_max, row_sum, row_target);
+    CU_TRY(ctx, cudaGetLastError());
+    ctx->launches++;
+    return B200_OK;
+}
+
 template <typename T, bool P_MN, bool Q_MN>
 int launch_simt_layout(b200_linear_ctx* ctx, const SimtParams& sp, bool vec) {
     dim3 grid(ceil_div_i(sp.No, ST_BN), ceil_div_i(sp.Mo, ST_BM), sp.splits);
@@ -1177,6 +1254,12 @@ extern "C" int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int bet
 extern "C" int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, void* const* outs,
                                              const void* const* xs, const void* const* ys, int M, const int* Ns, int K) {
     return gemm_bf16_grouped(ctx, which, beta1, count, outs, xs, ys, M, Ns, K);
+}
+extern "C" int b200_linear_forward_ce_stats_bf16(b200_linear_ctx* ctx, void* logits, long long ld_out, const void* x,
+                                                 long long ld_x, const void* w, long long ld_w, int M, int N, int K,
+                                                 const int* targets, int col0, float* row_max, float* row_sum,
+                                                 float* row_target) {
+    return forward_ce_stats(ctx, logits, ld_out, x, ld_x, w, ld_w, M, N, K, targets, col0, row_max, row_sum, row_target);
 }
 extern "C" int b200_linear_swiglu_forward_bf16(b200_linear_ctx* ctx, void* gate, void* up, void* hidden, const void* x,
                                                const void* w_gate, const void* w_up, int M, int ff, int K) {

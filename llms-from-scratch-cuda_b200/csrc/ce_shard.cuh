@@ -114,6 +114,35 @@ ce_shard_stats_bf16(const __nv_bfloat16* __restrict__ logits, int rows, int cols
     }
 }
 
+// The same three outputs from the (max, sum) pairs that the LM-head GEMM left per row and tile (gemm_sm100.cuh,
+// epilogue_store_stats): one warp per row merges the row's `np` pairs; the logits are touched only for the target.
+__global__ void __launch_bounds__(CE_THREADS)
+ce_merge_partials(const float2* __restrict__ partials, int np, const __nv_bfloat16* __restrict__ logits, int rows, int cols,
+                  long long ld, const int* __restrict__ targets, int col0, float* __restrict__ row_max,
+                  float* __restrict__ row_sum, float* __restrict__ row_tgt) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = CE_THREADS / 32;
+    for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
+        const float2* row = partials + static_cast<long long>(r) * np;
+        float m = -INFINITY, s = 0.f;
+        for (int i = lane; i < np; i += 32) {
+            const float2 v = row[i];
+            ce_online_merge(m, s, v.x, v.y);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+            ce_online_merge(m, s, m2, s2);
+        }
+        if (lane == 0) {
+            row_max[r] = m;
+            row_sum[r] = s;
+            const int t = targets[r] - col0;
+            row_tgt[r] = (t >= 0 && t < cols) ? __bfloat162float(logits[static_cast<long long>(r) * ld + t]) : 0.f;
+        }
+    }
+}
+
 // s_r *= exp(m_r - m): this rank's sum re-based to the global maximum (an empty shard has m_r = -inf, s_r = 0).
 __global__ void ce_shard_rescale(const float* __restrict__ local_max, const float* __restrict__ global_max,
                                  float* __restrict__ row_sum, int rows) {

@@ -337,6 +337,72 @@ __device__ __forceinline__ bool epilogue_store_bf16(const GemmParams& p, const C
     return true;
 }
 
+// LM-head forward with the cross-entropy statistics in the epilogue (EPI = 2; 256-wide tiles, whole tiles only): the
+// tile is stored as bf16 like any other, and while its rows are in registers each epilogue warp also forms, over the
+// columns it owns of the tile (chunks hsel and hsel + 2: 128 of the 256) and from the bf16-rounded values (what a
+// separate pass over the stored logits would read), the row maximum m and s = sum exp(l - m).  One (m, s) pair per
+// row, tile and hsel goes to stats[row][2 * n_blk + hsel]; a small kernel merges a row's pairs (ce_merge_partials).
+// Columns at or beyond p.No count as -inf.
+template <int NBUF>
+__device__ __forceinline__ void epilogue_store_stats(const GemmParams& p, const CUtensorMap* tmD, uint8_t* bufs, uint32_t taddr,
+                                                     int hsel, int row0, int lane, int n0, int n_blk) {
+    constexpr float L2E = 1.4426950408889634f;
+    if constexpr (NBUF == 2) {
+        if (elect_one()) tma_store_wait_read<0>();
+        __syncwarp();
+    }
+    float m = -INFINITY, ssum = 0.f;
+    int sel = 0;
+#pragma unroll 1
+    for (int c = hsel; c < 4; c += 2) {
+        const int col0 = n0 + c * 64;
+        if (col0 >= p.No) break;  // whole chunk beyond the matrix (warp-uniform)
+        uint8_t* buf = bufs + sel * EPI_BUF_BYTES;
+        sel ^= NBUF - 1;
+        uint32_t r[64];
+        tmem_ld_32x32(taddr + c * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld_32x32(taddr + c * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
+        if (elect_one()) tma_store_wait_read<NBUF - 1>();   // the warp's last store from this buffer has been read out
+        __syncwarp();
+        uint32_t pk[32];
+        float cm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            pk[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            const float lo = (col0 + 2 * j < p.No) ? bf16_lo(pk[j]) : -INFINITY;
+            const float hi = (col0 + 2 * j + 1 < p.No) ? bf16_hi(pk[j]) : -INFINITY;
+            cm = fmaxf(cm, fmaxf(lo, hi));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (row0 < p.Mo && elect_one()) {
+            tma_store_2d(tmD, smem_u32(buf), col0, row0);
+            tma_store_commit();
+        }
+        const float mn = fmaxf(m, cm);
+        if (mn != -INFINITY) {   // a row with nothing finite so far keeps (m, s) = (-inf, 0)
+            const float base = mn * L2E;
+            float acc4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float lo = (col0 + 2 * j < p.No) ? bf16_lo(pk[j]) : -INFINITY;
+                const float hi = (col0 + 2 * j + 1 < p.No) ? bf16_hi(pk[j]) : -INFINITY;
+                acc4[j & 3] += exp2f(fmaf(lo, L2E, -base)) + exp2f(fmaf(hi, L2E, -base));
+            }
+            ssum = ssum * exp2f(fmaf(m, L2E, -base)) + (acc4[0] + acc4[1]) + (acc4[2] + acc4[3]);   // m = -inf: ssum * 0
+            m = mn;
+        }
+    }
+    const int row = row0 + lane;
+    if (row < p.Mo)
+        reinterpret_cast<float2*>(p.ws)[static_cast<size_t>(row) * (2 * p.n_tiles) + 2 * n_blk + hsel] = make_float2(m, ssum);
+}
+
 // SwiGLU forward in the epilogue (EPI = 1; 256-wide pair tiles): accumulator columns 0..127 are 128 columns of
 // gate = X W_gate, columns 128..255 the same 128 columns of up = X W_up.  Epilogue warp (q, hsel) owns rows
 // row0..row0+31 and 64-column chunk hsel of both: it rounds gate and up to bf16 (what the reference's two GEMMs
@@ -675,6 +741,7 @@ __device__ __forceinline__ bool epilogue_peer_split(const GemmParams& p, GemmCtr
 // EPI = 1: the SwiGLU forward pair (see epilogue_swiglu): BN = 256, CTAS = 2, forward layout, whole tiles only.  The even
 // CTA of a pair feeds W_gate's columns (tmQ), the odd one the same columns of W_up (gx.q[0]); outputs: gate (tmD), up
 // (gx.d[0]), hidden (gx.d[1]); a tile index counts 128-column blocks of those three matrices.
+// EPI = 2: the LM-head forward that also leaves per-tile cross-entropy statistics in p.ws (see epilogue_store_stats).
 template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS, int EPI = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
@@ -683,7 +750,8 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     using Cfg = TileCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr bool PAIR = CTAS == 2;
-    static_assert(EPI == 0 || (BN == 256 && CTAS == 2 && !P_MN && Q_MN && !BETA1), "SwiGLU epilogue: 256-wide pair tiles, forward");
+    static_assert(EPI != 1 || (BN == 256 && CTAS == 2 && !P_MN && Q_MN && !BETA1), "SwiGLU epilogue: 256-wide pair tiles, forward");
+    static_assert(EPI != 2 || (BN == 256 && !P_MN && Q_MN && !BETA1), "cross-entropy statistics: 256-wide tiles, forward");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -769,7 +837,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     // L2 is the point of coherence for device memory, so a line fetched early is still current when the
     // copies into shared memory read it after the wait; inside the step the operands come from HBM (the
     // working set is far larger than L2) and this takes their first-touch latency off the critical path.
-    if (EPI == 0 && (warp == 0 || warp == 3) && have_first && !p.late_wait) {
+    if (EPI != 1 && (warp == 0 || warp == 3) && have_first && !p.late_wait) {
         if (elect_one()) {
             WorkItem w = w_first;
             narrow_to_krank(p, krank, w);
@@ -837,9 +905,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 int n_base;
-                const int gn = EPI ? static_cast<int>(rank) : group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
+                const int gn = EPI == 1 ? static_cast<int>(rank) : group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
-                const int n0 = EPI ? w.n_blk * Cfg::B_ROWS : (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
+                const int n0 = EPI == 1 ? w.n_blk * Cfg::B_ROWS : (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     if (!__all_sync(0xffffffffu, ready)) {
                         ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, p.status,
@@ -979,6 +1047,9 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             };
             if constexpr (EPI == 1) {
                 epilogue_swiglu(p, &tmD, &gx.d[0], &gx.d[1], my_buf, taddr, hsel, row0, lane, w.n_blk * 128);
+                release_acc();
+            } else if constexpr (EPI == 2) {
+                epilogue_store_stats<Cfg::EPI_BUFS>(p, &tmD, my_buf, taddr, hsel, row0, lane, w.n_blk * BN, w.n_blk);
                 release_acc();
             } else if (p.ksplit > 1) {
                 ok = epilogue_cluster_split<BN, BETA1, CTAS>(p, ctrl, tiles, tmD32g, my_buf, taddr, q, hsel, lane, warp,

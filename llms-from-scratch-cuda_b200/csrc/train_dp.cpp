@@ -15,8 +15,8 @@
 //    tiles; rank r owns columns [col0_r, col0_r + V_r) and multiplies by them where they lie (row pitch V,
 //    b200_linear_gemm_bf16_ld).  The R micro-batches that run at the same time form a round: the ranks
 //    gather their final hidden states [R*BT, C], every rank computes the logits of all R*BT tokens for its
-//    columns, the cross-entropy's row maximum and sum of exponentials are combined with two small
-//    all-reduces (b200_ce_shard_* kernels), dlogits is formed in place, the weight gradient lands in the
+//    columns (b200_linear_forward_ce_stats_bf16: the rows' maximum and sum of exponentials come out of that GEMM's
+//    epilogue), these are combined with two small all-reduces (b200_ce_shard_* kernels), dlogits is formed in place, the weight gradient lands in the
 //    rank's own columns of dw_out, and the input gradient [R*BT, C] is reduce-scattered back so that every
 //    rank continues the backward pass of its own micro-batch.  No rank ever holds a whole row of logits.
 //    This replaces llama2-mistral/src/model.cpp:612-614 (LM-head GEMM, crossentropy_forward) and :634-635
@@ -231,9 +231,17 @@ bool vp_lm_head_round(VocabParallel& vp, ModelBF16& m, const int* targets, const
         CUDA_TRY(cudaMemcpy(vp.targets_all, targets, static_cast<size_t>(BT) * sizeof(int), cudaMemcpyDeviceToDevice));
     }
     // logits_r = x_all * w_out[:, col0 : col0 + cols]
-    B200_TRY(b200_linear_gemm_bf16_ld(vp.ctx, B200_GEMM_FWD_NN, 0, logits, vp.cols, vp.x_all, C, m.w_out + vp.col0, V, rows,
-                                      vp.cols, C));
-    B200_TRY(b200_ce_shard_stats_bf16(logits, rows, vp.cols, vp.cols, vp.targets_all, vp.col0, lmax, sum, tgt, nullptr));
+    // with the rows' maxima, sums of exponentials and target logits formed in the GEMM's epilogue; where the operands
+    // do not suit that kernel: the plain product, then a pass over the stored logits
+    const int fused_rc = b200_linear_forward_ce_stats_bf16(vp.ctx, logits, vp.cols, vp.x_all, C, m.w_out + vp.col0, V, rows, vp.cols,
+                                                           C, vp.targets_all, vp.col0, lmax, sum, tgt);
+    if (fused_rc == B200_E_BADARG) {
+        B200_TRY(b200_linear_gemm_bf16_ld(vp.ctx, B200_GEMM_FWD_NN, 0, logits, vp.cols, vp.x_all, C, m.w_out + vp.col0, V, rows,
+                                          vp.cols, C));
+        B200_TRY(b200_ce_shard_stats_bf16(logits, rows, vp.cols, vp.cols, vp.targets_all, vp.col0, lmax, sum, tgt, nullptr));
+    } else {
+        B200_TRY(fused_rc);
+    }
     CUDA_TRY(cudaMemcpyAsync(gmax, lmax, static_cast<size_t>(rows) * sizeof(float), cudaMemcpyDeviceToDevice, 0));
     if (R > 1) NCCL_TRY(ncclAllReduce(gmax, gmax, static_cast<size_t>(rows), ncclFloat, ncclMax, comm, 0));
     B200_TRY(b200_ce_shard_rescale(lmax, gmax, sum, rows, nullptr));

@@ -96,7 +96,7 @@ class CudaShardOps:
 
 
 def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None, ops=CudaShardOps, in_place=False,
-                                 exchange=True):
+                                 exchange=True, stats=None):
     """Cross-entropy over a vocabulary that is split across ranks.
 
     logits_local [BT, V_r] (bf16) are this rank's columns [vocab_start, vocab_start + V_r) of the LM-head
@@ -107,10 +107,12 @@ def vocab_parallel_cross_entropy(logits_local, targets, vocab_start, group=None,
     `ops` supplies the four per-shard steps: this library's CUDA kernels unless a test passes a host
     restatement to exercise the exchange without a GPU.  in_place=True writes dlogits over the logits (the
     CUDA kernels allow it; no second [BT, V_r] buffer).  exchange=False treats the local columns as the
-    whole vocabulary even inside a process group (a single-GPU baseline run on every rank)."""
+    whole vocabulary even inside a process group (a single-GPU baseline run on every rank).
+    stats = (row_max, row_sum, row_target) of the local columns when the LM-head GEMM has already formed them in its
+    epilogue (linear.forward_ce_stats): the pass over the logits that computes them is then skipped."""
     bt = logits_local.shape[0]
     multi = exchange and dist.is_initialized() and dist.get_world_size(group) > 1
-    local_max, row_sum, tgt = ops.stats(logits_local, targets, vocab_start)
+    local_max, row_sum, tgt = stats if stats is not None else ops.stats(logits_local, targets, vocab_start)
     global_max = local_max.clone()
     if multi:
         dist.all_reduce(global_max, op=dist.ReduceOp.MAX, group=group)

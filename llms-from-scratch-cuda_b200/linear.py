@@ -232,6 +232,22 @@ def matmul_backward_grouped(handle, dA, dBs, dCs, A, Bs, M, Ns, K, accumulate_dA
         _ptr_array(Bs) if Bs is not None else None, M, ns, K), "matmul_backward_grouped")
 
 
+def forward_ce_stats(handle, logits, x, w, M, N, K, targets, col0):
+    """logits = x w (bf16; torch views with a row pitch allowed, as in gemm_ld) and, from the GEMM's epilogue, the
+    cross-entropy statistics of the N local columns: returns (row_max, row_sum, row_target) fp32 [M], the outputs of
+    ce_shard_stats without its pass over the stored logits (b200_linear_forward_ce_stats_bf16)."""
+    import torch
+    (po, lo), (px, lx), (pw, lw) = _ptr_ld(logits), _ptr_ld(x), _ptr_ld(w)
+    out = [torch.empty(M, device=logits.device, dtype=torch.float32) for _ in range(3)]
+    ll = ctypes.c_longlong
+    lib.b200_linear_forward_ce_stats_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ll, ctypes.c_void_p, ll, ctypes.c_void_p, ll,
+                                                      ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    handle._check(lib.b200_linear_forward_ce_stats_bf16(handle._h, po, lo, px, lx, pw, lw, M, N, K, targets.data_ptr(), col0,
+                                                        out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr()), "forward_ce_stats")
+    return tuple(out)
+
+
 def swiglu_forward_gemm(handle, gate, up, hidden, x, w_gate, w_up, M, ff, K):
     """gate = x w_gate, up = x w_up, hidden = SiLU(gate) * up in one launch (b200_linear_swiglu_forward_bf16)."""
     lib.b200_linear_swiglu_forward_bf16.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 3

@@ -140,6 +140,47 @@ def test_against_reference_kernels_live(pkg, handle, ref_lib):
     assert (o_d.float() - probs.cpu().float()).abs().max() <= 2.0 ** -8 * probs.float().abs().max().item()
 
 
+@pytest.mark.parametrize("rows,K,V,shards", [(1024, 768, 32000, [(0, 32000)]),          # the 125M LM head, one rank
+                                               (512, 256, 128256, [(0, 64256), (64256, 64000)]),   # LLaMA-3 vocabulary, two shards
+                                               (300, 320, 2312, [(0, 1032), (1032, 1280)]),      # ragged rows and widths
+                                               (130, 64, 520, [(0, 520)])])
+def test_statistics_from_the_lm_head_epilogue(pkg, handle, rows, K, V, shards):
+    """b200_linear_forward_ce_stats_bf16: the logits are the plain product's, and (row max, sum exp, target logit)
+    equal what b200_ce_shard_stats_bf16 reads back from them -- maximum and target logit exactly, the sum to fp32
+    rounding; the loss and dlogits that follow meet the float64 oracle (oracle/ce_oracle.py::exact) on the stored logits."""
+    g = torch.Generator(device=DEV).manual_seed(8642)
+    dt = torch.bfloat16
+    x = torch.randn(rows, K, device=DEV, generator=g).to(dt)
+    w = (torch.randn(K, V, device=DEV, generator=g) * (3.0 / K ** 0.5)).to(dt)
+    targets = torch.randint(0, V, (rows,), device=DEV, generator=g, dtype=torch.int32)
+    logits = torch.full((rows, V), float("nan"), device=DEV, dtype=dt)
+    plain = torch.empty(rows, V, device=DEV, dtype=dt)
+    fused = []
+    for a, n in shards:
+        fused.append(pkg.forward_ce_stats(handle, logits[:, a:a + n], x, w[:, a:a + n], rows, n, K, targets, a))
+        pkg.gemm_ld(handle, pkg.FWD_NN, 0, plain[:, a:a + n], x, w[:, a:a + n], rows, n, K)
+    handle.sync()
+    # the same products (where the plain path splits the contraction, fp32 partial sums are added in another order)
+    assert ((logits.double() - plain.double()).abs().max() / plain.double().abs().max()).item() <= 4e-3
+    for (a, n), (fm, fs, ft) in zip(shards, fused):
+        sm, ss, st = pkg.ce_shard_stats(logits[:, a:a + n], targets, a)
+        torch.cuda.synchronize()
+        assert torch.equal(fm, sm) and torch.equal(ft, st)
+        assert ((fs - ss).abs() <= 1e-5 * ss.abs()).all(), ((fs - ss).abs() / ss).max()
+    # the rest of the sharded cross-entropy on the fused statistics
+    gmax = torch.stack([f[0] for f in fused]).max(dim=0).values
+    for fm, fs, _ in fused:
+        pkg.ce_shard_rescale(fm, gmax, fs)
+    gsum = torch.stack([f[1] for f in fused]).sum(dim=0)
+    gtgt = torch.stack([f[2] for f in fused]).sum(dim=0)
+    loss = pkg.ce_shard_loss(gmax, gsum, gtgt)
+    d = torch.empty_like(logits)
+    for a, n in shards:
+        pkg.ce_shard_backward(logits[:, a:a + n], targets, a, gmax, gsum, 1.0 / rows, out=d[:, a:a + n])
+    torch.cuda.synchronize()
+    _check(loss, d, logits, targets)
+
+
 def test_bad_arguments(pkg, handle):
     logits = torch.zeros(4, 8, device=DEV, dtype=torch.bfloat16)
     targets = torch.zeros(4, device=DEV, dtype=torch.int32)

@@ -16,16 +16,21 @@ def test_reference_program_relinked_follows_the_reference_build():
     ref, ours = train_dropin.binaries()
     if not ref or not ours:
         pytest.skip("oracle/_ref/train_* not built (reference checkout absent at build time)")
-    res = train_dropin.overfit(steps=60, repeats_ref=2)
-    a, b = (r["losses"] for r in res["reference"])
+    res = train_dropin.overfit(steps=60, repeats_ref=3)
+    refs = [r["losses"] for r in res["reference"]]
+    a = refs[0]
     o = res["b200"]["losses"]
     assert res["b200"]["rc"] == 0 and all(r["rc"] == 0 for r in res["reference"]), res["b200"]["tail"]
     assert set(o) == set(a) and 60 in o and 1 in o
     for step in sorted(o):
-        ref_mid = 0.5 * (a[step] + b[step])
-        spread = abs(a[step] - b[step])  # the reference's own run-to-run spread (float atomics in its kernels)
-        # 1 % of the loss, the spread of the reference's own two runs, and the print resolution
-        assert abs(o[step] - ref_mid) <= 0.01 * ref_mid + 2 * spread + 1e-4, (step, o[step], a[step], b[step])
+        v = [r[step] for r in refs]
+        ref_mid = sum(v) / len(v)
+        # the reference's own run-to-run spread (float atomics in its kernels): three runs, because on the steepest
+        # steps of the curve (7.7 -> 0.27 between steps 10 and 30) two runs can agree by chance to 0.2 % while a third
+        # lies 1 % away
+        spread = max(v) - min(v)
+        # 1 % of the loss, twice that spread, and the print resolution
+        assert abs(o[step] - ref_mid) <= 0.01 * ref_mid + 2 * spread + 1e-4, (step, o[step], v)
     assert o[1] > 10.0 and o[60] < 0.05  # it starts at ln(32000) and is deep into the overfit by step 60
 
 
