@@ -504,7 +504,27 @@ template <typename T>
 int ce_forward(float* losses, T* logits_probs, const int* targets, int B, int Tlen, int V) {
     if (!losses || !logits_probs || !targets || B <= 0 || Tlen <= 0 || V <= 0) return B200_E_BADARG;
     const int rows = B * Tlen;
-    launch_pdl(ce_row_forward<T>, rows, CE_ROW_THREADS, 0, nullptr, losses, logits_probs, targets, rows, V);
+    // The kernel walks a row three times (maximum, exponentials, normalisation); the second and third walk are meant
+    // to hit L2.  With long rows (128 256 entries = 250 KB) four resident blocks per SM keep 150 MB in flight, more
+    // than the 126 MB L2 holds, and the later walks go back to HBM: an (unused) dynamic shared-memory request caps the
+    // residency so that the rows in flight stay below ~96 MB.
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return B200_E_CUDA;
+    const double row_bytes = static_cast<double>(V) * sizeof(T);
+    int resident = static_cast<int>(96.0e6 / row_bytes / sms);
+    resident = resident < 1 ? 1 : (resident > 4 ? 4 : resident);
+    size_t pad = 0;
+    if (resident < 4) {
+        pad = static_cast<size_t>(227 * 1024 / resident - 2048) & ~static_cast<size_t>(1023);
+        static bool configured[kMaxDev][2] = {};
+        if (dev < kMaxDev && !configured[dev][sizeof(T) == 2]) {
+            if (cudaFuncSetAttribute(ce_row_forward<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048) != cudaSuccess)
+                return B200_E_CUDA;
+            configured[dev][sizeof(T) == 2] = true;
+        }
+    }
+    launch_pdl(ce_row_forward<T>, rows, CE_ROW_THREADS, pad, nullptr, losses, logits_probs, targets, rows, V);
     return launch_ok();
 }
 
