@@ -7,20 +7,20 @@
 // One CTA per (batch, query head, 128 query rows); blocks are dispatched longest first (the last query tile of every
 // head before anybody's first).  Per 128-row key/value tile:
 //   S    = Q K^T            tcgen05.mma 128 x 128 x 64, both operands K-major from 128B-swizzled TMA tiles, S in TMEM
-//   P_h  = exp2(S_h - m_h)  h = the two 64-column halves of the tile, each a softmax of its own: thread (row, h) owns
-//                           half a row of S (TMEM lane = query row), its reference maximum m_h and its row sum, so
-//                           nothing is exchanged between threads per tile; P goes to shared memory as bf16 in the
-//                           K-major swizzled layout the tensor core reads (one 64-column panel per half)
-//   O_h += P_h V_h          tcgen05.mma 128 x 64 x 64, V as an MN-major operand (its rows are the contraction),
-//                           accumulating in TMEM over all tiles
+//   P_h  = exp2(S_h - m_h)  h = the NS (4, or 2) parts of the tile's 128 key columns, each a softmax of its own: thread
+//                           (row, h) owns that part of a row of S (TMEM lane = query row), its reference maximum m_h and
+//                           its row sum, so nothing is exchanged between threads per tile; P goes to shared memory as
+//                           bf16 in the K-major swizzled layout the tensor core reads (two 64-column panels)
+//   O_h += P_h V_h          tcgen05.mma 128 x 64 x (128 / NS), V as an MN-major operand (its rows are the contraction),
+//                           accumulating in TMEM over all tiles (NS accumulators of 64 columns beside the two of S)
 // m_h follows the true maximum lazily: it moves, and O_h is rescaled in TMEM (tcgen05.ld, multiply, tcgen05.st), only
 // when the maximum has grown by more than 2^FA_RESCALE_STEP, so P stays below 2^8 and after the first tiles of a row the
-// rescale is rare.  After the last tile the halves are combined: O = (w_a O_a + w_b O_b) / (w_a l_a + w_b l_b) with
-// w_h = 2^(m_h - max(m_a, m_b)).  S is double-buffered in TMEM and P, K/V in shared memory, so the tensor core computes
+// rescale is rare.  After the last tile the parts are combined: O = sum_h w_h O_h / sum_h w_h l_h with
+// w_h = 2^(m_h - max_h m_h).  S is double-buffered in TMEM and P, K/V in shared memory, so the tensor core computes
 // the next tile's S and this tile's products while the softmax warps work.
-// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4..11 = softmax + epilogue: warps w and w + 4 share
-// a TMEM lane quarter (32 query rows) and take one half each (and, in the epilogue, 32 of the 64 output columns), so
-// that every scheduler has two warps to interleave.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer, 2 = TMEM allocator, 4 .. 4 + 4 NS - 1 = softmax + epilogue: warps w,
+// w + 4, ... share a TMEM lane quarter (32 query rows) and take one part each (and, in the epilogue, 64 / NS of the 64
+// output columns), so that every scheduler has NS softmax warps to interleave.
 // Every wait is bounded (ptx.cuh): on expiry the CTA records a code in *status and leaves.
 #pragma once
 #include <cuda_bf16.h>
@@ -33,11 +33,10 @@ namespace b200 {
 constexpr int FA_BQ = 128;        // query rows per CTA = TMEM lanes
 constexpr int FA_BKV = 128;       // key/value rows per tile
 constexpr int FA_HD = 64;         // head dimension
-constexpr int FA_THREADS = 384;   // warps 0-3: producer, MMA issuer, TMEM allocator, idle; warps 4-11: softmax / epilogue
-constexpr int FA_SOFTMAX_WARPS = 8;
+// threads per CTA: 128 + 128 NS: warps 0-3 = producer, MMA issuer, TMEM allocator, idle; then 4 NS softmax / epilogue warps
 constexpr int FA_TILE_BYTES = 128 * 64 * 2;                 // one 128 x 64 bf16 tile, 128-byte rows
 constexpr int FA_KV_STAGES = 3;   // K/V tiles in flight: a stage is free again only after its P V product
-constexpr int FA_SMEM_BYTES = 4096 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
+constexpr int FA_SMEM_BYTES = 5120 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
                               2 * 2 * FA_TILE_BYTES /*P x 2: two 64-column panels each*/ + 1024 /*alignment*/;
 constexpr int FA_TMEM_COLS = 512;  // S: 2 x 128 columns, O: 2 x 64 columns (forward), dP / dQ / dK / dV (backward)
 constexpr float FA_RESCALE_STEP = 8.0f;   // a row's reference maximum moves only when the true maximum has grown by 2^8
@@ -58,10 +57,10 @@ struct alignas(8) FaCtrl {
     unsigned long long lsum;           // the two halves of every row have published their maximum and row sum (once, at the end)
     uint32_t tmem_base;
     int abort_flag;
-    float mpart[2][FA_BQ];             // [half][row]: reference maximum of that half of the row
-    float lpart[2][FA_BQ];             // [half][row]: its row sum, in units of 2^-maximum
+    float mpart[4][FA_BQ];             // [part][row]: reference maximum of that part of the row
+    float lpart[4][FA_BQ];             // [part][row]: its row sum, in units of 2^-maximum
 };
-constexpr int FA_CTRL_BYTES = 4096;
+constexpr int FA_CTRL_BYTES = 5120;   // a multiple of 1024: the tiles behind it stay 1024-byte aligned
 static_assert(sizeof(FaCtrl) <= FA_CTRL_BYTES, "control block");
 
 __device__ __forceinline__ float fa_exp2(float x) {
@@ -72,7 +71,11 @@ __device__ __forceinline__ float fa_exp2(float x) {
 
 // tmQ / tmO: {n_head*64, T, B} bf16, box {64, 128, 1};  tmK / tmV: {n_kv_head*64, T, B}, box {64, 128, 1};
 // all 128-byte swizzled.  Rows beyond T read as zero and are not written.
-__global__ void __launch_bounds__(FA_THREADS, 1)
+// NS = softmax threads per query row (2 or 4): each takes 128 / NS key columns of a tile as a softmax of its own, with
+// its own accumulator O_part (64 TMEM columns each: S 2 x 128 + O NS x 64 <= 512), and 4 NS softmax warps run beside
+// the four role warps (384 or 640 threads).
+template <int NS>
+__global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FaParams p) {
     extern __shared__ uint8_t fa_smem_raw[];
@@ -100,12 +103,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             for (int i = 0; i < 2; ++i) {
                 mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-                mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
-                mbar_init(smem_u32(&ctrl->p_full[i]), FA_SOFTMAX_WARPS);
+                mbar_init(smem_u32(&ctrl->s_empty[i]), (4 * NS));
+                mbar_init(smem_u32(&ctrl->p_full[i]), (4 * NS));
                 mbar_init(smem_u32(&ctrl->p_empty[i]), 1);
             }
             mbar_init(smem_u32(&ctrl->pv_done), 1);
-            mbar_init(smem_u32(&ctrl->lsum), FA_SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctrl->lsum), (4 * NS));
             ctrl->abort_flag = 0;
             fence_mbar_init();
         }
@@ -125,7 +128,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     tc_fence_after();
     griddep_sync();   // everything above touches no global memory and may overlap the previous kernel's tail
     const uint32_t tmem_base = ctrl->tmem_base;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;   // S[b] at +128 b; O of key-column half h at +64 h
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;   // S[b] at +128 b; O of key-column part h at +64 h
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -185,11 +188,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     const uint32_t pbase = smem_u32(sP + s * 2 * FA_TILE_BYTES);
 #pragma unroll
                     for (int k = 0; k < FA_BKV / UMMA_K; ++k) {
-                        // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel.  Panel h (k >> 2) meets
-                        // key rows 64 h .. 64 h + 63 of V and accumulates into its own O: the halves keep separate maxima.
+                        // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel.  Part k / KPP of the key
+                        // columns meets the matching key rows of V and accumulates into its own O: the parts keep separate maxima.
                         const uint64_t descP = umma_smem_desc(pbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
-                        umma_f16<1>(tmem_O + (k >> 2) * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV,
-                                    (i > 0 || (k & 3) > 0) ? 1u : 0u);
+                        constexpr int KPP = (FA_BKV / UMMA_K) / NS;   // MMAs per part of the key tile
+                        umma_f16<1>(tmem_O + (k / KPP) * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV,
+                                    (i > 0 || (k % KPP) > 0) ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&ctrl->pv_done));
                     umma_commit(smem_u32(&ctrl->kv_empty[st]));
@@ -200,16 +204,17 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ softmax + epilogue
         const int qrt = warp & 3;                                   // TMEM lane quarter of this warp
-        const int half = (warp - 4) >> 2;                           // which 64 key columns / 32 output columns of the row
+        const int part = (warp - 4) >> 2;                           // which 128 / NS key columns of the row
         const int r = qrt * 32 + lane;                              // query row inside the tile
         const int row = qt * FA_BQ + r;                             // query position
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
-        constexpr int HC = FA_BKV / 2, HO = FA_HD / 2;              // columns of S per thread; output columns per thread
-        // Each half of a row is a softmax of its own: reference maximum m (log2 units), row sum l in units of 2^-m, and
-        // an accumulator O_half in TMEM that the tensor core adds P_half V_half to.  m follows the true maximum lazily:
-        // it moves (and O_half, l are rescaled) only when the maximum has grown by more than FA_RESCALE_STEP, so that
+        constexpr int HC = FA_BKV / NS;                             // columns of S per thread
+        constexpr int OC = FA_HD / NS;                              // output columns per thread in the epilogue
+        // Each part of a row is a softmax of its own: reference maximum m (log2 units), row sum l in units of 2^-m, and
+        // an accumulator O_part in TMEM that the tensor core adds P_part V_part to.  m follows the true maximum lazily:
+        // it moves (and O_part, l are rescaled) only when the maximum has grown by more than FA_RESCALE_STEP, so that
         // P stays below 2^8 and the common tile costs one max, one FMA + exp2 and one add per element and no exchange.
-        // The two halves are put together once, after the last tile.
+        // The parts are put together once, after the last tile.
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
@@ -218,13 +223,13 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tS = tmem_S + s * 128 + lane_off + half * HC;
+            const uint32_t tS = tmem_S + s * 128 + lane_off + part * HC;
             const bool diag = j == qt;                              // the only tile that needs the causal / length mask
-            const int col0 = j * FA_BKV + half * HC;
-            // this thread's half of the row of S comes into registers with one wait; the S buffer is free for tile j + 2
+            const int col0 = j * FA_BKV + part * HC;
+            // this thread's part of the row of S comes into registers with one wait; the S buffer is free for tile j + 2
             float x[HC];
-            tmem_ld_32x32(tS, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
-            tmem_ld_32x32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
+#pragma unroll
+            for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[c * 32]));
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -244,7 +249,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2e;   // the scale is positive
             const bool grow = mx > m + FA_RESCALE_STEP;             // also the first finite maximum (m = -inf)
             if (__any_sync(0xffffffffu, grow)) {
-                // rare after the first tiles: move this row's reference maximum and bring l and O_half along
+                // rare after the first tiles: move this row's reference maximum and bring l and O_part along
                 const float m_new = grow ? mx : m;
                 const float alpha = (m_new == m) ? 1.0f : fa_exp2(m - m_new);   // 0 when m was -inf
                 if (j > 0) {
@@ -253,14 +258,14 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t acc[32];
-                        tmem_ld_32x32(tmem_O + half * FA_HD + lane_off + c * 32, acc);
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {   // 16 columns at a time: this path is rare and must stay cheap in registers
+                        uint32_t acc[16];
+                        tmem_ld_32x16(tmem_O + part * FA_HD + lane_off + c * 16, acc);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
-                        tmem_st_32x32(tmem_O + half * FA_HD + lane_off + c * 32, acc);
+                        for (int e = 0; e < 16; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * alpha);
+                        tmem_st_32x16(tmem_O + part * FA_HD + lane_off + c * 16, acc);
                     }
                     tmem_st_wait();
                 }
@@ -271,12 +276,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = mbar_wait(smem_u32(&ctrl->p_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            // P = exp2(S scale - m) as bf16 into this half's 64-column panel, row sum in fp32 (four chains)
-            const float neg_m = (m == -INFINITY) ? 0.f : -m;       // a half with nothing visible yet: P = exp2(-inf) = 0
-            uint8_t* panel = sP + s * 2 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
+            // P = exp2(S scale - m) as bf16 into this part's columns of the two 64-column panels, row sum in fp32
+            const float neg_m = (m == -INFINITY) ? 0.f : -m;       // a part with nothing visible yet: P = exp2(-inf) = 0
+            uint8_t* prow = sP + s * 2 * FA_TILE_BYTES + r * 128;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
@@ -285,9 +290,11 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     sum4[(e >> 1) & 3] += p0 + p1;
                     packed[e >> 1] = pack_bf16x2(p0, p1);
                 }
+                const int g32 = part * (HC / 32) + c;   // which 32-column group of the tile: panel g32 >> 1, half-row g32 & 1
+                uint8_t* panel = prow + (g32 >> 1) * FA_TILE_BYTES;
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {   // 16-byte chunks c * 4 .. + 3 of the 128-byte row, swizzled by the row
-                    const int chunk = (c * 4 + qd) ^ (r & 7);
+                for (int qd = 0; qd < 4; ++qd) {   // four 16-byte chunks of the 128-byte panel row, swizzled by the row
+                    const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
                     *reinterpret_cast<uint4*>(panel + chunk * 16) =
                         make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
                 }
@@ -299,9 +306,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         }
         if (ok) {
-            // the two halves of a row exchange (m, l); the last products must have retired
-            ctrl->mpart[half][r] = m;
-            ctrl->lpart[half][r] = l;
+            // the parts of a row exchange (m, l); the last products must have retired
+            ctrl->mpart[part][r] = m;
+            ctrl->lpart[part][r] = l;
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->lsum));
             ok = mbar_wait(smem_u32(&ctrl->lsum), 0, abort_flag, p.status, DEV_TIMEOUT_PEER) &&
@@ -310,37 +317,50 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         if (ok) {
             tc_fence_after();
-            const float m_a = ctrl->mpart[0][r], m_b = ctrl->mpart[1][r];
-            const float m_row = fmaxf(m_a, m_b);                        // finite: column `row` itself is always visible
-            const float w_a = (m_a == -INFINITY) ? 0.f : fa_exp2(m_a - m_row), w_b = (m_b == -INFINITY) ? 0.f : fa_exp2(m_b - m_row);
-            const float l_row = ctrl->lpart[0][r] * w_a + ctrl->lpart[1][r] * w_b;
+            float m_row = -INFINITY;                                    // finite: column `row` itself is always visible
+#pragma unroll
+            for (int a = 0; a < NS; ++a) m_row = fmaxf(m_row, ctrl->mpart[a][r]);
+            float w[NS], l_row = 0.f;
+#pragma unroll
+            for (int a = 0; a < NS; ++a) {
+                const float ma = ctrl->mpart[a][r];
+                w[a] = (ma == -INFINITY) ? 0.f : fa_exp2(ma - m_row);
+                l_row += ctrl->lpart[a][r] * w[a];
+            }
             const float inv = 1.0f / l_row;
             // every tensor-core read of the P buffers has completed (the last commit covers them): stage O in P buffer 0.
-            // This thread writes output columns 32 half .. 32 half + 31 of its row: w_a O_a + w_b O_b over l.
-            uint8_t* orow = sP + r * 128;
-            uint32_t va[HO], vb[HO];
-            tmem_ld_32x32(tmem_O + lane_off + half * HO, va);
-            tmem_ld_32x32(tmem_O + FA_HD + lane_off + half * HO, vb);
-            tmem_ld_wait();
-            const float ca = w_a * inv, cb = w_b * inv;
+            // This thread writes output columns OC part .. OC part + OC - 1 of its row: sum_a w_a O_a over l.
+            float y[OC];
 #pragma unroll
-            for (int qd = 0; qd < 4; ++qd) {
-                float y[8];
+            for (int e = 0; e < OC; ++e) y[e] = 0.f;
 #pragma unroll
-                for (int e = 0; e < 8; ++e)
-                    y[e] = __uint_as_float(va[qd * 8 + e]) * ca + __uint_as_float(vb[qd * 8 + e]) * cb;
-                const int chunk = (half * 4 + qd) ^ (r & 7);
-                *reinterpret_cast<uint4*>(orow + chunk * 16) =
-                    make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+            for (int a = 0; a < NS; ++a) {
+                const float ca = w[a] * inv;
+#pragma unroll
+                for (int g = 0; g < OC / 16; ++g) {
+                    uint32_t v[16];
+                    tmem_ld_32x16(tmem_O + a * FA_HD + lane_off + part * OC + g * 16, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) y[g * 16 + e] = fmaf(__uint_as_float(v[e]), ca, y[g * 16 + e]);
+                }
             }
-            if (half == 0 && row < p.T)
+            uint8_t* orow = sP + r * 128;
+#pragma unroll
+            for (int qd = 0; qd < OC / 8; ++qd) {
+                const int chunk = (part * (OC / 8) + qd) ^ (r & 7);
+                *reinterpret_cast<uint4*>(orow + chunk * 16) =
+                    make_uint4(pack_bf16x2(y[qd * 8], y[qd * 8 + 1]), pack_bf16x2(y[qd * 8 + 2], y[qd * 8 + 3]),
+                               pack_bf16x2(y[qd * 8 + 4], y[qd * 8 + 5]), pack_bf16x2(y[qd * 8 + 6], y[qd * 8 + 7]));
+            }
+            if (part == 0 && row < p.T)
                 p.lse[(static_cast<long long>(b) * p.n_head + h) * p.T + row] = (m_row + log2f(l_row)) * 0.69314718055994531f;
         }
-        // All eight epilogue warps come here exactly once, whether or not their waits succeeded, so this barrier
+        // All softmax / epilogue warps come here exactly once, whether or not their waits succeeded, so this barrier
         // cannot be left waiting; the tile is stored only if nobody gave up.
         tc_fence_before();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(NS * 128) : "memory");
         if (warp == 4 && !*abort_flag) {
             if (elect_one()) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
@@ -394,7 +414,9 @@ struct alignas(8) FbDqCtrl {
 // dQ for one (batch, query head, 128 query rows): per key tile S = Q K^T and dP = dO V^T on the tensor cores, the four
 // softmax warps turn them into dS (bf16, K-major in shared memory), and dQ += dS K accumulates in TMEM over all tiles.
 // tmQ / tmdO / tmdQ: {n_head*64, T, B}, box {64,128,1};  tmK / tmV: {n_kv_head*64, T, B}, box {64,128,1}.
-__global__ void __launch_bounds__(FA_THREADS, 1)
+// NS = softmax threads per query row (2 or 4), as in the forward kernel: 128 / NS key columns each.
+template <int NS>
+__global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ CUtensorMap tmdQ, const FbParams p) {
@@ -421,12 +443,12 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
-            mbar_init(smem_u32(&ctrl->ds_full[i]), FA_SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctrl->s_empty[i]), (4 * NS));
+            mbar_init(smem_u32(&ctrl->ds_full[i]), (4 * NS));
             mbar_init(smem_u32(&ctrl->ds_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctrl->dp_full), 1);
-        mbar_init(smem_u32(&ctrl->dp_empty), FA_SOFTMAX_WARPS);
+        mbar_init(smem_u32(&ctrl->dp_empty), (4 * NS));
         mbar_init(smem_u32(&ctrl->dq_full), 1);
         ctrl->abort_flag = 0;
         fence_mbar_init();
@@ -533,7 +555,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ dS + epilogue
         const int qrt = warp & 3;
-        const int half = (warp - 4) >> 2;   // which 64 key columns (and which 32 columns of dQ) of the row
+        const int part = (warp - 4) >> 2;   // which 128 / NS key columns (and which 64 / NS columns of dQ) of the row
+        constexpr int HC = FA_BKV / NS, OC = FA_HD / NS;
         const int r = qrt * 32 + lane;
         const int row = qt * FA_BQ + r;
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
@@ -549,27 +572,30 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tS = tmem_S + s * 128 + lane_off + half * 64, tP = tmem_dP + lane_off + half * 64;
+            const uint32_t tS = tmem_S + s * 128 + lane_off + part * HC, tP = tmem_dP + lane_off + part * HC;
             // only the diagonal tile and the tiles that reach beyond the sequence need a mask
             const bool masked = j == qt || (j + 1) * FA_BKV > p.T || (qt + 1) * FA_BQ > p.T;
-            const int col0 = j * FA_BKV + half * 64;
-            uint8_t* panel = sdS + s * 2 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
-            // This thread's 64 columns of dP come into registers at once and the (single) dP accumulator is handed
-            // back before any arithmetic: the tensor core forms dP of the next tile while this one is turned into dS.
-            uint32_t dv[64], sv[32];
-            tmem_ld_32x32(tP, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
-            tmem_ld_32x32(tP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+            const int col0 = j * FA_BKV + part * HC;
+            uint8_t* dsrow = sdS + s * 2 * FA_TILE_BYTES + r * 128;
+            // This thread's columns of dP come into registers at once and the (single) dP accumulator is handed back
+            // before any arithmetic: the tensor core forms dP of the next tile while this one is turned into dS.
+            uint32_t dv[HC], sv[32];
+#pragma unroll
+            for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tP + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[c * 32]));
             tmem_ld_32x32(tS, sv);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->dp_empty));
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&ctrl->dp_empty));
+                if (HC == 32) mbar_arrive(smem_u32(&ctrl->s_empty[s]));   // its only 32 columns of S are in registers too
+            }
             // the tensor core must have finished reading this dS buffer (tile j - 2)
             ok = mbar_wait(smem_u32(&ctrl->ds_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 if (c == 1) {
                     tmem_ld_32x32(tS + 32, sv);
                     tmem_ld_wait();
@@ -596,9 +622,11 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                                                      fa_exp2(x1) * (__uint_as_float(dv[c * 32 + e + 1]) - delta));
                     }
                 }
+                const int g32 = part * (HC / 32) + c;   // 32-column group of the tile: panel g32 >> 1, half-row g32 & 1
+                uint8_t* panel = dsrow + (g32 >> 1) * FA_TILE_BYTES;
 #pragma unroll
                 for (int qd = 0; qd < 4; ++qd) {
-                    const int chunk = (c * 4 + qd) ^ (r & 7);
+                    const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
                     *reinterpret_cast<uint4*>(panel + chunk * 16) =
                         make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
                 }
@@ -614,17 +642,17 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (ok) {
             tc_fence_after();
             uint8_t* orow = sdS + r * 128;   // every tensor-core read of the dS buffers has completed
-            {
-                const int c = half;
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_dQ + lane_off + c * 32, v);
+#pragma unroll
+            for (int g = 0; g < OC / 16; ++g) {
+                uint32_t v[16];
+                tmem_ld_32x16(tmem_dQ + lane_off + part * OC + g * 16, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {
+                for (int qd = 0; qd < 2; ++qd) {
                     float x[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[qd * 8 + e]) * p.scale;
-                    const int chunk = (c * 4 + qd) ^ (r & 7);
+                    const int chunk = (part * (OC / 8) + g * 2 + qd) ^ (r & 7);
                     *reinterpret_cast<uint4*>(orow + chunk * 16) =
                         make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
                 }
@@ -632,7 +660,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         tc_fence_before();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // all eight warps arrive here exactly once
+        asm volatile("bar.sync 1, %0;" ::"n"(NS * 128) : "memory");   // all softmax warps arrive here exactly once
         if (warp == 4 && !*abort_flag) {
             if (elect_one()) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
@@ -672,7 +700,8 @@ struct alignas(8) FbDkvCtrl {
 // softmax warps write P and dS as bf16 [query][key] tiles, and the tensor core reads those tiles as MN-major left
 // operands (their rows are the contraction): dV += P^T dO and dK += dS^T Q accumulate in TMEM over all iterations.
 // tmQ / tmdO: {n_head*64, T, B};  tmK / tmV / tmdK / tmdV: {n_kv_head*64, T, B};  boxes {64,128,1}.
-__global__ void __launch_bounds__(FA_THREADS, 1)
+template <int NS>   // softmax threads per query row (2 or 4)
+__global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV, const FbParams p) {
@@ -701,12 +730,12 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->s_empty[i]), FA_SOFTMAX_WARPS);
-            mbar_init(smem_u32(&ctrl->pds_full[i]), FA_SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctrl->s_empty[i]), (4 * NS));
+            mbar_init(smem_u32(&ctrl->pds_full[i]), (4 * NS));
             mbar_init(smem_u32(&ctrl->pds_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctrl->dp_full), 1);
-        mbar_init(smem_u32(&ctrl->dp_empty), FA_SOFTMAX_WARPS);
+        mbar_init(smem_u32(&ctrl->dp_empty), (4 * NS));
         mbar_init(smem_u32(&ctrl->dkv_full), 1);
         ctrl->abort_flag = 0;
         fence_mbar_init();
@@ -824,7 +853,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ P, dS + epilogue
         const int qrt = warp & 3;
-        const int half = (warp - 4) >> 2;   // which 64 key columns of the row; in the epilogue: dV (0) or dK (1)
+        const int part = (warp - 4) >> 2;   // which 128 / NS key columns of the row; in the epilogue: a share of dV or of dK
+        constexpr int HC = FA_BKV / NS;
         const int r = qrt * 32 + lane;
         const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
         bool ok = true;
@@ -851,25 +881,28 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t tS = tmem_S + s * 128 + lane_off + half * 64, tP = tmem_dP + lane_off + half * 64;
+            const uint32_t tS = tmem_S + s * 128 + lane_off + part * HC, tP = tmem_dP + lane_off + part * HC;
             const bool masked = i == kt || (kt + 1) * FA_BKV > p.T || (i + 1) * FA_BQ > p.T;
-            const int col0 = kt * FA_BKV + half * 64;
-            uint8_t* prow = sPdS + s * 4 * FA_TILE_BYTES + half * FA_TILE_BYTES + r * 128;
+            const int col0 = kt * FA_BKV + part * HC;
+            uint8_t* prow = sPdS + s * 4 * FA_TILE_BYTES + r * 128;
             uint8_t* dsrow = prow + 2 * FA_TILE_BYTES;
             // as in the dQ kernel: dP into registers at once, its accumulator handed back before the arithmetic
-            uint32_t dv[64], sv[32];
-            tmem_ld_32x32(tP, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
-            tmem_ld_32x32(tP + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+            uint32_t dv[HC], sv[32];
+#pragma unroll
+            for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tP + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[c * 32]));
             tmem_ld_32x32(tS, sv);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->dp_empty));
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&ctrl->dp_empty));
+                if (HC == 32) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+            }
             ok = mbar_wait(smem_u32(&ctrl->pds_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < HC / 32; ++c) {
                 if (c == 1) {
                     tmem_ld_32x32(tS + 32, sv);
                     tmem_ld_wait();
@@ -898,11 +931,13 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                         pd[e >> 1] = pack_bf16x2(p0 * (__uint_as_float(dv[c * 32 + e]) - delta), p1 * (__uint_as_float(dv[c * 32 + e + 1]) - delta));
                     }
                 }
+                const int g32 = part * (HC / 32) + c;   // 32-column group of the tile: panel g32 >> 1, half-row g32 & 1
+                const int poff = (g32 >> 1) * FA_TILE_BYTES;
 #pragma unroll
                 for (int qd = 0; qd < 4; ++qd) {
-                    const int chunk = (c * 4 + qd) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pp[4 * qd], pp[4 * qd + 1], pp[4 * qd + 2], pp[4 * qd + 3]);
-                    *reinterpret_cast<uint4*>(dsrow + chunk * 16) = make_uint4(pd[4 * qd], pd[4 * qd + 1], pd[4 * qd + 2], pd[4 * qd + 3]);
+                    const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + poff + chunk * 16) = make_uint4(pp[4 * qd], pp[4 * qd + 1], pp[4 * qd + 2], pp[4 * qd + 3]);
+                    *reinterpret_cast<uint4*>(dsrow + poff + chunk * 16) = make_uint4(pd[4 * qd], pd[4 * qd + 1], pd[4 * qd + 2], pd[4 * qd + 3]);
                 }
             }
             fence_proxy_async_smem();
@@ -915,31 +950,32 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         if (ok) {
             tc_fence_after();
-            // thread (r, half) now owns key row r of dV (half 0) or dK (half 1); stage them in the (free) P / dS buffers
-            {
-                const int which = half;
-                uint8_t* orow = sPdS + which * FA_TILE_BYTES + r * 128;
-                const float mul = which == 0 ? 1.0f : p.scale;
+            // the 2 x 64 output columns of key row r (dV, then dK) are shared out to the row's NS threads; staged in the
+            // (free) P / dS buffers
+            constexpr int OC = 2 * FA_HD / NS;                 // 64 (NS = 2) or 32 (NS = 4) columns per thread
+            const int which = (part * OC) / FA_HD;             // 0: dV, 1: dK
+            const int c_first = (part * OC) % FA_HD;           // first column inside that matrix
+            uint8_t* orow = sPdS + which * FA_TILE_BYTES + r * 128;
+            const float mul = which == 0 ? 1.0f : p.scale;
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32((which == 0 ? tmem_dV : tmem_dK) + lane_off + c * 32, v);
-                    tmem_ld_wait();
+            for (int c = 0; c < OC / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32((which == 0 ? tmem_dV : tmem_dK) + lane_off + c_first + c * 32, v);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int qd = 0; qd < 4; ++qd) {
-                        float x[8];
+                for (int qd = 0; qd < 4; ++qd) {
+                    float x[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[qd * 8 + e]) * mul;
-                        const int chunk = (c * 4 + qd) ^ (r & 7);
-                        *reinterpret_cast<uint4*>(orow + chunk * 16) =
-                            make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
-                    }
+                    for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[qd * 8 + e]) * mul;
+                    const int chunk = ((c_first + c * 32) / 8 + qd) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(orow + chunk * 16) =
+                        make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
                 }
             }
         }
         tc_fence_before();
         fence_proxy_async_smem();
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // all eight warps arrive here exactly once
+        asm volatile("bar.sync 1, %0;" ::"n"(NS * 128) : "memory");   // all softmax warps arrive here exactly once
         if (warp == 4 && !*abort_flag) {
             if (elect_one()) {
                 asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(

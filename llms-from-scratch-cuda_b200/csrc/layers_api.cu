@@ -85,9 +85,12 @@ int configure_attention() {
     ATTN_SMEM(attn_bwd_dq_simt<__nv_bfloat16>, ATTN_DQ_SMEM);
     ATTN_SMEM(attn_bwd_dkv_simt<float>, ATTN_DKV_SMEM);
     ATTN_SMEM(attn_bwd_dkv_simt<__nv_bfloat16>, ATTN_DKV_SMEM);
-    ATTN_SMEM(attn_fwd_sm100, FA_SMEM_BYTES);
-    ATTN_SMEM(attn_bwd_dq_sm100, FB_DQ_SMEM_BYTES);
-    ATTN_SMEM(attn_bwd_dkv_sm100, FB_DKV_SMEM_BYTES);
+    ATTN_SMEM(attn_fwd_sm100<2>, FA_SMEM_BYTES);
+    ATTN_SMEM(attn_fwd_sm100<4>, FA_SMEM_BYTES);
+    ATTN_SMEM(attn_bwd_dq_sm100<2>, FB_DQ_SMEM_BYTES);
+    ATTN_SMEM(attn_bwd_dq_sm100<4>, FB_DQ_SMEM_BYTES);
+    ATTN_SMEM(attn_bwd_dkv_sm100<2>, FB_DKV_SMEM_BYTES);
+    ATTN_SMEM(attn_bwd_dkv_sm100<4>, FB_DKV_SMEM_BYTES);
 #undef ATTN_SMEM
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -147,6 +150,15 @@ bool use_tensor_cores(const void* a, const void* b, const void* c, const void* d
              reinterpret_cast<uintptr_t>(d)) & 15) == 0;
 }
 
+int attn_row_threads() {   // B200_ATTN_ROW_THREADS: 0 (unset) = chosen per call
+    static const int v = [] {
+        const char* e = getenv("B200_ATTN_ROW_THREADS");
+        const int n = e ? atoi(e) : 0;
+        return (n == 2 || n == 4) ? n : 0;
+    }();
+    return v;
+}
+
 int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                      int B, int Tlen, int n_head, int n_kv_head, cudaStream_t stream) {
     b200_linear_ctx* ctx = b200_linear_default_ctx();
@@ -160,7 +172,13 @@ int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q,
     p.lse = lse;
     p.status = b200_linear_status_word(ctx);
     const dim3 grid(n_head, B, (Tlen + FA_BQ - 1) / FA_BQ);
-    launch_pdl(attn_fwd_sm100, grid, FA_THREADS, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+    // Softmax threads per query row: four (16 softmax warps) pay once a block walks many key tiles (T = 8192: 361 us
+    // against 395 us with two), two are quicker for short sequences (T = 512: 39.7 against 41.1 us).
+    // B200_ATTN_ROW_THREADS=2|4 forces one.
+    const int forced = attn_row_threads();
+    const bool two = forced ? forced == 2 : Tlen < 2048;
+    if (two) launch_pdl(attn_fwd_sm100<2>, grid, 128 + 2 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+    else launch_pdl(attn_fwd_sm100<4>, grid, 128 + 4 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 
@@ -205,8 +223,16 @@ int flash_backward_tc(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, c
     p.delta = delta;
     p.status = b200_linear_status_word(ctx);
     const int tiles = (Tlen + FA_BQ - 1) / FA_BQ;
-    launch_pdl(attn_bwd_dq_sm100, dim3(n_head, B, tiles), FA_THREADS, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
-    launch_pdl(attn_bwd_dkv_sm100, dim3(n_kv_head, B, tiles), FA_THREADS, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+    // two softmax threads per query row for the backward kernels (four measured 3-6 % slower at T = 512 and T = 8192)
+    // unless B200_ATTN_ROW_THREADS=4 forces four
+    const bool two = attn_row_threads() != 4;
+    if (two) {
+        launch_pdl(attn_bwd_dq_sm100<2>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        launch_pdl(attn_bwd_dkv_sm100<2>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+    } else {
+        launch_pdl(attn_bwd_dq_sm100<4>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        launch_pdl(attn_bwd_dkv_sm100<4>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+    }
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 

@@ -33,7 +33,8 @@ def layers(pkg):
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,T,nh,nkv", [(2, 256, 12, 4), (1, 130, 6, 2), (1, 64, 4, 4), (1, 1024, 3, 1), (3, 33, 2, 1)])
+@pytest.mark.parametrize("B,T,nh,nkv", [(2, 256, 12, 4), (1, 130, 6, 2), (1, 64, 4, 4), (1, 1024, 3, 1), (3, 33, 2, 1),
+                                       (1, 2100, 3, 1)])   # long enough for the forward kernel with four threads per row
 def test_fused_attention_core_forward_and_backward(layers, handle, dt, B, T, nh, nkv):
     """context, lse, dq, dk, dv of the fused kernels against float64, including sequence lengths that are not a
     multiple of the tile, grouped (nh > nkv) and ungrouped heads; and run-to-run determinism of the backward."""
