@@ -74,7 +74,9 @@ __device__ __forceinline__ float fa_exp2(float x) {
 // NS = softmax threads per query row (2 or 4): each takes 128 / NS key columns of a tile as a softmax of its own, with
 // its own accumulator O_part (64 TMEM columns each: S 2 x 128 + O NS x 64 <= 512), and 4 NS softmax warps run beside
 // the four role warps (384 or 640 threads).
-template <int NS>
+// P_TMEM: P goes back to tensor memory as bf16 (over the first half of each 32-column group of the S buffer it came
+// from) and the tensor core reads it from there as the left operand of P V, instead of through shared memory.
+template <int NS, bool P_TMEM>
 __global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FaParams p) {
@@ -103,7 +105,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             for (int i = 0; i < 2; ++i) {
                 mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-                mbar_init(smem_u32(&ctrl->s_empty[i]), (4 * NS));
+                mbar_init(smem_u32(&ctrl->s_empty[i]), P_TMEM ? 1 : (4 * NS));   // P_TMEM: freed by the tensor core after P V
                 mbar_init(smem_u32(&ctrl->p_full[i]), (4 * NS));
                 mbar_init(smem_u32(&ctrl->p_empty[i]), 1);
             }
@@ -186,15 +188,23 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     // V tile: 128 contraction rows of 128 bytes, 8-row groups 1024 bytes apart, 16 rows per MMA
                     const uint64_t descV = umma_smem_desc(smem_u32(sKV + st * 2 * FA_TILE_BYTES + FA_TILE_BYTES), 64 * 64 * 2, 1024);
                     const uint32_t pbase = smem_u32(sP + s * 2 * FA_TILE_BYTES);
+                    constexpr int KPP = (FA_BKV / UMMA_K) / NS;   // MMAs per part of the key tile
 #pragma unroll
                     for (int k = 0; k < FA_BKV / UMMA_K; ++k) {
-                        // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel.  Part k / KPP of the key
-                        // columns meets the matching key rows of V and accumulates into its own O: the parts keep separate maxima.
-                        const uint64_t descP = umma_smem_desc(pbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
-                        constexpr int KPP = (FA_BKV / UMMA_K) / NS;   // MMAs per part of the key tile
-                        umma_f16<1>(tmem_O + (k / KPP) * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV,
-                                    (i > 0 || (k % KPP) > 0) ? 1u : 0u);
+                        // Part k / KPP of the key columns meets the matching key rows of V and accumulates into its own O:
+                        // the parts keep separate maxima.
+                        const uint32_t acc = (i > 0 || (k % KPP) > 0) ? 1u : 0u;
+                        if constexpr (P_TMEM) {
+                            // P of keys 16 k .. 16 k + 15: 8 packed columns in the first half of 32-column group k / 2 of S
+                            umma_f16_ts(tmem_O + (k / KPP) * 64, tmem_S + s * 128 + (k >> 1) * 32 + (k & 1) * 8,
+                                        descV + ((k * UMMA_K * 128) >> 4), idesc_PV, acc);
+                        } else {
+                            // P: two 64-column panels of 128-byte rows; 32 bytes per MMA inside a panel
+                            const uint64_t descP = umma_smem_desc(pbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
+                            umma_f16<1>(tmem_O + (k / KPP) * 64, descP, descV + ((k * UMMA_K * 128) >> 4), idesc_PV, acc);
+                        }
                     }
+                    if constexpr (P_TMEM) umma_commit(smem_u32(&ctrl->s_empty[s]));   // P lived in this S buffer
                     umma_commit(smem_u32(&ctrl->pv_done));
                     umma_commit(smem_u32(&ctrl->kv_empty[st]));
                     umma_commit(smem_u32(&ctrl->p_empty[s]));
@@ -231,9 +241,11 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&x[c * 32]));
             tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+            if constexpr (!P_TMEM) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (diag) {
 #pragma unroll
@@ -272,10 +284,12 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 l *= alpha;
                 m = m_new;
             }
-            // the tensor core must have finished reading this P buffer (tile j - 2)
-            ok = mbar_wait(smem_u32(&ctrl->p_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if constexpr (!P_TMEM) {
+                // the tensor core must have finished reading this P buffer (tile j - 2)
+                ok = mbar_wait(smem_u32(&ctrl->p_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
             // P = exp2(S scale - m) as bf16 into this part's columns of the two 64-column panels, row sum in fp32
             const float neg_m = (m == -INFINITY) ? 0.f : -m;       // a part with nothing visible yet: P = exp2(-inf) = 0
             uint8_t* prow = sP + s * 2 * FA_TILE_BYTES + r * 128;
@@ -291,16 +305,22 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     packed[e >> 1] = pack_bf16x2(p0, p1);
                 }
                 const int g32 = part * (HC / 32) + c;   // which 32-column group of the tile: panel g32 >> 1, half-row g32 & 1
-                uint8_t* panel = prow + (g32 >> 1) * FA_TILE_BYTES;
+                if constexpr (P_TMEM) {
+                    // over the first 16 columns of the group's own S columns (already in this thread's registers)
+                    tmem_st_32x16(tmem_S + s * 128 + lane_off + g32 * 32, packed);
+                } else {
+                    uint8_t* panel = prow + (g32 >> 1) * FA_TILE_BYTES;
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {   // four 16-byte chunks of the 128-byte panel row, swizzled by the row
-                    const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(panel + chunk * 16) =
-                        make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
+                    for (int qd = 0; qd < 4; ++qd) {   // four 16-byte chunks of the 128-byte panel row, swizzled by the row
+                        const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(panel + chunk * 16) =
+                            make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
+                    }
                 }
             }
-            fence_proxy_async_smem();
-            tc_fence_before();                                         // orders a rescale of O before the next product
+            if constexpr (P_TMEM) tmem_st_wait();
+            else fence_proxy_async_smem();
+            tc_fence_before();                                         // orders P / a rescale of O before the next product
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->p_full[s]));    // this warp's part of P is ready for the tensor core
             l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
@@ -415,7 +435,9 @@ struct alignas(8) FbDqCtrl {
 // softmax warps turn them into dS (bf16, K-major in shared memory), and dQ += dS K accumulates in TMEM over all tiles.
 // tmQ / tmdO / tmdQ: {n_head*64, T, B}, box {64,128,1};  tmK / tmV: {n_kv_head*64, T, B}, box {64,128,1}.
 // NS = softmax threads per query row (2 or 4), as in the forward kernel: 128 / NS key columns each.
-template <int NS>
+// DS_TMEM: dS goes back to tensor memory as bf16 (over the first half of each 32-column group of the S buffer) and is
+// the left operand of dS K from there, instead of through shared memory.
+template <int NS, bool DS_TMEM>
 __global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -443,7 +465,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->s_empty[i]), (4 * NS));
+            mbar_init(smem_u32(&ctrl->s_empty[i]), DS_TMEM ? 1 : (4 * NS));   // DS_TMEM: freed by the tensor core after dS K
             mbar_init(smem_u32(&ctrl->ds_full[i]), (4 * NS));
             mbar_init(smem_u32(&ctrl->ds_empty[i]), 1);
         }
@@ -543,11 +565,18 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     const uint32_t dsbase = smem_u32(sdS + s * 2 * FA_TILE_BYTES);
 #pragma unroll
                     for (int k = 0; k < FA_BKV / UMMA_K; ++k) {
-                        const uint64_t descdS = umma_smem_desc(dsbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
-                        umma_f16<1>(tmem_dQ, descdS, descKm + ((k * UMMA_K * 128) >> 4), idesc_dQ, (i > 0 || k > 0) ? 1u : 0u);
+                        if constexpr (DS_TMEM) {
+                            // dS of keys 16 k .. 16 k + 15: 8 packed columns in the first half of 32-column group k / 2 of S
+                            umma_f16_ts(tmem_dQ, tmem_S + s * 128 + (k >> 1) * 32 + (k & 1) * 8, descKm + ((k * UMMA_K * 128) >> 4),
+                                        idesc_dQ, (i > 0 || k > 0) ? 1u : 0u);
+                        } else {
+                            const uint64_t descdS = umma_smem_desc(dsbase + (k >> 2) * FA_TILE_BYTES + (k & 3) * UMMA_K * 2, 16, 1024);
+                            umma_f16<1>(tmem_dQ, descdS, descKm + ((k * UMMA_K * 128) >> 4), idesc_dQ, (i > 0 || k > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(smem_u32(&ctrl->kv_empty[st]));
-                    umma_commit(smem_u32(&ctrl->ds_empty[s]));
+                    if constexpr (DS_TMEM) umma_commit(smem_u32(&ctrl->s_empty[s]));   // dS lived in this S buffer
+                    else umma_commit(smem_u32(&ctrl->ds_empty[s]));
                     if (i == n_kv - 1) umma_commit(smem_u32(&ctrl->dq_full));
                 }
             }
@@ -588,20 +617,24 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(smem_u32(&ctrl->dp_empty));
-                if (HC == 32) mbar_arrive(smem_u32(&ctrl->s_empty[s]));   // its only 32 columns of S are in registers too
+                if (HC == 32 && !DS_TMEM) mbar_arrive(smem_u32(&ctrl->s_empty[s]));   // its only 32 columns of S are in registers too
             }
-            // the tensor core must have finished reading this dS buffer (tile j - 2)
-            ok = mbar_wait(smem_u32(&ctrl->ds_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if constexpr (!DS_TMEM) {
+                // the tensor core must have finished reading this dS buffer (tile j - 2)
+                ok = mbar_wait(smem_u32(&ctrl->ds_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
 #pragma unroll
             for (int c = 0; c < HC / 32; ++c) {
                 if (c == 1) {
                     tmem_ld_32x32(tS + 32, sv);
                     tmem_ld_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+                    if constexpr (!DS_TMEM) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty[s]));
+                    }
                 }
                 uint32_t packed[16];
                 if (masked) {
@@ -623,15 +656,25 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                     }
                 }
                 const int g32 = part * (HC / 32) + c;   // 32-column group of the tile: panel g32 >> 1, half-row g32 & 1
-                uint8_t* panel = dsrow + (g32 >> 1) * FA_TILE_BYTES;
+                if constexpr (DS_TMEM) {
+                    // over the first 16 columns of the group's own S columns (already in this thread's registers)
+                    tmem_st_32x16(tmem_S + s * 128 + lane_off + g32 * 32, packed);
+                } else {
+                    uint8_t* panel = dsrow + (g32 >> 1) * FA_TILE_BYTES;
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd) {
-                    const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(panel + chunk * 16) =
-                        make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
+                    for (int qd = 0; qd < 4; ++qd) {
+                        const int chunk = ((g32 & 1) * 4 + qd) ^ (r & 7);
+                        *reinterpret_cast<uint4*>(panel + chunk * 16) =
+                            make_uint4(packed[4 * qd], packed[4 * qd + 1], packed[4 * qd + 2], packed[4 * qd + 3]);
+                    }
                 }
             }
-            fence_proxy_async_smem();
+            if constexpr (DS_TMEM) {
+                tmem_st_wait();
+                tc_fence_before();
+            } else {
+                fence_proxy_async_smem();
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->ds_full[s]));
         }

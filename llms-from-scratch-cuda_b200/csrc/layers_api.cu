@@ -85,10 +85,14 @@ int configure_attention() {
     ATTN_SMEM(attn_bwd_dq_simt<__nv_bfloat16>, ATTN_DQ_SMEM);
     ATTN_SMEM(attn_bwd_dkv_simt<float>, ATTN_DKV_SMEM);
     ATTN_SMEM(attn_bwd_dkv_simt<__nv_bfloat16>, ATTN_DKV_SMEM);
-    ATTN_SMEM(attn_fwd_sm100<2>, FA_SMEM_BYTES);
-    ATTN_SMEM(attn_fwd_sm100<4>, FA_SMEM_BYTES);
-    ATTN_SMEM(attn_bwd_dq_sm100<2>, FB_DQ_SMEM_BYTES);
-    ATTN_SMEM(attn_bwd_dq_sm100<4>, FB_DQ_SMEM_BYTES);
+    ATTN_SMEM((attn_fwd_sm100<2, false>), FA_SMEM_BYTES);
+    ATTN_SMEM((attn_fwd_sm100<4, false>), FA_SMEM_BYTES);
+    ATTN_SMEM((attn_fwd_sm100<2, true>), FA_SMEM_BYTES);
+    ATTN_SMEM((attn_fwd_sm100<4, true>), FA_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dq_sm100<2, false>), FB_DQ_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dq_sm100<4, false>), FB_DQ_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dq_sm100<2, true>), FB_DQ_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dq_sm100<4, true>), FB_DQ_SMEM_BYTES);
     ATTN_SMEM(attn_bwd_dkv_sm100<2>, FB_DKV_SMEM_BYTES);
     ATTN_SMEM(attn_bwd_dkv_sm100<4>, FB_DKV_SMEM_BYTES);
 #undef ATTN_SMEM
@@ -159,6 +163,16 @@ int attn_row_threads() {   // B200_ATTN_ROW_THREADS: 0 (unset) = chosen per call
     return v;
 }
 
+// P (forward) and dS (dQ kernel) reach the tensor core as a tensor-memory operand; B200_ATTN_P_TMEM=0 sends them
+// through shared memory instead (T = 8192 forward 361 us instead of 322 us).
+bool attn_operand_in_tmem() {
+    static const bool on = [] {
+        const char* e = getenv("B200_ATTN_P_TMEM");
+        return !(e && atoi(e) == 0);
+    }();
+    return on;
+}
+
 int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
                      int B, int Tlen, int n_head, int n_kv_head, cudaStream_t stream) {
     b200_linear_ctx* ctx = b200_linear_default_ctx();
@@ -177,8 +191,13 @@ int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q,
     // B200_ATTN_ROW_THREADS=2|4 forces one.
     const int forced = attn_row_threads();
     const bool two = forced ? forced == 2 : Tlen < 2048;
-    if (two) launch_pdl(attn_fwd_sm100<2>, grid, 128 + 2 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
-    else launch_pdl(attn_fwd_sm100<4>, grid, 128 + 4 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+    if (attn_operand_in_tmem()) {
+        if (two) launch_pdl(attn_fwd_sm100<2, true>, grid, 128 + 2 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+        else launch_pdl(attn_fwd_sm100<4, true>, grid, 128 + 4 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+    } else {
+        if (two) launch_pdl(attn_fwd_sm100<2, false>, grid, 128 + 2 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+        else launch_pdl(attn_fwd_sm100<4, false>, grid, 128 + 4 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+    }
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }
 
@@ -226,11 +245,14 @@ int flash_backward_tc(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, c
     // two softmax threads per query row for the backward kernels (four measured 3-6 % slower at T = 512 and T = 8192)
     // unless B200_ATTN_ROW_THREADS=4 forces four
     const bool two = attn_row_threads() != 4;
+    const bool ts = attn_operand_in_tmem();
     if (two) {
-        launch_pdl(attn_bwd_dq_sm100<2>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        if (ts) launch_pdl(attn_bwd_dq_sm100<2, true>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        else launch_pdl(attn_bwd_dq_sm100<2, false>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
         launch_pdl(attn_bwd_dkv_sm100<2>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     } else {
-        launch_pdl(attn_bwd_dq_sm100<4>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        if (ts) launch_pdl(attn_bwd_dq_sm100<4, true>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        else launch_pdl(attn_bwd_dq_sm100<4, false>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
         launch_pdl(attn_bwd_dkv_sm100<4>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     }
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
