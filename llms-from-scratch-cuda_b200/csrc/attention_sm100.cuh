@@ -734,6 +734,7 @@ struct alignas(8) FbDkvCtrl {
     unsigned long long dp_full, dp_empty;
     unsigned long long pds_full[2], pds_empty[2];   // P and dS (bf16) in shared memory, double-buffered
     unsigned long long dkv_full;
+    unsigned long long stat_full[3];                // transposed form: the iteration's lse / delta are in shared memory
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -743,7 +744,13 @@ struct alignas(8) FbDkvCtrl {
 // softmax warps write P and dS as bf16 [query][key] tiles, and the tensor core reads those tiles as MN-major left
 // operands (their rows are the contraction): dV += P^T dO and dK += dS^T Q accumulate in TMEM over all iterations.
 // tmQ / tmdO: {n_head*64, T, B};  tmK / tmV / tmdK / tmdV: {n_kv_head*64, T, B};  boxes {64,128,1}.
-template <int NS>   // softmax threads per query row (2 or 4)
+// KT ("keys on the lanes"): the two score products are formed transposed, S^T = K Q^T and dP^T = V dO^T, so that a
+// thread owns a KEY row and P^T, dS^T have the keys along the TMEM lanes: written back as bf16 over the thread's own
+// S^T columns (P^T in the first, dS^T in the second 16 columns of each 32-column group) they are the tensor core's
+// left operands of dV += P^T dO and dK += dS^T Q straight from tensor memory.  No P / dS in shared memory: the
+// kernel's shared-memory traffic per iteration halves.  The per-query statistics (lse, delta) now vary along the
+// columns and come through a small double-buffered array in shared memory.
+template <int NS, bool KT>   // NS: softmax threads per row of the score tile (2 or 4)
 __global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -773,13 +780,14 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctrl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->s_empty[i]), (4 * NS));
+            mbar_init(smem_u32(&ctrl->s_empty[i]), KT ? 1 : (4 * NS));   // KT: freed by the tensor core after dV, dK
             mbar_init(smem_u32(&ctrl->pds_full[i]), (4 * NS));
             mbar_init(smem_u32(&ctrl->pds_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctrl->dp_full), 1);
         mbar_init(smem_u32(&ctrl->dp_empty), (4 * NS));
         mbar_init(smem_u32(&ctrl->dkv_full), 1);
+        for (int i = 0; i < 3; ++i) mbar_init(smem_u32(&ctrl->stat_full[i]), 4);
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
@@ -846,9 +854,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 if (issuer) {
                     const uint64_t descQ = umma_smem_desc(qaddr, 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
-                        umma_f16<1>(tmem_S + s * 128, descQ + ((k * UMMA_K * 2) >> 4), descK + ((k * UMMA_K * 2) >> 4), idesc_S,
-                                    k > 0 ? 1u : 0u);
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)   // S = Q K^T, or S^T = K Q^T (both operands K-major either way)
+                        umma_f16<1>(tmem_S + s * 128, (KT ? descK : descQ) + ((k * UMMA_K * 2) >> 4),
+                                    (KT ? descQ : descK) + ((k * UMMA_K * 2) >> 4), idesc_S, k > 0 ? 1u : 0u);
                     umma_commit(smem_u32(&ctrl->s_full[s]));
                 }
                 ok = mbar_wait(smem_u32(&ctrl->dp_empty), (it & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
@@ -858,9 +866,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 if (issuer) {
                     const uint64_t descdO = umma_smem_desc(qaddr + FA_TILE_BYTES, 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < FA_HD / UMMA_K; ++k)
-                        umma_f16<1>(tmem_dP, descdO + ((k * UMMA_K * 2) >> 4), descV + ((k * UMMA_K * 2) >> 4), idesc_S,
-                                    k > 0 ? 1u : 0u);
+                    for (int k = 0; k < FA_HD / UMMA_K; ++k)   // dP = dO V^T, or dP^T = V dO^T
+                        umma_f16<1>(tmem_dP, (KT ? descV : descdO) + ((k * UMMA_K * 2) >> 4),
+                                    (KT ? descdO : descV) + ((k * UMMA_K * 2) >> 4), idesc_S, k > 0 ? 1u : 0u);
                     umma_commit(smem_u32(&ctrl->dp_full));
                 }
             }
@@ -879,16 +887,30 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     const uint64_t descdS = umma_smem_desc(pbase + 2 * FA_TILE_BYTES, FA_TILE_BYTES, 1024);
                     const uint64_t descQm = umma_smem_desc(qaddr, 64 * 64 * 2, 1024);
                     const uint64_t descdOm = umma_smem_desc(qaddr + FA_TILE_BYTES, 64 * 64 * 2, 1024);
+                    if constexpr (KT) {
+                        constexpr uint32_t idesc_TS = umma_idesc(1, FA_BKV, FA_HD, 0, 1);   // left operand from TMEM, dO / Q MN-major
 #pragma unroll
-                    for (int k = 0; k < FA_BQ / UMMA_K; ++k)
-                        umma_f16<1>(tmem_dV, descP + ((k * UMMA_K * 128) >> 4), descdOm + ((k * UMMA_K * 128) >> 4), idesc_T,
-                                    (i > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < FA_BQ / UMMA_K; ++k)   // queries 16 k .. 16 k + 15: 8 packed columns of group k / 2
+                            umma_f16_ts(tmem_dV, tmem_S + s * 128 + (k >> 1) * 32 + (k & 1) * 8, descdOm + ((k * UMMA_K * 128) >> 4),
+                                        idesc_TS, (i > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < FA_BQ / UMMA_K; ++k)
-                        umma_f16<1>(tmem_dK, descdS + ((k * UMMA_K * 128) >> 4), descQm + ((k * UMMA_K * 128) >> 4), idesc_T,
-                                    (i > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(smem_u32(&ctrl->qdo_empty[st]));
-                    umma_commit(smem_u32(&ctrl->pds_empty[s]));
+                        for (int k = 0; k < FA_BQ / UMMA_K; ++k)
+                            umma_f16_ts(tmem_dK, tmem_S + s * 128 + (k >> 1) * 32 + 16 + (k & 1) * 8, descQm + ((k * UMMA_K * 128) >> 4),
+                                        idesc_TS, (i > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(smem_u32(&ctrl->qdo_empty[st]));
+                        umma_commit(smem_u32(&ctrl->s_empty[s]));   // P^T and dS^T lived in this S buffer
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < FA_BQ / UMMA_K; ++k)
+                            umma_f16<1>(tmem_dV, descP + ((k * UMMA_K * 128) >> 4), descdOm + ((k * UMMA_K * 128) >> 4), idesc_T,
+                                        (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int k = 0; k < FA_BQ / UMMA_K; ++k)
+                            umma_f16<1>(tmem_dK, descdS + ((k * UMMA_K * 128) >> 4), descQm + ((k * UMMA_K * 128) >> 4), idesc_T,
+                                        (i > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(smem_u32(&ctrl->qdo_empty[st]));
+                        umma_commit(smem_u32(&ctrl->pds_empty[s]));
+                    }
                     if (i == n_it - 1) umma_commit(smem_u32(&ctrl->dkv_full));
                 }
             }
@@ -912,6 +934,84 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         };
         float lse2_next = 0.f, delta_next = 0.f;
         if (n_it > 0) stats(0, lse2_next, delta_next);
+        if constexpr (KT) {
+            // keys on the lanes: this thread owns key row `key` of the tile and HC query columns of S^T and dP^T
+            // [3 buffers][lse2: 128 | delta: 128].  Three, not two: a thread that starts iteration it has seen S^T of
+            // iteration it - 1, which the tensor core forms only after every warp finished iteration it - 3 -- nothing
+            // later is guaranteed, so the buffer written at it must not be the one read at it - 2.
+            float* stat = reinterpret_cast<float*>(sPdS + 2 * FA_TILE_BYTES);
+            const int key = kt * FA_BKV + r;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int s = it & 1;
+                const int i = kt + it % n_q;
+                // the statistics of this iteration's 128 queries: the part-0 thread of a row publishes the pair it
+                // fetched one iteration ago (stats() indexes by r = query row here), everybody reads them by column
+                const int sb = it % 3;
+                if (part == 0) {
+                    stat[sb * 256 + r] = lse2_next;
+                    stat[sb * 256 + 128 + r] = delta_next;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctrl->stat_full[sb]));
+                    if (it + 1 < n_it) stats(it + 1, lse2_next, delta_next);
+                }
+                ok = mbar_wait(smem_u32(&ctrl->s_full[s]), (it >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
+                     mbar_wait(smem_u32(&ctrl->dp_full), it & 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_F) &&
+                     mbar_wait(smem_u32(&ctrl->stat_full[sb]), (it / 3) & 1, abort_flag, p.status, DEV_TIMEOUT_PEER);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tS = tmem_S + s * 128 + lane_off + part * HC, tP = tmem_dP + lane_off + part * HC;
+                const bool masked = i == kt || (kt + 1) * FA_BKV > p.T || (i + 1) * FA_BQ > p.T;
+                const int q0 = i * FA_BQ + part * HC;            // first query position of this thread's columns
+                const float4* lse4 = reinterpret_cast<const float4*>(stat + sb * 256 + part * HC);
+                const float4* del4 = reinterpret_cast<const float4*>(stat + sb * 256 + 128 + part * HC);
+                uint32_t dv[HC], sv[32];
+#pragma unroll
+                for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tP + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[c * 32]));
+                tmem_ld_32x32(tS, sv);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->dp_empty));
+#pragma unroll
+                for (int c = 0; c < HC / 32; ++c) {
+                    if (c == 1) {
+                        tmem_ld_32x32(tS + 32, sv);
+                        tmem_ld_wait();
+                    }
+                    uint32_t pp[16], pd[16];
+#pragma unroll
+                    for (int e4 = 0; e4 < 8; ++e4) {              // four queries at a time: one 16-byte read of each statistic
+                        const float4 l4 = lse4[c * 8 + e4], d4 = del4[c * 8 + e4];
+                        const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq4[4] = {d4.x, d4.y, d4.z, d4.w};
+                        float pv[4], dsv[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int e = e4 * 4 + u;
+                            float x = fmaf(__uint_as_float(sv[e]), p.scale_log2e, -lq[u]);
+                            if (masked) {
+                                const int query = q0 + c * 32 + e;
+                                if (key > query || key >= p.T || query >= p.T) x = -INFINITY;
+                            }
+                            pv[u] = fa_exp2(x);
+                            dsv[u] = pv[u] * (__uint_as_float(dv[c * 32 + e]) - dq4[u]);
+                        }
+                        pp[e4 * 2] = pack_bf16x2(pv[0], pv[1]);
+                        pp[e4 * 2 + 1] = pack_bf16x2(pv[2], pv[3]);
+                        pd[e4 * 2] = pack_bf16x2(dsv[0], dsv[1]);
+                        pd[e4 * 2 + 1] = pack_bf16x2(dsv[2], dsv[3]);
+                    }
+                    // P^T over the first, dS^T over the second 16 columns of this 32-column group of S^T (already in registers)
+                    const int g32 = part * (HC / 32) + c;
+                    tmem_st_32x16(tmem_S + s * 128 + lane_off + g32 * 32, pp);
+                    tmem_st_32x16(tmem_S + s * 128 + lane_off + g32 * 32 + 16, pd);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctrl->pds_full[s]));
+            }
+        } else {
         for (int it = 0; it < n_it && ok; ++it) {
             const int s = it & 1;
             const int i = kt + it % n_q;
@@ -986,6 +1086,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->pds_full[s]));
+        }
         }
         if (ok) {
             ok = mbar_wait(smem_u32(&ctrl->dkv_full), 0, abort_flag, p.status, DEV_TIMEOUT_TMEM_F);

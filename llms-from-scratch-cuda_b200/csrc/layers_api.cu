@@ -93,8 +93,10 @@ int configure_attention() {
     ATTN_SMEM((attn_bwd_dq_sm100<4, false>), FB_DQ_SMEM_BYTES);
     ATTN_SMEM((attn_bwd_dq_sm100<2, true>), FB_DQ_SMEM_BYTES);
     ATTN_SMEM((attn_bwd_dq_sm100<4, true>), FB_DQ_SMEM_BYTES);
-    ATTN_SMEM(attn_bwd_dkv_sm100<2>, FB_DKV_SMEM_BYTES);
-    ATTN_SMEM(attn_bwd_dkv_sm100<4>, FB_DKV_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dkv_sm100<2, false>), FB_DKV_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dkv_sm100<4, false>), FB_DKV_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dkv_sm100<2, true>), FB_DKV_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dkv_sm100<4, true>), FB_DKV_SMEM_BYTES);
 #undef ATTN_SMEM
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -154,23 +156,25 @@ bool use_tensor_cores(const void* a, const void* b, const void* c, const void* d
              reinterpret_cast<uintptr_t>(d)) & 15) == 0;
 }
 
+// The three switches below are read at every call (a getenv beside a kernel launch), so that a test can flip them.
 int attn_row_threads() {   // B200_ATTN_ROW_THREADS: 0 (unset) = chosen per call
-    static const int v = [] {
-        const char* e = getenv("B200_ATTN_ROW_THREADS");
-        const int n = e ? atoi(e) : 0;
-        return (n == 2 || n == 4) ? n : 0;
-    }();
-    return v;
+    const char* e = getenv("B200_ATTN_ROW_THREADS");
+    const int n = e ? atoi(e) : 0;
+    return (n == 2 || n == 4) ? n : 0;
+}
+// B200_ATTN_DKV_TRANSPOSED=1: the dK / dV kernel in its "keys on the lanes" form (S^T, dP^T; P^T and dS^T as
+// tensor-memory operands).  Correct, but measured slower than the shared-memory form (T = 8192 backward 1013 us
+// against 918 us), so it is off unless asked for.
+bool attn_dkv_transposed() {
+    const char* e = getenv("B200_ATTN_DKV_TRANSPOSED");
+    return e && atoi(e) != 0;
 }
 
 // P (forward) and dS (dQ kernel) reach the tensor core as a tensor-memory operand; B200_ATTN_P_TMEM=0 sends them
 // through shared memory instead (T = 8192 forward 361 us instead of 322 us).
 bool attn_operand_in_tmem() {
-    static const bool on = [] {
-        const char* e = getenv("B200_ATTN_P_TMEM");
-        return !(e && atoi(e) == 0);
-    }();
-    return on;
+    const char* e = getenv("B200_ATTN_P_TMEM");
+    return !(e && atoi(e) == 0);
 }
 
 int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v,
@@ -245,15 +249,17 @@ int flash_backward_tc(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, c
     // two softmax threads per query row for the backward kernels (four measured 3-6 % slower at T = 512 and T = 8192)
     // unless B200_ATTN_ROW_THREADS=4 forces four
     const bool two = attn_row_threads() != 4;
-    const bool ts = attn_operand_in_tmem();
+    const bool ts = attn_operand_in_tmem(), kt = attn_dkv_transposed();
     if (two) {
         if (ts) launch_pdl(attn_bwd_dq_sm100<2, true>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
         else launch_pdl(attn_bwd_dq_sm100<2, false>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
-        launch_pdl(attn_bwd_dkv_sm100<2>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+        if (kt) launch_pdl(attn_bwd_dkv_sm100<2, true>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+        else launch_pdl(attn_bwd_dkv_sm100<2, false>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     } else {
         if (ts) launch_pdl(attn_bwd_dq_sm100<4, true>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
         else launch_pdl(attn_bwd_dq_sm100<4, false>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
-        launch_pdl(attn_bwd_dkv_sm100<4>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+        if (kt) launch_pdl(attn_bwd_dkv_sm100<4, true>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+        else launch_pdl(attn_bwd_dkv_sm100<4, false>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     }
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
 }

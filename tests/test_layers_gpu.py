@@ -85,6 +85,33 @@ def _attention_inputs(dt, B, T, C, nh, nkv):
     return inp, ws, dout
 
 
+@pytest.mark.parametrize("env", [{"B200_ATTN_ROW_THREADS": "4"}, {"B200_ATTN_ROW_THREADS": "2"}, {"B200_ATTN_P_TMEM": "0"},
+                                 {"B200_ATTN_DKV_TRANSPOSED": "1"}, {"B200_ATTN_DKV_TRANSPOSED": "1", "B200_ATTN_ROW_THREADS": "4"}])
+@pytest.mark.parametrize("B,T,nh,nkv", [(2, 300, 6, 2), (1, 2100, 3, 1)])
+def test_fused_attention_kernel_variants(layers, handle, monkeypatch, env, B, T, nh, nkv):
+    """The tensor-core attention kernels in their other forms (two / four softmax threads per row, P and dS through shared
+    memory instead of tensor memory, the dK / dV kernel with the keys on the TMEM lanes) against float64."""
+    from oracle import layers_oracle as lo
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    dt, hd = torch.bfloat16, 64
+    q, k, v = rnd((B * T, nh * hd), 1, dt), rnd((B * T, nkv * hd), 2, dt), rnd((B * T, nkv * hd), 3, dt)
+    dctx = rnd((B * T, nh * hd), 4, dt)
+    qd, kd, vd, dd = (t.to(DEV) for t in (q, k, v, dctx))
+    ctx = torch.empty(B * T, nh * hd, device=DEV, dtype=dt)
+    lse = torch.empty(B, nh, T, device=DEV, dtype=torch.float32)
+    layers.flash_attention_forward(ctx, lse, qd, kd, vd, B, T, nh, nkv, hd)
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    layers.flash_attention_backward(dq, dk, dv, dd, qd, kd, vd, lse, B, T, nh, nkv, hd, context=ctx)
+    torch.cuda.synchronize()
+    c64, l64 = lo.attention_core(q.double(), k.double(), v.double(), B, T, nh, nkv, hd)
+    assert rel(ctx, c64) <= TOL[dt]
+    assert (lse.double().cpu() - l64).abs().max().item() <= 1e-4
+    g64 = lo.attention_core_grads(dctx.double(), q.double(), k.double(), v.double(), B, T, nh, nkv, hd)
+    for got, want, name in zip((dq, dk, dv), g64, "qkv"):
+        assert rel(got, want) <= TOL[dt], (env, name, rel(got, want))
+
+
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("B,T,C,nh,nkv,theta", [(2, 256, 768, 12, 4, 10000.0), (1, 64, 256, 4, 2, 500000.0)])
 def test_attention_layer_against_float64(layers, handle, dt, B, T, C, nh, nkv, theta):
