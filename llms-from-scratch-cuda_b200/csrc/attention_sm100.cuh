@@ -35,9 +35,13 @@ constexpr int FA_BKV = 128;       // key/value rows per tile
 constexpr int FA_HD = 64;         // head dimension
 // threads per CTA: 128 + 128 NS: warps 0-3 = producer, MMA issuer, TMEM allocator, idle; then 4 NS softmax / epilogue warps
 constexpr int FA_TILE_BYTES = 128 * 64 * 2;                 // one 128 x 64 bf16 tile, 128-byte rows
-constexpr int FA_KV_STAGES = 3;   // K/V tiles in flight: a stage is free again only after its P V product
+constexpr int FA_KV_STAGES = 3;      // K/V tiles in flight: a stage is free again only after its P V product
+constexpr int FA_KV_STAGES_TS = 5;   // ... when P / dS go through tensor memory and their shared-memory buffers are stages instead
+constexpr int FA_KV_STAGES_MAX = 5;
 constexpr int FA_SMEM_BYTES = 5120 /*control*/ + FA_TILE_BYTES /*Q*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K,V stages*/ +
                               2 * 2 * FA_TILE_BYTES /*P x 2: two 64-column panels each*/ + 1024 /*alignment*/;
+// P through tensor memory: five K/V stages, one tile of output staging where the P buffers were
+constexpr int FA_SMEM_BYTES_TS = 5120 + FA_TILE_BYTES + FA_KV_STAGES_TS * 2 * FA_TILE_BYTES + FA_TILE_BYTES + 1024;
 constexpr int FA_TMEM_COLS = 512;  // S: 2 x 128 columns, O: 2 x 64 columns (forward), dP / dQ / dK / dV (backward)
 constexpr float FA_RESCALE_STEP = 8.0f;   // a row's reference maximum moves only when the true maximum has grown by 2^8
 
@@ -50,7 +54,7 @@ struct FaParams {
 
 struct alignas(8) FaCtrl {
     unsigned long long q_full;
-    unsigned long long kv_full[FA_KV_STAGES], kv_empty[FA_KV_STAGES];
+    unsigned long long kv_full[FA_KV_STAGES_MAX], kv_empty[FA_KV_STAGES_MAX];
     unsigned long long s_full[2], s_empty[2];
     unsigned long long p_full[2], p_empty[2];
     unsigned long long pv_done;        // the P V products of one more key tile have retired (one phase per tile)
@@ -80,12 +84,13 @@ template <int NS, bool P_TMEM>
 __global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const FaParams p) {
+    constexpr int STAGES = P_TMEM ? FA_KV_STAGES_TS : FA_KV_STAGES;
     extern __shared__ uint8_t fa_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     FaCtrl* ctrl = reinterpret_cast<FaCtrl*>(smem);
     uint8_t* sQ = smem + FA_CTRL_BYTES;
     uint8_t* sKV = sQ + FA_TILE_BYTES;            // stage s: [K tile | V tile]
-    uint8_t* sP = sKV + FA_KV_STAGES * 2 * FA_TILE_BYTES;   // buffer b: [columns 0..63 | columns 64..127]
+    uint8_t* sP = sKV + STAGES * 2 * FA_TILE_BYTES;   // buffer b: [columns 0..63 | columns 64..127]
     volatile int* abort_flag = &ctrl->abort_flag;
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -99,7 +104,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if (warp == 1) {
         if (lane == 0) {
             mbar_init(smem_u32(&ctrl->q_full), 1);
-            for (int i = 0; i < FA_KV_STAGES; ++i) {
+            for (int i = 0; i < STAGES; ++i) {
                 mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
                 mbar_init(smem_u32(&ctrl->kv_empty[i]), 1);
             }
@@ -141,8 +146,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
-            const int s = j % FA_KV_STAGES;
-            ok = mbar_wait(smem_u32(&ctrl->kv_empty[s]), ((j / FA_KV_STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            const int s = j % STAGES;
+            ok = mbar_wait(smem_u32(&ctrl->kv_empty[s]), ((j / STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (issuer) {
@@ -163,8 +168,8 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         for (int j = 0; j <= n_kv && ok; ++j) {
             if (j < n_kv) {   // S_j = Q K_j^T
-                const int s = j & 1, st = j % FA_KV_STAGES;
-                ok = mbar_wait(smem_u32(&ctrl->kv_full[st]), (j / FA_KV_STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                const int s = j & 1, st = j % STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->kv_full[st]), (j / STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
                      mbar_wait(smem_u32(&ctrl->s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -179,7 +184,7 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
             if (j >= 1) {     // O_h += P_ih V_ih for the tile before, h = the two 64-column halves of the key tile
-                const int i = j - 1, s = i & 1, st = i % FA_KV_STAGES;
+                const int i = j - 1, s = i & 1, st = i % STAGES;
                 ok = mbar_wait(smem_u32(&ctrl->p_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -411,6 +416,9 @@ attn_fwd_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 constexpr int FB_DQ_SMEM_BYTES = 1024 + 2 * FA_TILE_BYTES /*Q, dO*/ + FA_KV_STAGES * 2 * FA_TILE_BYTES /*K, V stages*/ +
                                  2 * 2 * FA_TILE_BYTES /*dS x 2*/ + 1024;
 
+// dS through tensor memory: five K/V stages, one tile of output staging where the dS buffers were
+constexpr int FB_DQ_SMEM_BYTES_TS = 1024 + 2 * FA_TILE_BYTES + FA_KV_STAGES_TS * 2 * FA_TILE_BYTES + FA_TILE_BYTES + 1024;
+
 struct FbParams {
     int B, T, n_head, n_kv_head;
     float scale_log2e;     // log2(e) / sqrt(head_dim)
@@ -422,7 +430,7 @@ struct FbParams {
 
 struct alignas(8) FbDqCtrl {
     unsigned long long q_full;
-    unsigned long long kv_full[FA_KV_STAGES], kv_empty[FA_KV_STAGES];
+    unsigned long long kv_full[FA_KV_STAGES_MAX], kv_empty[FA_KV_STAGES_MAX];
     unsigned long long s_full[2], s_empty[2];      // S double-buffered in TMEM
     unsigned long long dp_full, dp_empty;          // dP single-buffered
     unsigned long long ds_full[2], ds_empty[2];    // dS (bf16) double-buffered in shared memory
@@ -442,13 +450,14 @@ __global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                   const __grid_constant__ CUtensorMap tmdQ, const FbParams p) {
+    constexpr int STAGES = DS_TMEM ? FA_KV_STAGES_TS : FA_KV_STAGES;
     extern __shared__ uint8_t fa_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     FbDqCtrl* ctrl = reinterpret_cast<FbDqCtrl*>(smem);
     uint8_t* sQ = smem + 1024;
     uint8_t* sdO = sQ + FA_TILE_BYTES;
     uint8_t* sKV = sdO + FA_TILE_BYTES;                       // stage s: [K tile | V tile]
-    uint8_t* sdS = sKV + FA_KV_STAGES * 2 * FA_TILE_BYTES;    // buffer b: [key columns 0..63 | 64..127]
+    uint8_t* sdS = sKV + STAGES * 2 * FA_TILE_BYTES;    // buffer b: [key columns 0..63 | 64..127]
     volatile int* abort_flag = &ctrl->abort_flag;
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -459,7 +468,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (warp == 1 && lane == 0) {
         mbar_init(smem_u32(&ctrl->q_full), 1);
-        for (int i = 0; i < FA_KV_STAGES; ++i) {
+        for (int i = 0; i < STAGES; ++i) {
             mbar_init(smem_u32(&ctrl->kv_full[i]), 1);
             mbar_init(smem_u32(&ctrl->kv_empty[i]), 1);
         }
@@ -503,8 +512,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
-            const int s = j % FA_KV_STAGES;
-            ok = mbar_wait(smem_u32(&ctrl->kv_empty[s]), ((j / FA_KV_STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            const int s = j % STAGES;
+            ok = mbar_wait(smem_u32(&ctrl->kv_empty[s]), ((j / STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (issuer) {
@@ -526,8 +535,8 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         ok = __all_sync(0xffffffffu, ok);
         for (int j = 0; j <= n_kv && ok; ++j) {
             if (j < n_kv) {   // S_j = Q K_j^T and dP_j = dO V_j^T
-                const int s = j & 1, st = j % FA_KV_STAGES;
-                ok = mbar_wait(smem_u32(&ctrl->kv_full[st]), (j / FA_KV_STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                const int s = j & 1, st = j % STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->kv_full[st]), (j / STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
                      mbar_wait(smem_u32(&ctrl->s_empty[s]), ((j >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -555,7 +564,7 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
             }
             if (j >= 1) {     // dQ += dS_i K_i for the tile before
-                const int i = j - 1, s = i & 1, st = i % FA_KV_STAGES;
+                const int i = j - 1, s = i & 1, st = i % STAGES;
                 ok = mbar_wait(smem_u32(&ctrl->ds_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -724,12 +733,17 @@ attn_bwd_dq_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 }
 
 constexpr int FB_QDO_STAGES = 2;
+constexpr int FB_QDO_STAGES_KT = 4;   // transposed form: no P / dS in shared memory, two more Q / dO stages instead
+constexpr int FB_QDO_STAGES_MAX = 4;
 constexpr int FB_DKV_SMEM_BYTES = 1024 + 2 * FA_TILE_BYTES /*K, V*/ + FB_QDO_STAGES * 2 * FA_TILE_BYTES /*Q, dO stages*/ +
                                   2 * 4 * FA_TILE_BYTES /*(P, dS) x 2, two 64-column panels each*/ + 1024;
 
+// transposed form: four Q / dO stages; where P / dS were: two tiles of output staging and the 3 KB of row statistics
+constexpr int FB_DKV_SMEM_BYTES_KT = 1024 + 2 * FA_TILE_BYTES + 4 * 2 * FA_TILE_BYTES + 2 * FA_TILE_BYTES + 4096 + 1024;
+
 struct alignas(8) FbDkvCtrl {
     unsigned long long kv_full;
-    unsigned long long qdo_full[FB_QDO_STAGES], qdo_empty[FB_QDO_STAGES];
+    unsigned long long qdo_full[FB_QDO_STAGES_MAX], qdo_empty[FB_QDO_STAGES_MAX];
     unsigned long long s_full[2], s_empty[2];
     unsigned long long dp_full, dp_empty;
     unsigned long long pds_full[2], pds_empty[2];   // P and dS (bf16) in shared memory, double-buffered
@@ -755,13 +769,14 @@ __global__ void __launch_bounds__(128 + NS * 128, 1)
 attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV, const FbParams p) {
+    constexpr int STAGES = KT ? FB_QDO_STAGES_KT : FB_QDO_STAGES;
     extern __shared__ uint8_t fa_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     FbDkvCtrl* ctrl = reinterpret_cast<FbDkvCtrl*>(smem);
     uint8_t* sK = smem + 1024;
     uint8_t* sV = sK + FA_TILE_BYTES;
     uint8_t* sQdO = sV + FA_TILE_BYTES;                        // stage s: [Q tile | dO tile]
-    uint8_t* sPdS = sQdO + FB_QDO_STAGES * 2 * FA_TILE_BYTES;  // buffer b: [P: 2 panels | dS: 2 panels]
+    uint8_t* sPdS = sQdO + STAGES * 2 * FA_TILE_BYTES;  // buffer b: [P: 2 panels | dS: 2 panels]
     volatile int* abort_flag = &ctrl->abort_flag;
 
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
@@ -774,7 +789,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     if (warp == 1 && lane == 0) {
         mbar_init(smem_u32(&ctrl->kv_full), 1);
-        for (int i = 0; i < FB_QDO_STAGES; ++i) {
+        for (int i = 0; i < STAGES; ++i) {
             mbar_init(smem_u32(&ctrl->qdo_full[i]), 1);
             mbar_init(smem_u32(&ctrl->qdo_empty[i]), 1);
         }
@@ -820,9 +835,9 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         bool ok = true;
         for (int it = 0; it < n_it && ok; ++it) {
-            const int s = it % FB_QDO_STAGES;
+            const int s = it % STAGES;
             const int h = kvh * ratio + it / n_q, i = kt + it % n_q;
-            ok = mbar_wait(smem_u32(&ctrl->qdo_empty[s]), ((it / FB_QDO_STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
+            ok = mbar_wait(smem_u32(&ctrl->qdo_empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_EMPTY);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (issuer) {
@@ -844,8 +859,8 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         for (int it = 0; it <= n_it && ok; ++it) {
             if (it < n_it) {   // S = Q K^T, dP = dO V^T
-                const int s = it & 1, st = it % FB_QDO_STAGES;
-                ok = mbar_wait(smem_u32(&ctrl->qdo_full[st]), (it / FB_QDO_STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
+                const int s = it & 1, st = it % STAGES;
+                ok = mbar_wait(smem_u32(&ctrl->qdo_full[st]), (it / STAGES) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL) &&
                      mbar_wait(smem_u32(&ctrl->s_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag, p.status, DEV_TIMEOUT_TMEM_E);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
@@ -873,7 +888,7 @@ attn_bwd_dkv_sm100(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
             }
             if (it >= 1) {     // dV += P^T dO, dK += dS^T Q for the iteration before
-                const int i = it - 1, s = i & 1, st = i % FB_QDO_STAGES;
+                const int i = it - 1, s = i & 1, st = i % STAGES;
                 ok = mbar_wait(smem_u32(&ctrl->pds_full[s]), (i >> 1) & 1, abort_flag, p.status, DEV_TIMEOUT_FULL);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;

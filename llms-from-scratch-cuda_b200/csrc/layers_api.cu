@@ -87,16 +87,16 @@ int configure_attention() {
     ATTN_SMEM(attn_bwd_dkv_simt<__nv_bfloat16>, ATTN_DKV_SMEM);
     ATTN_SMEM((attn_fwd_sm100<2, false>), FA_SMEM_BYTES);
     ATTN_SMEM((attn_fwd_sm100<4, false>), FA_SMEM_BYTES);
-    ATTN_SMEM((attn_fwd_sm100<2, true>), FA_SMEM_BYTES);
-    ATTN_SMEM((attn_fwd_sm100<4, true>), FA_SMEM_BYTES);
+    ATTN_SMEM((attn_fwd_sm100<2, true>), FA_SMEM_BYTES_TS);
+    ATTN_SMEM((attn_fwd_sm100<4, true>), FA_SMEM_BYTES_TS);
     ATTN_SMEM((attn_bwd_dq_sm100<2, false>), FB_DQ_SMEM_BYTES);
     ATTN_SMEM((attn_bwd_dq_sm100<4, false>), FB_DQ_SMEM_BYTES);
-    ATTN_SMEM((attn_bwd_dq_sm100<2, true>), FB_DQ_SMEM_BYTES);
-    ATTN_SMEM((attn_bwd_dq_sm100<4, true>), FB_DQ_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dq_sm100<2, true>), FB_DQ_SMEM_BYTES_TS);
+    ATTN_SMEM((attn_bwd_dq_sm100<4, true>), FB_DQ_SMEM_BYTES_TS);
     ATTN_SMEM((attn_bwd_dkv_sm100<2, false>), FB_DKV_SMEM_BYTES);
     ATTN_SMEM((attn_bwd_dkv_sm100<4, false>), FB_DKV_SMEM_BYTES);
-    ATTN_SMEM((attn_bwd_dkv_sm100<2, true>), FB_DKV_SMEM_BYTES);
-    ATTN_SMEM((attn_bwd_dkv_sm100<4, true>), FB_DKV_SMEM_BYTES);
+    ATTN_SMEM((attn_bwd_dkv_sm100<2, true>), FB_DKV_SMEM_BYTES_KT);
+    ATTN_SMEM((attn_bwd_dkv_sm100<4, true>), FB_DKV_SMEM_BYTES_KT);
 #undef ATTN_SMEM
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -196,8 +196,8 @@ int flash_forward_tc(__nv_bfloat16* context, float* lse, const __nv_bfloat16* q,
     const int forced = attn_row_threads();
     const bool two = forced ? forced == 2 : Tlen < 2048;
     if (attn_operand_in_tmem()) {
-        if (two) launch_pdl(attn_fwd_sm100<2, true>, grid, 128 + 2 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
-        else launch_pdl(attn_fwd_sm100<4, true>, grid, 128 + 4 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
+        if (two) launch_pdl(attn_fwd_sm100<2, true>, grid, 128 + 2 * 128, FA_SMEM_BYTES_TS, stream, tmQ, tmK, tmV, tmO, p);
+        else launch_pdl(attn_fwd_sm100<4, true>, grid, 128 + 4 * 128, FA_SMEM_BYTES_TS, stream, tmQ, tmK, tmV, tmO, p);
     } else {
         if (two) launch_pdl(attn_fwd_sm100<2, false>, grid, 128 + 2 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
         else launch_pdl(attn_fwd_sm100<4, false>, grid, 128 + 4 * 128, FA_SMEM_BYTES, stream, tmQ, tmK, tmV, tmO, p);
@@ -251,14 +251,14 @@ int flash_backward_tc(__nv_bfloat16* dq, __nv_bfloat16* dk, __nv_bfloat16* dv, c
     const bool two = attn_row_threads() != 4;
     const bool ts = attn_operand_in_tmem(), kt = attn_dkv_transposed();
     if (two) {
-        if (ts) launch_pdl(attn_bwd_dq_sm100<2, true>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        if (ts) launch_pdl(attn_bwd_dq_sm100<2, true>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES_TS, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
         else launch_pdl(attn_bwd_dq_sm100<2, false>, dim3(n_head, B, tiles), 128 + 2 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
-        if (kt) launch_pdl(attn_bwd_dkv_sm100<2, true>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+        if (kt) launch_pdl(attn_bwd_dkv_sm100<2, true>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES_KT, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
         else launch_pdl(attn_bwd_dkv_sm100<2, false>, dim3(n_kv_head, B, tiles), 128 + 2 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     } else {
-        if (ts) launch_pdl(attn_bwd_dq_sm100<4, true>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
+        if (ts) launch_pdl(attn_bwd_dq_sm100<4, true>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES_TS, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
         else launch_pdl(attn_bwd_dq_sm100<4, false>, dim3(n_head, B, tiles), 128 + 4 * 128, FB_DQ_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdQ, p);
-        if (kt) launch_pdl(attn_bwd_dkv_sm100<4, true>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
+        if (kt) launch_pdl(attn_bwd_dkv_sm100<4, true>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES_KT, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
         else launch_pdl(attn_bwd_dkv_sm100<4, false>, dim3(n_kv_head, B, tiles), 128 + 4 * 128, FB_DKV_SMEM_BYTES, stream, tmQ, tmdO, tmK, tmV, tmdK, tmdV, p);
     }
     return cudaGetLastError() == cudaSuccess ? B200_OK : B200_E_CUDA;
