@@ -990,6 +990,8 @@ def run_attention(args):
 def main():
     # stdout carries the one JSON line: whatever NCCL prints at its debug level (a version banner, warnings) goes to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":   # that level's banner is a bare printf to stdout
+        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None, help="profile mode: <projection>:<fwd_nn|dgrad_nt|wgrad_tn>")
     ap.add_argument("--tokens", type=int, default=2048)
