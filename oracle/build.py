@@ -106,12 +106,12 @@ def build_train(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=False
         subprocess.run(common + ["-x", "cu", "-c", src, "-o", obj], check=True)
         objs.append(obj)
     matmul_obj = objs.pop()
-    subprocess.run(["nvcc", "-o", ref_bin] + objs + [matmul_obj, "-lcublas",
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-o", ref_bin] + objs + [matmul_obj, "-lcublas",
                                                     "-Xlinker", "-rpath=/usr/local/cuda/lib64"], check=True)
-    subprocess.run(["nvcc", "-o", our_bin] + objs + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim",
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-o", our_bin] + objs + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim",
                    "-Xlinker", "-rpath=$ORIGIN/../../llms-from-scratch-cuda_b200"], check=True)
     slim = [o for o in objs if os.path.basename(o)[:-2] not in LAYER_SOURCES]
-    subprocess.run(["nvcc", "-o", layers_bin] + slim + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim",
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-o", layers_bin] + slim + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim",
                    "-Xlinker", "-rpath=$ORIGIN/../../llms-from-scratch-cuda_b200"], check=True)
     return ref_bin, our_bin
 
@@ -152,12 +152,12 @@ def build_train_dp(reference=DEFAULT_REFERENCE, model="llama2-mistral", force=Fa
                     "-x", "cu", "-c", driver, "-o", drv_obj], check=True)
     rpath = "-rpath=$ORIGIN/../../llms-from-scratch-cuda_b200"
     slim = [o for o in objs if os.path.basename(o)[:-2] not in LAYER_SOURCES]
-    subprocess.run(["nvcc", "-o", out, drv_obj] + slim + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim", "-lnccl",
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out, drv_obj] + slim + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim", "-lnccl",
                    "-Xlinker", rpath], check=True)
-    subprocess.run(["nvcc", "-o", out_gemm, drv_obj] + objs + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim", "-lnccl",
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out_gemm, drv_obj] + objs + ["-L", pkg, "-lb200_linear", "-lb200_cublas_shim", "-lnccl",
                    "-Xlinker", rpath], check=True)
     # the reference's own matmul.o comes first: its matmul_forward / matmul_backward win over the library's
-    subprocess.run(["nvcc", "-o", out_ref, drv_obj] + objs + [os.path.join(obj_dir, "matmul.cu.o"), "-L", pkg, "-lb200_linear",
+    subprocess.run(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out_ref, drv_obj] + objs + [os.path.join(obj_dir, "matmul.cu.o"), "-L", pkg, "-lb200_linear",
                    "-lcublas", "-lnccl", "-Xlinker", rpath, "-Xlinker", "-rpath=/usr/local/cuda/lib64"], check=True)
     return out, out_ref
 
