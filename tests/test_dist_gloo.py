@@ -76,6 +76,13 @@ def _worker(rank, world, port, q):
         ok_loss = torch.allclose(loss_rows.double(), ref_loss, atol=1e-4)
         ok_d = torch.allclose(d_local.double(), ref_d[:, start:start + size], atol=1e-6)
         ok_dx = torch.allclose(dx, ref_dx, atol=1e-5)
+        # the same with the per-shard statistics handed in (as the LM-head GEMM's epilogue delivers them): the
+        # statistics pass is skipped, the exchange and the result are unchanged
+        logits_r = (x @ w_r).float()
+        pre = HostShardOps.stats(logits_r, targets, start)
+        loss2, d2 = d.vocab_parallel_cross_entropy(logits_r, targets, start, ops=HostShardOps, stats=pre)
+        ok_loss = ok_loss and torch.equal(loss2, loss_rows)
+        ok_d = ok_d and torch.equal(d2, d_local)
         # dW buckets: every rank contributes rank+1; the sum is world*(world+1)/2
         b = d.GradBuckets([(4, 6), (3, 5)], torch.float32, "cpu")
         for view in b.views:
