@@ -428,8 +428,9 @@ int ensure_counters(b200_linear_ctx* ctx, int n, int set = 0) {
     return B200_OK;
 }
 
-template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS>
-int launch_one(b200_linear_ctx* ctx, const GemmGroupMaps& gx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
+// EPI = 0: one product (gx is GemmNoMaps); EPI = 3: grouped launch (gx carries the other products' maps)
+template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS, int EPI>
+int launch_one(b200_linear_ctx* ctx, const typename GemmExtraMaps<EPI>::type& gx, const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmD,
                const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
     using Cfg = TileCfg<BN, CTAS>;
     if (gp.ksplit > 1) {  // the receive space of the cluster exchange must fit the pipeline stages
@@ -440,7 +441,7 @@ int launch_one(b200_linear_ctx* ctx, const GemmGroupMaps& gx, const CUtensorMap&
     }
     // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the function
     static bool configured[kMaxDevices] = {};
-    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, BETA1, CTAS>;
+    auto kern = gemm_bf16_sm100<BN, P_MN, Q_MN, BETA1, CTAS, EPI>;
     if (!configured[ctx->device]) {
         CU_TRY(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured[ctx->device] = true;
@@ -466,33 +467,33 @@ int launch_one(b200_linear_ctx* ctx, const GemmGroupMaps& gx, const CUtensorMap&
     return B200_OK;
 }
 
-template <bool P_MN, bool Q_MN, bool BETA1>
-int launch_bn(b200_linear_ctx* ctx, const GemmGroupMaps& gx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
+template <bool P_MN, bool Q_MN, bool BETA1, int EPI>
+int launch_bn(b200_linear_ctx* ctx, const typename GemmExtraMaps<EPI>::type& gx, int bn, int ctas, const CUtensorMap& tmP, const CUtensorMap& tmQ,
               const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
     if (ctas == 2) {
         switch (bn) {
-            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
-            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+            case 256: return launch_one<256, P_MN, Q_MN, BETA1, 2, EPI>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+            case 128: return launch_one<128, P_MN, Q_MN, BETA1, 2, EPI>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
             default: return B200_E_BADARG;
         }
     }
     switch (bn) {
-        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
-        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
-        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
-        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 256: return launch_one<256, P_MN, Q_MN, BETA1, 1, EPI>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 192: return launch_one<192, P_MN, Q_MN, BETA1, 1, EPI>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 128: return launch_one<128, P_MN, Q_MN, BETA1, 1, EPI>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
+        case 64: return launch_one<64, P_MN, Q_MN, BETA1, 1, EPI>(ctx, gx, tmP, tmQ, tmD, tmD32, gp, grid);
         default: return B200_E_BADARG;
     }
 }
 
-template <bool P_MN, bool Q_MN>
-int launch_beta(b200_linear_ctx* ctx, const GemmGroupMaps& gx, int bn, int ctas, int beta1, const CUtensorMap& tmP,
+template <bool P_MN, bool Q_MN, int EPI>
+int launch_beta(b200_linear_ctx* ctx, const typename GemmExtraMaps<EPI>::type& gx, int bn, int ctas, int beta1, const CUtensorMap& tmP,
                 const CUtensorMap& tmQ, const CUtensorMap& tmD, const CUtensorMap& tmD32, const GemmParams& gp, int grid) {
-    return beta1 ? launch_bn<P_MN, Q_MN, true>(ctx, gx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid)
-                 : launch_bn<P_MN, Q_MN, false>(ctx, gx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid);
+    return beta1 ? launch_bn<P_MN, Q_MN, true, EPI>(ctx, gx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid)
+                 : launch_bn<P_MN, Q_MN, false, EPI>(ctx, gx, bn, ctas, tmP, tmQ, tmD, tmD32, gp, grid);
 }
-// products 1 and 2 of a launch that has none
-const GemmGroupMaps g_no_group = {};
+// what a single product passes where a grouped launch has its other products' maps
+const GemmNoMaps g_no_group = {};
 
 template <typename T>
 int launch_simt(b200_linear_ctx* ctx, int which, int beta1, T* out, const T* x, const T* y, int M, int N,
@@ -689,9 +690,9 @@ int gemm_bf16(b200_linear_ctx* ctx, int which, int beta1, void* out, const void*
         if (rc) return rc;
     }
 
-    if (p_mn) return launch_beta<true, true>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
-    if (q_mn) return launch_beta<false, true>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
-    return launch_beta<false, false>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    if (p_mn) return launch_beta<true, true, 0>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    if (q_mn) return launch_beta<false, true, 0>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
+    return launch_beta<false, false, 0>(ctx, g_no_group, bn, ctas, beta1, tmP, tmQ, tmD, tmD32, gp, grid);
 }
 
 // Up to three products in one launch (dense operands).
@@ -796,9 +797,9 @@ int gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, voi
         gx.d[i - 1] = tmD[i];
         gx.d32[i - 1] = tmD32[i];
     }
-    if (p_mn) return launch_beta<true, true>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
-    if (q_mn) return launch_beta<false, true>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
-    return launch_beta<false, false>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
+    if (p_mn) return launch_beta<true, true, 3>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
+    if (q_mn) return launch_beta<false, true, 3>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
+    return launch_beta<false, false, 3>(ctx, gx, bn, ctas, beta1, tmP[0], tmQ[0], tmD[0], tmD32[0], gp, grid);
 }
 
 // gate = X W_gate, up = X W_up and hidden = SiLU(gate) * up in one launch: 256-wide pair tiles whose left half is 128

@@ -48,6 +48,22 @@ constexpr int GRP_NONE = 0x7FFFFFFF;
 struct alignas(64) GemmGroupMaps {
     CUtensorMap p[2], q[2], d[2], d32[2];
 };
+// What a launch of a single product passes in their place: nothing (a kilobyte less of kernel parameters per launch).
+struct GemmNoMaps {};
+// EPI (the kernel's last template parameter): 0 = one product, 1 = SwiGLU forward pair, 2 = LM-head forward with
+// cross-entropy statistics, 3 = grouped launch.  1 and 3 carry the extra tensor maps.
+template <int EPI>
+struct GemmExtraMaps {
+    using type = GemmNoMaps;
+};
+template <>
+struct GemmExtraMaps<1> {
+    using type = GemmGroupMaps;
+};
+template <>
+struct GemmExtraMaps<3> {
+    using type = GemmGroupMaps;
+};
 
 struct GemmParams {
     int Mo, No, Kc;          // output rows, output cols, contraction length
@@ -746,7 +762,7 @@ template <int BN, bool P_MN, bool Q_MN, bool BETA1, int CTAS, int EPI = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
                 const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmD32,
-                const __grid_constant__ GemmGroupMaps gx, const GemmParams p) {
+                const __grid_constant__ typename GemmExtraMaps<EPI>::type gx, const GemmParams p) {
     using Cfg = TileCfg<BN, CTAS>;
     constexpr int STAGES = Cfg::STAGES;
     constexpr bool PAIR = CTAS == 2;
@@ -811,10 +827,34 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
     // grouped launch: the maps of product g (g = 0: the kernel's own)
-    auto map_p = [&](int g) { return g == 0 ? &tmP : (g == 1 ? &gx.p[0] : &gx.p[1]); };
-    auto map_q = [&](int g) { return g == 0 ? &tmQ : (g == 1 ? &gx.q[0] : &gx.q[1]); };
-    auto map_d = [&](int g) { return g == 0 ? &tmD : (g == 1 ? &gx.d[0] : &gx.d[1]); };
-    auto map_d32 = [&](int g) { return g == 0 ? &tmD32 : (g == 1 ? &gx.d32[0] : &gx.d32[1]); };
+    constexpr bool HAS_MAPS = EPI == 1 || EPI == 3, GROUPED = EPI == 3;
+    auto map_p = [&](int g) -> const CUtensorMap* {
+        if constexpr (HAS_MAPS) return g == 0 ? &tmP : (g == 1 ? &gx.p[0] : &gx.p[1]);
+        else return &tmP;
+    };
+    auto map_q = [&](int g) -> const CUtensorMap* {
+        if constexpr (HAS_MAPS) return g == 0 ? &tmQ : (g == 1 ? &gx.q[0] : &gx.q[1]);
+        else return &tmQ;
+    };
+    auto map_d = [&](int g) -> const CUtensorMap* {
+        if constexpr (HAS_MAPS) return g == 0 ? &tmD : (g == 1 ? &gx.d[0] : &gx.d[1]);
+        else return &tmD;
+    };
+    auto map_d32 = [&](int g) -> const CUtensorMap* {
+        if constexpr (HAS_MAPS) return g == 0 ? &tmD32 : (g == 1 ? &gx.d32[0] : &gx.d32[1]);
+        else return &tmD32;
+    };
+    // which product a column tile / contraction block belongs to: 0 and origin 0 unless this is a grouped launch
+    auto grp_n = [&](int n_blk, int& base) {
+        if constexpr (GROUPED) return group_of(p.grp_n[0], p.grp_n[1], n_blk, base);
+        base = 0;
+        return 0;
+    };
+    auto grp_k = [&](int kb, int& base) {
+        if constexpr (GROUPED) return group_of(p.grp_k[0], p.grp_k[1], kb, base);
+        base = 0;
+        return 0;
+    };
     // the first work item does not depend on memory: know it before the dependency wait
     WorkItem w_first;
     const bool have_first = get_work(p, slot, nslots, 0, w_first);
@@ -842,7 +882,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             WorkItem w = w_first;
             narrow_to_krank(p, krank, w);
             int n_base;
-            const int gn = group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
+            const int gn = grp_n(w.n_blk, n_base);
             const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
             const int n0 = (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
             const int kb_end = min(w.kb1, w.kb0 + STAGES);
@@ -854,7 +894,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 const int r0 = is_q ? n0 : m0;
                 for (int kb = w.kb0; kb < kb_end; ++kb) {
                     int k_base;
-                    const int gk = group_of(p.grp_k[0], p.grp_k[1], kb, k_base);
+                    const int gk = grp_k(kb, k_base);
                     const CUtensorMap* tm = is_q ? map_q(gn + gk) : map_p(gk);
                     const int c0 = (kb - k_base) * BK;
                     if (!mn) tma_prefetch_l2_2d(tm, c0, r0);
@@ -905,7 +945,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             for (int i = 0; ok && next_work(i, w); ++i) {
                 narrow_to_krank(p, krank, w);
                 int n_base;
-                const int gn = EPI == 1 ? static_cast<int>(rank) : group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
+                const int gn = EPI == 1 ? (n_base = 0, static_cast<int>(rank)) : grp_n(w.n_blk, n_base);
                 const int m0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM;
                 const int n0 = EPI == 1 ? w.n_blk * Cfg::B_ROWS : (w.n_blk - n_base) * BN + static_cast<int>(rank) * Cfg::B_ROWS;
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -922,7 +962,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                     const uint32_t bar = PAIR ? map_to_cta(local_bar, leader) : local_bar;
                     const uint32_t sP = smem_u32(tiles + stage * Cfg::STAGE_BYTES);
                     int k_base;
-                    const int gk = group_of(p.grp_k[0], p.grp_k[1], kb, k_base);
+                    const int gk = grp_k(kb, k_base);
                     const int c0 = (kb - k_base) * BK;
                     if (issuer) {
                         if (rank == 0)
@@ -1031,7 +1071,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
             tc_fence_after();
             const int row0 = (w.m_blk * CTAS + static_cast<int>(rank)) * BM + q * 32;
             int n_base;
-            const int gn = group_of(p.grp_n[0], p.grp_n[1], w.n_blk, n_base);
+            const int gn = grp_n(w.n_blk, n_base);
             const int col_tile = (w.n_blk - n_base) * BN;   // first column of the tile inside its own product
             const CUtensorMap* tmDg = map_d(gn);
             const CUtensorMap* tmD32g = map_d32(gn);
@@ -1046,7 +1086,7 @@ gemm_bf16_sm100(const __grid_constant__ CUtensorMap tmP, const __grid_constant__
                 }
             };
             if constexpr (EPI == 1) {
-                epilogue_swiglu(p, &tmD, &gx.d[0], &gx.d[1], my_buf, taddr, hsel, row0, lane, w.n_blk * 128);
+                epilogue_swiglu(p, map_d(0), map_d(1), map_d(2), my_buf, taddr, hsel, row0, lane, w.n_blk * 128);
                 release_acc();
             } else if constexpr (EPI == 2) {
                 epilogue_store_stats<Cfg::EPI_BUFS>(p, &tmD, my_buf, taddr, hsel, row0, lane, w.n_blk * BN, w.n_blk);
