@@ -159,6 +159,9 @@ typedef struct {
 } b200_linear_plan_t;
 int b200_linear_plan_bf16(int which, int beta1, int M, int N, int K, int sm_count,
                           b200_linear_plan_t* plan);
+/* The plan b200_linear_gemm_bf16_grouped would launch (host arithmetic only; usable without a GPU): the tile width
+ * divides every Ns[i] for the column-concatenated products, plan->bn == 0 when the shapes run as single products. */
+int b200_linear_plan_grouped_bf16(int which, int count, int M, const int* Ns, int K, int sm_count, b200_linear_plan_t* plan);
 /* Force a plan for subsequent bf16 calls on this context (bn = -1 restores the heuristic).
  * splits: 0 = cut only the ragged last wave (automatic), 1 = cut nothing, >= 2 = cut every tile
  * (partials through the workspace), < 0 = share every tile among a cluster of |splits| CTAs (or

@@ -1252,6 +1252,31 @@ extern "C" int b200_linear_gemm_bf16_ld(b200_linear_ctx* ctx, int which, int bet
     if (ld_out < 0 || ld_x < 0 || ld_y < 0) return B200_E_BADARG;
     return gemm_bf16(ctx, which, beta1 ? 1 : 0, out, x, y, M, N, K, 0, 0, ld_out, ld_x, ld_y);
 }
+// The plan of a grouped launch (pure host arithmetic, like b200_linear_plan_bf16): plan->bn == 0 when the shapes do
+// not suit the one-launch path and the products would run one by one.
+extern "C" int b200_linear_plan_grouped_bf16(int which, int count, int M, const int* Ns, int K, int sm_count,
+                                             b200_linear_plan_t* plan) {
+    if (!plan || !Ns || count < 1 || count > 3 || M <= 0 || K <= 0 || sm_count <= 0 || which < 0 || which > 2) return B200_E_BADARG;
+    memset(plan, 0, sizeof(*plan));
+    long long n_total = 0;
+    int n_align = 0;
+    bool fast = count > 1 && (K % 8) == 0 && (which != B200_GEMM_WGRAD_TN || (K % 64) == 0);
+    for (int i = 0; i < count; ++i) {
+        if (Ns[i] <= 0) return B200_E_BADARG;
+        n_total += Ns[i];
+        if ((Ns[i] % 64) != 0) fast = false;
+        int a = n_align, b = Ns[i];
+        while (b) { const int t = a % b; a = b; b = t; }
+        n_align = a;
+    }
+    if (n_total > 0x7FFFFFFF) return B200_E_BADARG;
+    if (!fast) return B200_OK;   // bn = 0: single products
+    const int Nt = static_cast<int>(n_total);
+    if (which == B200_GEMM_FWD_NN) plan_dims(M, Nt, K, sm_count, n_align, plan);
+    else if (which == B200_GEMM_DGRAD_NT) plan_dims(M, K, Nt, sm_count, 0, plan);
+    else plan_dims(K, Nt, M, sm_count, n_align, plan);
+    return B200_OK;
+}
 extern "C" int b200_linear_gemm_bf16_grouped(b200_linear_ctx* ctx, int which, int beta1, int count, void* const* outs,
                                              const void* const* xs, const void* const* ys, int M, const int* Ns, int K) {
     return gemm_bf16_grouped(ctx, which, beta1, count, outs, xs, ys, M, Ns, K);

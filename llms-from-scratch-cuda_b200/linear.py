@@ -263,6 +263,18 @@ def plan_bf16(which, beta1, M, N, K, sm_count=148):
     return p
 
 
+def plan_grouped_bf16(which, M, Ns, K, sm_count=148):
+    """The plan of a grouped launch (host arithmetic only); bn == 0: the products would run one by one."""
+    p = Plan()
+    ns = (ctypes.c_int * 3)(*Ns)
+    lib.b200_linear_plan_grouped_bf16.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_void_p]
+    rc = lib.b200_linear_plan_grouped_bf16(which, len(Ns), M, ns, K, sm_count, ctypes.byref(p))
+    if rc:
+        raise LinearError(rc, "plan_grouped_bf16", f" ({strerror(rc)})")
+    return p
+
+
 # ---- cross-entropy over a vocabulary sharded across GPUs: the per-shard kernels (torch CUDA tensors in,
 # ---- launched on torch's current stream; cuda/crossentropy.cu:96-132 is what they replace in that mode)
 def _ce_check(rc, what):

@@ -89,3 +89,27 @@ def test_estimate_grows_when_sms_are_taken_away(pkg):
             full = pkg.plan_bf16(which, which == 2, 8192, N, K, 148).est_ns
             third = pkg.plan_bf16(which, which == 2, 8192, N, K, 48).est_ns
             assert third > full, (which, N, K, full, third)
+
+
+@pytest.mark.parametrize("which", [0, 1, 2])
+def test_grouped_plan_never_lets_a_tile_straddle_two_products(pkg, which):
+    """Column-concatenated groups (forward, weight gradient): the tile width divides every member's width; the input
+    gradient (products concatenated along the contraction) is planned like one product of the summed width; widths
+    that are not multiples of 64 fall back to single products (bn = 0)."""
+    groups = [(768, 256, 256), (2048, 2048), (1024, 256, 256), (128, 64, 192), (4096, 4096, 4096), (64, 64)]
+    for M, Ns in itertools.product([512, 8192, 16384], groups):
+        K = 768
+        p = pkg.plan_grouped_bf16(which, M, list(Ns), K, 148)
+        assert p.bn in (64, 128, 192, 256)
+        total = sum(Ns)
+        rows = 256 if p.cta_pair else 128
+        if which == 1:   # dX = sum_i dY_i W_i^T: output M x K, contraction = the summed widths
+            assert p.tiles == -(-M // rows) * -(-K // p.bn)
+        else:
+            assert all(n % p.bn == 0 for n in Ns), (Ns, p.bn)
+            out_rows = M if which == 0 else K
+            assert p.tiles == -(-out_rows // rows) * (total // p.bn)
+    assert pkg.plan_grouped_bf16(which, 1024, [72, 136], 264, 148).bn == 0      # not multiples of 64
+    assert pkg.plan_grouped_bf16(which, 1024, [768], 768, 148).bn == 0          # a group of one is a single product
+    with pytest.raises(pkg.LinearError):
+        pkg.plan_grouped_bf16(which, 1024, [768, 0], 768, 148)
